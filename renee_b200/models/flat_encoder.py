@@ -1,0 +1,301 @@
+"""Flat-buffer encoder engine with a hand-written forward and backward pass.
+
+The reference runs the HF encoder under autograd, DDP and apex FusedAdam (main.py:160-161,
+177-181; dl_base.py:299-300, 360, 372).  On B200 the 131K-label configurations are launch-bound,
+so this engine is built for CUDA-graph capture instead:
+
+* every parameter is a view into ONE flat fp32 master buffer (decayed parameters first, then the
+  no-decay group), with a low-precision compute copy, a flat gradient buffer and flat Adam moments —
+  the gradient all-reduce and the fused AdamW each touch one contiguous range;
+* the q/k/v projections are adjacent in the buffer, so one GEMM computes all three;
+* forward and backward are explicit sequences of GEMMs (library calls — framework layer) and fused
+  kernels from :mod:`renee_b200.ops` (bias+dropout+residual+LayerNorm, bias+GELU, attention,
+  embedding gather+LayerNorm, pooling), writing into pre-allocated activations; no autograd graph,
+  no allocator calls inside the step;
+* dropout masks are recomputed from a counter-based RNG in the backward pass.
+
+State-dict keys are those of HF DistilBERT (see :mod:`renee_b200.models.encoder`).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from .. import ops
+from .encoder import EncoderConfig
+
+ALIGN = 128  # elements; keeps every parameter 256-byte aligned in bf16
+
+
+# dropout stream ids (call sites); layer l uses base + 8*l
+_S_EMB, _S_ATTN, _S_FFN, _S_PROBS, _S_CLS = 1, 2, 3, 4, 5
+
+
+def _no_decay(name: str) -> bool:
+    """The reference's no-decay filter is a substring match on ``bias``, ``LayerNorm.bias`` and
+    ``LayerNorm.weight`` (dl_base.py:229).  DistilBERT names its block norms ``sa_layer_norm`` /
+    ``output_layer_norm``, so only biases and ``embeddings.LayerNorm.weight`` escape weight decay."""
+    return any(nd in name for nd in ("bias", "LayerNorm.bias", "LayerNorm.weight"))
+
+
+@dataclass
+class _Slot:
+    offset: int
+    shape: tuple
+    numel: int
+
+
+class FlatEncoder:
+    def __init__(self, cfg: EncoderConfig, device, act_dtype=torch.bfloat16, pooling: str = "mean",
+                 bottleneck_dims: int = 0, seed: int = 0, grad_buffer: torch.Tensor | None = None):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.act_dtype = act_dtype
+        self.pooling = pooling
+        self.bottleneck_dims = int(bottleneck_dims)
+        self.out_dims = self.bottleneck_dims if self.bottleneck_dims > 0 else cfg.dim
+        H, Fd = cfg.dim, cfg.hidden_dim
+        names = [("embeddings.word_embeddings.weight", (cfg.vocab_size, H)),
+                 ("embeddings.position_embeddings.weight", (cfg.max_position_embeddings, H)),
+                 ("embeddings.LayerNorm.weight", (H,)), ("embeddings.LayerNorm.bias", (H,))]
+        for l in range(cfg.n_layers):
+            p = f"transformer.layer.{l}."
+            names += [(p + "attention.q_lin.weight", (H, H)), (p + "attention.k_lin.weight", (H, H)),
+                      (p + "attention.v_lin.weight", (H, H)),
+                      (p + "attention.q_lin.bias", (H,)), (p + "attention.k_lin.bias", (H,)),
+                      (p + "attention.v_lin.bias", (H,)),
+                      (p + "attention.out_lin.weight", (H, H)), (p + "attention.out_lin.bias", (H,)),
+                      (p + "sa_layer_norm.weight", (H,)), (p + "sa_layer_norm.bias", (H,)),
+                      (p + "ffn.lin1.weight", (Fd, H)), (p + "ffn.lin1.bias", (Fd,)),
+                      (p + "ffn.lin2.weight", (H, Fd)), (p + "ffn.lin2.bias", (H,)),
+                      (p + "output_layer_norm.weight", (H,)), (p + "output_layer_norm.bias", (H,))]
+        self.encoder_param_names = [n for n, _ in names]
+        if self.bottleneck_dims > 0:
+            names.append(("__bottleneck__.transformer_weight", (self.bottleneck_dims, H)))
+        decay = [(n, s) for n, s in names if not _no_decay(n)]
+        nodecay = [(n, s) for n, s in names if _no_decay(n)]
+        self.slots: dict[str, _Slot] = {}
+        off = 0
+        for n, s in decay:
+            numel = math.prod(s)
+            self.slots[n] = _Slot(off, s, numel)
+            # q/k/v must stay adjacent (no padding between them): H*H and H are multiples of ALIGN
+            off += (numel + ALIGN - 1) // ALIGN * ALIGN
+        self.n_decay = off
+        for n, s in nodecay:
+            numel = math.prod(s)
+            self.slots[n] = _Slot(off, s, numel)
+            off += (numel + ALIGN - 1) // ALIGN * ALIGN
+        self.numel = off
+        if H % ALIGN != 0:
+            raise ValueError(f"hidden size must be a multiple of {ALIGN}")
+        dev = self.device
+        self.p32 = torch.zeros(off, dtype=torch.float32, device=dev)
+        self.p16 = self.p32 if act_dtype == torch.float32 else torch.zeros(off, dtype=act_dtype, device=dev)
+        if grad_buffer is not None:
+            assert grad_buffer.numel() >= off and grad_buffer.dtype == act_dtype
+            self.g = grad_buffer[:off]
+        else:
+            self.g = torch.zeros(off, dtype=act_dtype, device=dev)
+        self.m = torch.zeros(off, dtype=torch.float32, device=dev)
+        self.v = torch.zeros(off, dtype=torch.float32, device=dev)
+        self._init_params(seed)
+        self._acts = None
+        self._acts_key = None
+
+    # ------------------------------------------------------------------ parameter views
+    def view(self, buf: torch.Tensor, name: str) -> torch.Tensor:
+        s = self.slots[name]
+        return buf[s.offset: s.offset + s.numel].view(s.shape)
+
+    def _qkv(self, buf, l, kind):
+        p = f"transformer.layer.{l}.attention.q_lin.{kind}"
+        s = self.slots[p]
+        H = self.cfg.dim
+        n = 3 * s.numel
+        return buf[s.offset: s.offset + n].view((3 * H, H) if kind == "weight" else (3 * H,))
+
+    def _init_params(self, seed: int) -> None:
+        g = torch.Generator(device="cpu").manual_seed(int(seed))
+        std = self.cfg.initializer_range
+        for n, s in self.slots.items():
+            if n.endswith("LayerNorm.weight") or n.endswith("layer_norm.weight"):
+                t = torch.ones(s.shape)
+            elif n.endswith("bias"):
+                t = torch.zeros(s.shape)
+            elif n.startswith("__bottleneck__"):
+                stdv = 1.0 / math.sqrt(s.shape[1])
+                t = (torch.rand(s.shape, generator=g) * 2 - 1) * stdv
+            else:
+                t = torch.randn(s.shape, generator=g) * std
+                if n == "embeddings.word_embeddings.weight":
+                    t[self.cfg.pad_token_id].zero_()
+            self.view(self.p32, n).copy_(t)
+        self.sync_compute_copy()
+
+    def sync_compute_copy(self) -> None:
+        if self.p16 is not self.p32:
+            self.p16.copy_(self.p32)
+
+    def encoder_state_dict(self) -> dict:
+        return {n: self.view(self.p32, n).detach().clone() for n in self.encoder_param_names}
+
+    def load_encoder_state_dict(self, sd: dict, strict: bool = True) -> None:
+        missing = [n for n in self.encoder_param_names if n not in sd]
+        if strict and missing:
+            raise KeyError(f"missing encoder keys: {missing[:4]} ...")
+        for n in self.encoder_param_names:
+            if n in sd:
+                self.view(self.p32, n).copy_(sd[n].to(self.p32.device, torch.float32))
+        self.sync_compute_copy()
+
+    def bottleneck_weight(self, buf=None):
+        return self.view(self.p32 if buf is None else buf, "__bottleneck__.transformer_weight")
+
+    # ------------------------------------------------------------------ activations
+    def _alloc(self, b: int, S: int):
+        key = (b, S)
+        if self._acts_key is not None and self._acts_key[0] >= b and self._acts_key[1] == S:
+            return
+        cfg, dev, dt = self.cfg, self.device, self.act_dtype
+        T, H, Fd, nh = b * S, cfg.dim, cfg.hidden_dim, cfg.n_heads
+        e = lambda *shape, dtype=dt: torch.empty(*shape, dtype=dtype, device=dev)
+        layers = []
+        for _ in range(cfg.n_layers):
+            layers.append(dict(qkv=e(T, 3 * H), ctx=e(T, H), ao=e(T, H), pre1=e(T, H), h1=e(T, H),
+                               mean1=e(T, dtype=torch.float32), rstd1=e(T, dtype=torch.float32),
+                               f1=e(T, Fd), a1=e(T, Fd), f2=e(T, H), pre2=e(T, H), h2=e(T, H),
+                               mean2=e(T, dtype=torch.float32), rstd2=e(T, dtype=torch.float32),
+                               att=ops.attention_workspace(b, S, nh, dev, dt)))
+        self._acts = dict(h0=e(T, H), mean0=e(T, dtype=torch.float32), rstd0=e(T, dtype=torch.float32),
+                          layers=layers, pooled=e(b, H, dtype=torch.float32),
+                          dh=e(T, H), dh_b=e(T, H), dqkv=e(T, 3 * H), dctx=e(T, H), df1=e(T, Fd), da1=e(T, Fd),
+                          emb=e(b, self.out_dims, dtype=torch.float32))
+        self._acts_key = key
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, input_ids: torch.Tensor, attention_mask: torch.Tensor, rng, train: bool = True) -> torch.Tensor:
+        """ids/mask ``[b, S]`` int32 on the device → pooled embedding ``[b, D]`` fp32 (before the
+        classifier-input dropout)."""
+        cfg = self.cfg
+        b, S = input_ids.shape
+        self._alloc(b, S)
+        A = self._acts
+        T, H = b * S, cfg.dim
+        P = self.p16
+        pd = cfg.dropout if train else 0.0
+        pa = cfg.attention_dropout if train else 0.0
+        self._fw = dict(ids=input_ids, mask=attention_mask, b=b, S=S, pd=pd, pa=pa, rng=rng)
+        h = A["h0"][:T]
+        ops.embed_ln_fwd(input_ids, self.view(P, "embeddings.word_embeddings.weight"),
+                         self.view(P, "embeddings.position_embeddings.weight"),
+                         self.view(P, "embeddings.LayerNorm.weight"), self.view(P, "embeddings.LayerNorm.bias"),
+                         cfg.layer_norm_eps, S, pd, rng, _S_EMB, h, A["mean0"][:T], A["rstd0"][:T])
+        for l, L in enumerate(A["layers"]):
+            pre = f"transformer.layer.{l}."
+            sb = 8 * (l + 1)
+            qkv = L["qkv"][:T]
+            torch.mm(h, self._qkv(P, l, "weight").t(), out=qkv)
+            ctx = L["ctx"][:T]
+            ops.attention_fwd(qkv, self._qkv(P, l, "bias"), attention_mask, cfg.n_heads, pa, rng, sb + _S_PROBS,
+                              ctx, L["att"])
+            ao = L["ao"][:T]
+            torch.mm(ctx, self.view(P, pre + "attention.out_lin.weight").t(), out=ao)
+            h1 = L["h1"][:T]
+            # HF DistilBERT applies no dropout to the attention output projection
+            ops.bias_dropout_add_ln_fwd(ao, self.view(P, pre + "attention.out_lin.bias"), h,
+                                        self.view(P, pre + "sa_layer_norm.weight"), self.view(P, pre + "sa_layer_norm.bias"),
+                                        cfg.layer_norm_eps, 0.0, rng, sb + _S_ATTN,
+                                        h1, L["pre1"][:T], L["mean1"][:T], L["rstd1"][:T])
+            f1 = L["f1"][:T]
+            torch.mm(h1, self.view(P, pre + "ffn.lin1.weight").t(), out=f1)
+            a1 = L["a1"][:T]
+            ops.bias_gelu_fwd(f1, self.view(P, pre + "ffn.lin1.bias"), a1)
+            f2 = L["f2"][:T]
+            torch.mm(a1, self.view(P, pre + "ffn.lin2.weight").t(), out=f2)
+            h2 = L["h2"][:T]
+            ops.bias_dropout_add_ln_fwd(f2, self.view(P, pre + "ffn.lin2.bias"), h1,
+                                        self.view(P, pre + "output_layer_norm.weight"),
+                                        self.view(P, pre + "output_layer_norm.bias"),
+                                        cfg.layer_norm_eps, pd, rng, sb + _S_FFN,
+                                        h2, L["pre2"][:T], L["mean2"][:T], L["rstd2"][:T])
+            L["h_in"] = h
+            h = h2
+        pooled = A["pooled"][:b]
+        ops.pool_fwd(h.view(b, S, H), attention_mask, self.pooling, pooled)
+        if self.bottleneck_dims > 0:
+            emb = A["emb"][:b]
+            torch.mm(pooled, self.bottleneck_weight().t(), out=emb)   # fp32, master weights
+            return emb
+        return pooled
+
+    # ------------------------------------------------------------------ backward
+    def backward(self, d_emb: torch.Tensor, on_layer_done=None) -> None:
+        """``d_emb [b, D]`` fp32 → gradients of every parameter written into the flat ``g`` buffer
+        (overwritten, not accumulated).  ``on_layer_done(lo, hi)`` is called with the flat range
+        whose gradients have just become final, so a caller can start reducing it across ranks while
+        the remaining layers are still being differentiated."""
+        cfg, A, fw = self.cfg, self._acts, self._fw
+        b, S, pd, pa, rng = fw["b"], fw["S"], fw["pd"], fw["pa"], fw["rng"]
+        T, H = b * S, cfg.dim
+        P, G = self.p16, self.g
+        mask = fw["mask"]
+        if self.bottleneck_dims > 0:
+            gw = self.view(G, "__bottleneck__.transformer_weight")
+            pooled = A["pooled"][:b]
+            if gw.dtype == torch.float32:
+                torch.mm(d_emb.t(), pooled, out=gw)
+            else:
+                gw.copy_(torch.mm(d_emb.t(), pooled))
+            d_pool = torch.mm(d_emb, self.bottleneck_weight())
+        else:
+            d_pool = d_emb
+        dh = A["dh"][:T]
+        ops.pool_bwd(d_pool, mask, self.pooling, S, dh.view(b, S, H))
+        for l in reversed(range(cfg.n_layers)):
+            L = A["layers"][l]
+            pre = f"transformer.layer.{l}."
+            sb = 8 * (l + 1)
+            h_in = L["h_in"]
+            # ---- output LN + FFN
+            d_pre2, d_f2 = ops.bias_dropout_add_ln_bwd(
+                dh, L["pre2"][:T], self.view(P, pre + "output_layer_norm.weight"), L["mean2"][:T], L["rstd2"][:T],
+                pd, rng, sb + _S_FFN,
+                self.view(G, pre + "output_layer_norm.weight"), self.view(G, pre + "output_layer_norm.bias"),
+                self.view(G, pre + "ffn.lin2.bias"), A["dh_b"][:T], L["f2"][:T])
+            torch.mm(d_f2.t(), L["a1"][:T], out=self.view(G, pre + "ffn.lin2.weight"))
+            da1 = A["da1"][:T]
+            torch.mm(d_f2, self.view(P, pre + "ffn.lin2.weight"), out=da1)
+            df1 = A["df1"][:T]
+            ops.bias_gelu_bwd(da1, L["f1"][:T], self.view(P, pre + "ffn.lin1.bias"),
+                              self.view(G, pre + "ffn.lin1.bias"), df1)
+            torch.mm(df1.t(), L["h1"][:T], out=self.view(G, pre + "ffn.lin1.weight"))
+            # dh1 = d_pre2 (residual) + df1 @ W1
+            dh1 = torch.addmm(d_pre2, df1, self.view(P, pre + "ffn.lin1.weight"), out=dh)
+            # ---- attention LN + attention
+            d_pre1, d_ao = ops.bias_dropout_add_ln_bwd(
+                dh1, L["pre1"][:T], self.view(P, pre + "sa_layer_norm.weight"), L["mean1"][:T], L["rstd1"][:T],
+                0.0, rng, sb + _S_ATTN,
+                self.view(G, pre + "sa_layer_norm.weight"), self.view(G, pre + "sa_layer_norm.bias"),
+                self.view(G, pre + "attention.out_lin.bias"), A["dh_b"][:T], L["ao"][:T])
+            torch.mm(d_ao.t(), L["ctx"][:T], out=self.view(G, pre + "attention.out_lin.weight"))
+            dctx = A["dctx"][:T]
+            torch.mm(d_ao, self.view(P, pre + "attention.out_lin.weight"), out=dctx)
+            dqkv = A["dqkv"][:T]
+            ops.attention_bwd(dctx, L["qkv"][:T], self._qkv(P, l, "bias"), mask, cfg.n_heads, pa, rng,
+                              sb + _S_PROBS, L["att"], dqkv, self._qkv(G, l, "bias"))
+            torch.mm(dqkv.t(), h_in, out=self._qkv(G, l, "weight"))
+            torch.addmm(d_pre1, dqkv, self._qkv(P, l, "weight"), out=dh)
+            if on_layer_done is not None:
+                on_layer_done(l)
+        ops.embed_ln_bwd(dh, fw["ids"], self.view(P, "embeddings.word_embeddings.weight"),
+                         self.view(P, "embeddings.position_embeddings.weight"),
+                         self.view(P, "embeddings.LayerNorm.weight"), A["mean0"][:T], A["rstd0"][:T],
+                         S, pd, rng, _S_EMB, cfg.pad_token_id,
+                         self.view(G, "embeddings.word_embeddings.weight"),
+                         self.view(G, "embeddings.position_embeddings.weight"),
+                         self.view(G, "embeddings.LayerNorm.weight"), self.view(G, "embeddings.LayerNorm.bias"))
+        if on_layer_done is not None:
+            on_layer_done(-1)

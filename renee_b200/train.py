@@ -1,0 +1,423 @@
+"""Training runtime: the optimized loss-skipping step, the autograd baseline step, the epoch loop.
+
+Parity with the reference's ``GenericModel`` (dl_base.py:146-455):
+
+* ``XCTrainer.train_step``  ↔ the optimized branch of ``fit`` (dl_base.py:297-378): encoder forward,
+  embedding all-gather, manual classifier forward/backward with loss skipping, SGD-momentum on the
+  classifier (unscaled), hand-off of the encoder-input gradient ``dX`` (scaled by the loss scale),
+  encoder backward, Adam on the encoder, both cosine schedules stepped every iteration;
+* ``XCTrainer.default_step`` ↔ ``--default-impl`` (dl_base.py:274-295): dense targets,
+  ``BCEWithLogitsLoss(sum)`` and autograd — the numerical oracle of the optimized path;
+* ``fit`` ↔ the epoch loop with evaluation every ``evaluation_epochs`` epochs and on the last one,
+  and a checkpoint per epoch (dl_base.py:382-393).
+
+On a GPU the optimized step is a fixed sequence of kernel launches on static buffers (no autograd
+graph, no allocation), which is what allows it to be captured in a CUDA graph; step-varying values
+(learning rates, dropout seed, loss scale) are read from device memory.
+"""
+from __future__ import annotations
+
+import os
+import random
+import sys
+import time
+from dataclasses import dataclass, field, asdict
+
+import numpy as np
+import torch
+import torch.nn as nn
+
+from . import ops
+from .data.collate import XCBatch
+from .models.encoder import (DistilEncoder, EncoderConfig, FP32Linear, TransformerInputLayer)
+from .models.flat_encoder import FlatEncoder
+from .models.xfc import XFCClassifier
+from .optim.hparams import HP, HyperParams
+from .optim.schedule import CosineWarmupSchedule
+from .ops.rng import DropoutRNG
+from .parallel.collectives import TorchCollectives
+from .parallel.dist import DistContext
+from .utils.sharding import LabelSharding, batch_row_range
+
+LOSS_SAMPLE_FREQ = 100   # dl_base.py:144
+_S_CLS_DROPOUT = 5
+
+
+@dataclass
+class TrainConfig:
+    batch_size: int = 8            # per GPU
+    epochs: int = 50
+    expname: str = "renee-exp"
+    seed: int = 42
+    bottleneck_dims: int = 0
+    dropout: float = 0.5
+    lr1: float = 0.0025
+    lr2: float = 1e-5
+    mo: float = 0.9
+    wd1: float = 0.01
+    wd2: float = 0.01
+    fp32encoder: bool = False
+    fp16xfc: bool = False
+    noloss: bool = False
+    checkpoint_resume: str = ""
+    warmup: int = 140000
+    accum: int = 1
+    maxlen: int = 32
+    default_impl: bool = False
+    custom_cuda: bool = False
+    pooling: str = "mean"
+    encoder_dtype: str = "bf16"      # compute dtype of the encoder on a GPU unless fp32encoder
+    adam_eps: float = 1e-6           # main.py:181
+    evaluation_epochs: int = 5       # main.py:184
+    cuda_graph: bool = True
+    fused_comm: bool = True
+    stochastic_round: bool = False
+    out_dir: str = ""
+
+    @classmethod
+    def from_args(cls, args) -> "TrainConfig":
+        names = cls.__dataclass_fields__.keys()
+        return cls(**{k: getattr(args, k) for k in names if hasattr(args, k)})
+
+
+class DefaultModel(nn.Module):
+    """Module layout of the reference's ``GenericModel``: ``embed = Sequential(encoder wrapper,
+    [bottleneck], dropout)`` and ``xfc_weight [Ls, D]`` (dl_base.py:147-187)."""
+
+    def __init__(self, enc_cfg: EncoderConfig, labels_per_rank: int, cfg: TrainConfig):
+        super().__init__()
+        mods = [TransformerInputLayer(DistilEncoder(enc_cfg), cfg.pooling)]
+        D = enc_cfg.dim
+        if cfg.bottleneck_dims > 0:
+            mods.append(FP32Linear(enc_cfg.dim, cfg.bottleneck_dims, bias=False))
+            D = cfg.bottleneck_dims
+        mods.append(nn.Dropout(cfg.dropout))
+        self.embed = nn.Sequential(*mods)
+        self.xfc_weight = nn.Parameter(torch.empty(labels_per_rank, D))
+        nn.init.normal_(self.xfc_weight, mean=0.0, std=0.02)
+
+
+def split_param_groups(named_params, wd2: float):
+    """The reference's grouping (dl_base.py:219-236): names containing ``xfc`` → SGD; everything else
+    → Adam with a no-decay group for names containing ``bias`` / ``LayerNorm.bias`` /
+    ``LayerNorm.weight``."""
+    xfc, tf = [], []
+    for n, p in named_params:
+        if p.requires_grad:
+            (xfc if "xfc" in n else tf).append((n, p))
+    nd = ("bias", "LayerNorm.bias", "LayerNorm.weight")
+    groups = [{"params": [p for n, p in tf if not any(k in n for k in nd)], "weight_decay": wd2},
+              {"params": [p for n, p in tf if any(k in n for k in nd)], "weight_decay": 0.0}]
+    return [p for _, p in xfc], groups
+
+
+class XCTrainer:
+    def __init__(self, cfg: TrainConfig, enc_cfg: EncoderConfig, sharding: LabelSharding, ctx: DistContext,
+                 steps_per_epoch: int, comm=None):
+        self.cfg = cfg
+        self.enc_cfg = enc_cfg
+        self.sharding = sharding
+        self.ctx = ctx
+        self.rank, self.G = ctx.rank, ctx.world_size
+        self.device = ctx.device
+        self.comm = comm if comm is not None else TorchCollectives(ctx)
+        self.steps_per_epoch = int(steps_per_epoch)
+        self.total_steps = int(steps_per_epoch * cfg.epochs)
+        self.epoch = 0
+        self.count = 0                      # optimizer steps taken (dl_base.py:363)
+        self.best_score = -9999999.0
+        self.name = cfg.expname
+        self.out_dir = cfg.out_dir
+        if self.out_dir:
+            os.makedirs(self.out_dir, exist_ok=True)
+        self.B = cfg.batch_size * self.G
+        self.Ls = sharding.labels_per_rank
+        on_gpu = self.device.type == "cuda"
+        self.act_dtype = torch.float32 if (cfg.fp32encoder or not on_gpu) else \
+            (torch.bfloat16 if cfg.encoder_dtype == "bf16" else torch.float16)
+        self.xfc_sched = CosineWarmupSchedule(cfg.lr1, cfg.warmup, self.total_steps)
+        self.tf_sched = CosineWarmupSchedule(cfg.lr2, cfg.warmup, self.total_steps)
+        self.rng = DropoutRNG(cfg.seed)
+        self.hp = HyperParams(self.device, init_scale=2.0 ** 12 if cfg.fp16xfc else 2.0 ** 16,
+                              enabled=not cfg.fp32encoder)
+        self.step_rng = ops.StepRNG(0, self.hp.seed_tensor())
+        self.loss_sum = 0.0
+        self.loss_steps = 0
+        if cfg.default_impl:
+            self._init_default()
+        else:
+            self._init_optimized()
+
+    # ------------------------------------------------------------------ construction
+    def _init_default(self) -> None:
+        cfg = self.cfg
+        torch.manual_seed(cfg.seed)
+        self.model = DefaultModel(self.enc_cfg, self.Ls, cfg).to(self.device)
+        xfc_params, tf_groups = split_param_groups(self.model.named_parameters(), cfg.wd2)
+        self.xfc_optimizer = torch.optim.SGD(xfc_params, lr=cfg.lr1, momentum=cfg.mo, weight_decay=cfg.wd1)
+        self.tf_optimizer = torch.optim.AdamW(tf_groups, lr=cfg.lr2, eps=cfg.adam_eps)
+        self.loss_fn = nn.BCEWithLogitsLoss(reduction="sum")
+
+    def _init_optimized(self) -> None:
+        cfg = self.cfg
+        D = cfg.bottleneck_dims if cfg.bottleneck_dims > 0 else self.enc_cfg.dim
+        self.D = D
+        self.encoder = FlatEncoder(self.enc_cfg, self.device, self.act_dtype, cfg.pooling, cfg.bottleneck_dims,
+                                   seed=cfg.seed, grad_buffer=self.comm.grad_buffer(self.act_dtype, self.enc_cfg, cfg)
+                                   if hasattr(self.comm, "grad_buffer") else None)
+        self.xfc = XFCClassifier(self.Ls, D, self.device, cfg.fp16xfc,
+                                 rank=self.rank, seed=cfg.seed, max_batch=self.B, accum=cfg.accum,
+                                 stochastic_round=cfg.stochastic_round)
+        dev = self.device
+        b, S = cfg.batch_size + 1, cfg.maxlen
+        self.max_nnz = 0
+        self.buf = dict(
+            ids=torch.zeros(b, S, dtype=torch.int32, device=dev),
+            mask=torch.zeros(b, S, dtype=torch.int32, device=dev),
+            x_local=torch.zeros(b, D, dtype=self.xfc.dtype, device=dev),
+            X=torch.zeros(self.B + self.G, D, dtype=self.xfc.dtype, device=dev),
+            dX=torch.zeros(self.B + self.G, D, dtype=torch.float32, device=dev),
+            dx_local=torch.zeros(b, D, dtype=torch.float32, device=dev),
+            de=torch.zeros(b, D, dtype=torch.float32, device=dev),
+            nnz=torch.zeros(1, dtype=torch.int32, device=dev),
+            loss=torch.zeros(1, dtype=torch.float32, device=dev),
+        )
+        self._ensure_pos_capacity(max(1024, self.B * 8))
+
+    def _ensure_pos_capacity(self, n: int) -> None:
+        if n <= self.max_nnz:
+            return
+        cap = 1
+        while cap < n:
+            cap *= 2
+        self.max_nnz = cap
+        self.buf["pos_rows"] = torch.zeros(cap, dtype=torch.int32, device=self.device)
+        self.buf["pos_labels"] = torch.zeros(cap, dtype=torch.int32, device=self.device)
+        self._graph = None   # static addresses changed
+
+    # ------------------------------------------------------------------ one step (optimized)
+    def _set_hparams(self) -> None:
+        seed = self.rng.seed_for_step()
+        self.step_rng.set(seed)
+        self.hp.set_step(self.xfc_sched.lr(), self.tf_sched.lr(), seed)
+        self.hp.upload()
+
+    def _upload(self, batch: XCBatch) -> tuple[int, int]:
+        b = batch.input_ids.shape[0]
+        nnz = int(batch.pos_rows.numel())
+        self._ensure_pos_capacity(nnz)
+        bf = self.buf
+        bf["ids"][:b].copy_(batch.input_ids, non_blocking=True)
+        bf["mask"][:b].copy_(batch.attention_mask, non_blocking=True)
+        bf["pos_rows"][:nnz].copy_(batch.pos_rows, non_blocking=True)
+        bf["pos_labels"][:nnz].copy_(batch.pos_labels, non_blocking=True)
+        bf["nnz"].fill_(nnz)
+        return b, nnz
+
+    def h2d_bytes(self, batch: XCBatch) -> int:
+        return int(batch.input_ids.numel() * 4 + batch.attention_mask.numel() * 4 + batch.pos_rows.numel() * 8
+                   + HP.HOST_SLOTS * 4)
+
+    def train_step(self, batch: XCBatch) -> torch.Tensor | None:
+        """Runs one optimized step; returns the sampled loss tensor (device, un-normalised) on
+        sampling steps, else ``None``.  No host synchronisation happens here."""
+        if self.cfg.default_impl:
+            return self.default_step(batch)
+        cfg = self.cfg
+        self._set_hparams()
+        b, nnz = self._upload(batch)
+        B = batch.batch_size
+        want_loss = (not cfg.noloss) and (self.count % LOSS_SAMPLE_FREQ == 0)
+        loss = self._device_step(b, B, nnz, want_loss)
+        self.count += 1
+        self.rng.advance()
+        self.xfc_sched.step()
+        self.tf_sched.step()
+        if want_loss:
+            self._pending_loss = (loss, B)
+        return loss
+
+    def _device_step(self, b: int, B: int, nnz: int, want_loss: bool):
+        cfg, bf, enc = self.cfg, self.buf, self.encoder
+        ids, mask = bf["ids"][:b], bf["mask"][:b]
+        emb = enc.forward(ids, mask, self.step_rng, train=True)
+        x_local = bf["x_local"][:b]
+        ops.dropout_cast_fwd(emb, cfg.dropout, self.step_rng, _S_CLS_DROPOUT, x_local)
+        X = self.comm.gather_embeddings(x_local, B, bf["X"])
+        dX = bf["dX"][:B]
+        loss = self.xfc.step(X, bf["pos_rows"], bf["pos_labels"], bf["nnz"] if X.is_cuda else nnz, dX,
+                             self.hp, cfg.mo, cfg.wd1, want_loss)
+        if want_loss:
+            loss = self.comm.allreduce_scalar(loss.reshape(1))
+        dx_local = self.comm.reduce_scatter_dx(dX, B, bf["dx_local"])
+        de = bf["de"][:b]
+        ops.dropout_bwd(dx_local, cfg.dropout, self.step_rng, _S_CLS_DROPOUT, de)
+        enc.backward(de)
+        self.comm.allreduce_grads(enc.g, self.hp)
+        ops.adamw_step(enc.p32, enc.m, enc.v, enc.g, enc.p16, self.hp, 0.9, 0.999, cfg.adam_eps, cfg.wd2, enc.n_decay)
+        self.hp.update_scale()
+        return loss
+
+    def pop_loss(self) -> float | None:
+        """Normalised sampled loss of the most recent sampling step (synchronises)."""
+        pend = getattr(self, "_pending_loss", None)
+        if pend is None:
+            return None
+        loss, B = pend
+        self._pending_loss = None
+        return float(loss.item()) / (B * self.sharding.padded_labels)
+
+    # ------------------------------------------------------------------ one step (autograd baseline)
+    def default_step(self, batch: XCBatch):
+        cfg, m = self.cfg, self.model
+        dev = self.device
+        B = batch.batch_size
+        data = {"input_ids": batch.input_ids.to(dev), "attention_mask": batch.attention_mask.to(dev)}
+        embed = m.embed(data)
+        X = _AllGatherRows.apply(embed, self.comm, B) if self.G > 1 else embed
+        out = X @ m.xfc_weight.t()
+        y = batch.dense_targets.to(dev)
+        loss = self.loss_fn(out, y)
+        loss.backward()
+        if self.G > 1:  # DDP semantics: encoder gradients are averaged over ranks
+            for n, p in m.named_parameters():
+                if "xfc" not in n and p.grad is not None:
+                    torch.distributed.all_reduce(p.grad)
+                    p.grad.mul_(1.0 / self.G)
+        for opt, sched in ((self.xfc_optimizer, self.xfc_sched), (self.tf_optimizer, self.tf_sched)):
+            for g in opt.param_groups:
+                g["lr"] = sched.lr()
+            opt.step()
+            opt.zero_grad(set_to_none=True)
+            sched.step()
+        self.count += 1
+        self._pending_loss = (loss.detach().reshape(1).clone(), B)
+        if self.G > 1:
+            self.comm.allreduce_scalar(self._pending_loss[0])
+        return self._pending_loss[0]
+
+    # ------------------------------------------------------------------ state dict (reference layout)
+    def state_dict(self) -> dict:
+        if self.cfg.default_impl:
+            return {k: v.detach().clone() for k, v in self.model.state_dict().items()}
+        sd = {"xfc_weight": self.xfc.state_dict_weight()}
+        for k, v in self.encoder.encoder_state_dict().items():
+            sd[f"embed.0.transformer.{k}"] = v
+        if self.cfg.bottleneck_dims > 0:
+            sd["embed.1.transformer_weight"] = self.encoder.bottleneck_weight().detach().clone()
+        return sd
+
+    def load_state_dict(self, sd: dict) -> None:
+        sd = normalise_state_dict_keys(sd)
+        if self.cfg.default_impl:
+            self.model.load_state_dict(sd)
+            return
+        self.xfc.load_weight(sd["xfc_weight"])
+        pre = "embed.0.transformer."
+        self.encoder.load_encoder_state_dict({k[len(pre):]: v for k, v in sd.items() if k.startswith(pre)})
+        if self.cfg.bottleneck_dims > 0:
+            self.encoder.bottleneck_weight().copy_(sd["embed.1.transformer_weight"].to(self.device, torch.float32))
+            self.encoder.sync_compute_copy()
+
+    # ------------------------------------------------------------------ epoch loop
+    def fit(self, loader, evaluator=None, log=print) -> None:
+        from .checkpoint import maybe_resume, save_checkpoint
+        cfg = self.cfg
+        if cfg.checkpoint_resume:
+            prev = maybe_resume(self, cfg.checkpoint_resume)
+            if prev is not None:
+                log(f"Resuming training from epoch:  {self.epoch} with loss:  {prev}")
+            else:
+                log("No checkpoint file to resume. Starting training from scratch")
+        for epoch in range(self.epoch, cfg.epochs):
+            self.epoch = epoch
+            self.loss_sum, self.loss_steps = 0.0, 0
+            t0 = time.time()
+            n_rows = 0
+            for batch in loader.epoch(epoch):
+                self.train_step(batch)
+                n_rows += batch.batch_size
+                l = self.pop_loss()
+                if l is not None:
+                    self.loss_sum += l
+                    self.loss_steps += 1
+            if self.device.type == "cuda":
+                torch.cuda.synchronize()
+            mean_loss = self.loss_sum / self.loss_steps if self.loss_steps else 0.0
+            if self.ctx.is_main:
+                log(f"mean loss after epoch {epoch} : {'%.4E' % mean_loss}")
+                log(f"Scale:  {self.hp.get_scale()}")
+                log(f"epoch {epoch}: {n_rows / max(time.time() - t0, 1e-9):.1f} samples/s (wall)")
+                sys.stdout.flush()
+            last = epoch == cfg.epochs - 1
+            if evaluator is not None and (((epoch + 1) % cfg.evaluation_epochs == 0) or last):
+                evaluator(self, epoch, mean_loss, self.out_dir, self.name)
+            if cfg.checkpoint_resume:
+                save_checkpoint(self, cfg.checkpoint_resume, mean_loss)
+        self.epoch = cfg.epochs
+
+    def save(self, out_dir: str | None = None) -> str:
+        out_dir = out_dir or self.out_dir
+        os.makedirs(out_dir, exist_ok=True)
+        path = os.path.join(out_dir, f"{self.name}_{self.rank}_state_dict.pt")
+        torch.save(self.state_dict(), path)
+        return path
+
+    def load(self, out_dir: str | None = None) -> None:
+        out_dir = out_dir or self.out_dir
+        path = os.path.join(out_dir, f"{self.name}_{self.rank}_state_dict.pt")
+        self.load_state_dict(torch.load(path, map_location="cpu"))
+
+    # ------------------------------------------------------------------ inference helpers
+    @torch.no_grad()
+    def embed_eval(self, batch: XCBatch) -> torch.Tensor:
+        """Embeddings of this rank's rows in eval mode (no dropout), classifier dtype."""
+        dev = self.device
+        if self.cfg.default_impl:
+            self.model.eval()
+            e = self.model.embed({"input_ids": batch.input_ids.to(dev), "attention_mask": batch.attention_mask.to(dev)})
+            self.model.train()
+            return e
+        b = batch.input_ids.shape[0]
+        ids = batch.input_ids.to(dev, non_blocking=True)
+        mask = batch.attention_mask.to(dev, non_blocking=True)
+        emb = self.encoder.forward(ids, mask, self.step_rng, train=False)
+        return emb.to(self.xfc.dtype)
+
+    def local_topk(self, X: torch.Tensor, k: int):
+        if self.cfg.default_impl:
+            Z = X.float() @ self.model.xfc_weight.float().t()
+            return torch.topk(Z, min(k, Z.shape[1]), dim=1)
+        return self.xfc.topk(X, k)
+
+
+class _AllGatherRows(torch.autograd.Function):
+    """All-gather with gradient: the backward sums every rank's gradient and returns this rank's
+    rows — the reference's ``AllGather`` autograd function (dl_base.py:457-481)."""
+
+    @staticmethod
+    def forward(ctx, x_local, comm, B):
+        ctx.comm, ctx.B, ctx.b = comm, B, x_local.shape[0]
+        out = torch.empty(B, x_local.shape[1], dtype=x_local.dtype, device=x_local.device)
+        return comm.gather_embeddings(x_local.detach(), B, out).clone()
+
+    @staticmethod
+    def backward(ctx, grad):
+        out = torch.empty(ctx.b, grad.shape[1], dtype=grad.dtype, device=grad.device)
+        return ctx.comm.reduce_scatter_dx(grad.contiguous(), ctx.B, out).clone(), None, None
+
+
+def normalise_state_dict_keys(sd: dict) -> dict:
+    """Accept the key variants the reference's wrappers produce: DDP inserts ``module.`` after
+    ``embed.`` (main.py:161) and ``torch.compile`` inserts ``_orig_mod.`` (main.py:156)."""
+    out = {}
+    for k, v in sd.items():
+        k2 = k.replace("embed.module.", "embed.").replace("._orig_mod.", ".")
+        out[k2] = v
+    return out
+
+
+def seed_everything(seed: int) -> None:
+    torch.manual_seed(seed)
+    random.seed(seed)
+    np.random.seed(seed)
