@@ -91,7 +91,8 @@ class XFCClassifier:
     def scratch(self, B: int):
         if self._scratch is None or self._scratch["B"] < B:
             chunk = min(self.chunk, (self.Ls + 127) // 128 * 128)
-            self._scratch = {"B": B, "Gt": torch.empty(chunk * B, dtype=torch.float16 if self.dtype == torch.float16 else torch.float32,
+            ldg = (B + 7) // 8 * 8
+            self._scratch = {"B": B, "Gt": torch.empty(chunk * ldg, dtype=torch.float16 if self.dtype == torch.float16 else torch.float32,
                                                       device=self.device)}
         return self._scratch
 

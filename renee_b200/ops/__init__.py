@@ -136,12 +136,12 @@ def dropout_bwd(dx, p, rng, stream, out):
 
 
 # ----------------------------------------------------------------------------- optimizer
-def adamw_step(p32, m, v, g, p16, hp, beta1, beta2, eps, wd, n_decay):
+def adamw_step(p32, m, v, g, p16, hp, beta1, beta2, eps, wd, n_decay, grad_mult=1.0):
     """``hp`` is the device-resident hyper-parameter block (see :mod:`renee_b200.optim.hparams`):
     learning rate, Adam step count, inverse loss scale and the found-inf flag are read from it."""
     if _is_cuda(p32):
-        return _cuda().adamw_step(p32, m, v, g, p16, hp, beta1, beta2, eps, wd, n_decay)
+        return _cuda().adamw_step(p32, m, v, g, p16, hp, beta1, beta2, eps, wd, n_decay, grad_mult)
     from ..optim.hparams import HP
     h = hp.buf
     ref.adamw_step(p32, m, v, g, None if p16 is p32 else p16, float(h[HP.LR_ENC]), beta1, beta2, eps, wd, n_decay,
-                   float(h[HP.ADAM_STEP]) + 1.0, float(h[HP.INV_SCALE]), float(h[HP.FOUND_INF]))
+                   float(h[HP.ADAM_STEP]) + 1.0, float(h[HP.INV_SCALE]) * grad_mult, float(h[HP.FOUND_INF]))

@@ -1,0 +1,583 @@
+// Fused encoder kernels (memory-bound, one pass over the activations each):
+//   embed_ln_fwd / embed_ln_bwd            word+position gather, LayerNorm, dropout (+ scatter of gradients)
+//   bias_dropout_add_ln_fwd / _bwd         y = LN(resid + dropout(x + bias))
+//   bias_gelu_fwd / _bwd                   exact-erf GELU with the bias add and the bias gradient fused
+//   pool_fwd / pool_bwd                    mask-weighted mean or CLS pooling
+//   dropout_cast_fwd / dropout_bwd         classifier-input dropout
+//   colsum                                 column sums (bias gradients)
+// They stand in for the ATen/Inductor kernels behind the HF encoder the reference runs
+// (dl_base.py:121-141 and the DistilBERT blocks it wraps).  Rows are handled one warp each with
+// 16-byte accesses; column reductions (dgamma, dbeta, dbias) are accumulated in registers across the
+// rows of a warp, combined per block in shared memory, added to an fp32 accumulator in global memory
+// and converted by the last block to finish, which also re-zeroes the accumulator for the next call.
+#include "common.cuh"
+
+namespace rb {
+
+constexpr int kMaxNV = 8;  // hidden sizes up to 2048
+
+template <typename T> __device__ __forceinline__ void atomic_add8(T* p, const float (&v)[8]);
+template <> __device__ __forceinline__ void atomic_add8<float>(float* p, const float (&v)[8]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) atomicAdd(p + i, v[i]);
+}
+template <> __device__ __forceinline__ void atomic_add8<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[8]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    atomicAdd(reinterpret_cast<__nv_bfloat162*>(p) + i, __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]));
+}
+template <> __device__ __forceinline__ void atomic_add8<__half>(__half* p, const float (&v)[8]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    atomicAdd(reinterpret_cast<__half2*>(p) + i, __floats2half2_rn(v[2 * i], v[2 * i + 1]));
+}
+
+// Last-block-done column reduction epilogue.  Every block has already added its partial sums to
+// acc[n_vec][H] (fp32, global).  The last block converts acc to the outputs and clears it.
+template <typename T>
+__device__ void finalize_columns(float* acc, unsigned* counter, int n_vec, int H, T* o0, T* o1, T* o2) {
+  __shared__ bool last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned done = atomicAdd(counter, 1u);
+    last = (done == gridDim.x * gridDim.y - 1);
+  }
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  T* outs[3] = {o0, o1, o2};
+  for (int v = 0; v < n_vec; ++v) {
+    if (outs[v] == nullptr) continue;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+      float s = __ldcg(acc + (size_t)v * H + c);
+      outs[v][c] = from_f<T>(s);
+    }
+  }
+  for (int i = threadIdx.x; i < n_vec * H; i += blockDim.x) acc[i] = 0.f;
+  if (threadIdx.x == 0) *counter = 0u;
+}
+
+// ------------------------------------------------------------------------------------ LN forward
+template <typename T, int NV>
+__global__ void __launch_bounds__(128) bias_dropout_add_ln_fwd_kernel(
+    const T* __restrict__ x, const T* __restrict__ bias, const T* __restrict__ resid,
+    const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y, T* __restrict__ pre,
+    float* __restrict__ mean, float* __restrict__ rstd, int rows, int H, float eps, float p,
+    const int* __restrict__ seed_ptr, uint32_t stream) {
+  const int lane = threadIdx.x & 31;
+  const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (row >= rows) return;
+  const uint32_t seed = p > 0.f ? (uint32_t)(*seed_ptr) : 0u;
+  const float inv_keep = p > 0.f ? 1.f / (1.f - p) : 1.f;
+  float v[NV][8];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int col = (lane + 32 * i) * 8;
+    if (col < H) {
+      float a[8], b[8], r[8];
+      load8(x + (size_t)row * H + col, a);
+      load8(bias + col, b);
+      load8(resid + (size_t)row * H + col, r);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float t = a[j] + b[j];
+        if (p > 0.f) t = keep(seed, stream, (uint32_t)(row * H + col + j), p) ? t * inv_keep : 0.f;
+        v[i][j] = round_through<T>(r[j] + t);
+        sum += v[i][j];
+      }
+      store8(pre + (size_t)row * H + col, v[i]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
+    }
+  }
+  const float mu = warp_sum(sum) / H;
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int col = (lane + 32 * i) * 8;
+    if (col < H) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { float d = v[i][j] - mu; sq += d * d; }
+    }
+  }
+  const float rs = rsqrtf(warp_sum(sq) / H + eps);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int col = (lane + 32 * i) * 8;
+    if (col < H) {
+      float g[8], b[8], o[8];
+      load8(gamma + col, g);
+      load8(beta + col, b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mu) * rs * g[j] + b[j];
+      store8(y + (size_t)row * H + col, o);
+    }
+  }
+  if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
+}
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(128) embed_ln_fwd_kernel(
+    const int* __restrict__ ids, const T* __restrict__ word, const T* __restrict__ pos,
+    const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y,
+    float* __restrict__ mean, float* __restrict__ rstd, int rows, int H, int S, float eps, float p,
+    const int* __restrict__ seed_ptr, uint32_t stream) {
+  const int lane = threadIdx.x & 31;
+  const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (row >= rows) return;
+  const uint32_t seed = p > 0.f ? (uint32_t)(*seed_ptr) : 0u;
+  const float inv_keep = p > 0.f ? 1.f / (1.f - p) : 1.f;
+  const int id = ids[row];
+  const int s = row % S;
+  float v[NV][8];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int col = (lane + 32 * i) * 8;
+    if (col < H) {
+      float a[8], b[8];
+      load8(word + (size_t)id * H + col, a);
+      load8(pos + (size_t)s * H + col, b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { v[i][j] = a[j] + b[j]; sum += v[i][j]; }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
+    }
+  }
+  const float mu = warp_sum(sum) / H;
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int col = (lane + 32 * i) * 8;
+    if (col < H) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { float d = v[i][j] - mu; sq += d * d; }
+    }
+  }
+  const float rs = rsqrtf(warp_sum(sq) / H + eps);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int col = (lane + 32 * i) * 8;
+    if (col < H) {
+      float g[8], b[8], o[8];
+      load8(gamma + col, g);
+      load8(beta + col, b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float t = (v[i][j] - mu) * rs * g[j] + b[j];
+        if (p > 0.f) t = keep(seed, stream, (uint32_t)(row * H + col + j), p) ? t * inv_keep : 0.f;
+        o[j] = t;
+      }
+      store8(y + (size_t)row * H + col, o);
+    }
+  }
+  if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
+}
+
+// ------------------------------------------------------------------------------------ LN backward
+// EMBED = false: inputs dy, pre;   outputs d_pre, d_branch (if p > 0), dgamma, dbeta, dbias.
+// EMBED = true : inputs dy (dropout re-applied to it), ids/word/pos to rebuild the LN input; outputs
+//                dgamma, dbeta and gradients scattered into dword (atomic, pad id skipped) and dpos.
+//                The launch makes the total warp count a multiple of S so a warp sees one position.
+template <typename T, int NV, bool EMBED>
+__global__ void __launch_bounds__(128) ln_bwd_kernel(
+    const T* __restrict__ dy, const T* __restrict__ pre, const int* __restrict__ ids,
+    const T* __restrict__ word, const T* __restrict__ pos, const T* __restrict__ gamma,
+    const float* __restrict__ mean, const float* __restrict__ rstd,
+    T* __restrict__ d_pre, T* __restrict__ d_branch, T* __restrict__ dword, T* __restrict__ dpos,
+    float* __restrict__ acc, unsigned* __restrict__ counter, T* __restrict__ dgamma, T* __restrict__ dbeta,
+    T* __restrict__ dbias, int rows, int H, int S, int pad_id, float p, const int* __restrict__ seed_ptr,
+    uint32_t stream) {
+  extern __shared__ float sm[];  // [3][H]
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  const int warp = blockIdx.x * wpb + (threadIdx.x >> 5);
+  const int total_warps = gridDim.x * wpb;
+  const uint32_t seed = p > 0.f ? (uint32_t)(*seed_ptr) : 0u;
+  const float inv_keep = p > 0.f ? 1.f / (1.f - p) : 1.f;
+  for (int i = threadIdx.x; i < 3 * H; i += blockDim.x) sm[i] = 0.f;
+  __syncthreads();
+
+  float gam[NV][8], a_dg[NV][8], a_db[NV][8], a_bias[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int col = (lane + 32 * i) * 8;
+    if (col < H) load8(gamma + col, gam[i]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { a_dg[i][j] = 0.f; a_db[i][j] = 0.f; a_bias[i][j] = 0.f; }
+  }
+  for (int row = warp; row < rows; row += total_warps) {
+    const float mu = mean[row], rs = rstd[row];
+    float xh[NV][8], g[NV][8];
+    float s1 = 0.f, s2 = 0.f;
+    int id = 0;
+    if (EMBED) id = ids[row];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int col = (lane + 32 * i) * 8;
+      if (col < H) {
+        float d[8], x[8];
+        load8(dy + (size_t)row * H + col, d);
+        if (EMBED) {
+          float b[8];
+          load8(word + (size_t)id * H + col, x);
+          load8(pos + (size_t)(row % S) * H + col, b);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            x[j] += b[j];
+            if (p > 0.f) d[j] = keep(seed, stream, (uint32_t)(row * H + col + j), p) ? d[j] * inv_keep : 0.f;
+          }
+        } else {
+          load8(pre + (size_t)row * H + col, x);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] = (x[j] - mu) * rs;
+          g[i][j] = d[j] * gam[i][j];
+          s1 += g[i][j];
+          s2 += g[i][j] * xh[i][j];
+          a_dg[i][j] += d[j] * xh[i][j];
+          a_db[i][j] += d[j];
+        }
+      }
+    }
+    s1 = warp_sum(s1) / H;
+    s2 = warp_sum(s2) / H;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int col = (lane + 32 * i) * 8;
+      if (col < H) {
+        float dx[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dx[j] = (g[i][j] - s1 - xh[i][j] * s2) * rs;
+        if (EMBED) {
+          if (id != pad_id) atomic_add8(dword + (size_t)id * H + col, dx);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) a_bias[i][j] += dx[j];   // position-embedding gradient of this warp's position
+        } else {
+          store8(d_pre + (size_t)row * H + col, dx);
+          if (p > 0.f) {
+            float db[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              db[j] = keep(seed, stream, (uint32_t)(row * H + col + j), p) ? dx[j] * inv_keep : 0.f;
+              a_bias[i][j] += round_through<T>(db[j]);
+            }
+            store8(d_branch + (size_t)row * H + col, db);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) a_bias[i][j] += round_through<T>(dx[j]);
+          }
+        }
+      }
+    }
+  }
+  if (EMBED && warp < rows) {
+    const int s = warp % S;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int col = (lane + 32 * i) * 8;
+      if (col < H) atomic_add8(dpos + (size_t)s * H + col, a_bias[i]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int col = (lane + 32 * i) * 8;
+    if (col < H) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        atomicAdd(&sm[col + j], a_dg[i][j]);
+        atomicAdd(&sm[H + col + j], a_db[i][j]);
+        if (!EMBED) atomicAdd(&sm[2 * H + col + j], a_bias[i][j]);
+      }
+    }
+  }
+  __syncthreads();
+  const int nvec = EMBED ? 2 : 3;
+  for (int i = threadIdx.x; i < nvec * H; i += blockDim.x) atomicAdd(acc + i, sm[i]);
+  finalize_columns<T>(acc, counter, nvec, H, dgamma, dbeta, EMBED ? nullptr : dbias);
+}
+
+// ------------------------------------------------------------------------------------ GELU
+__device__ __forceinline__ float gelu_f(float z) { return 0.5f * z * (1.f + erff(z * 0.70710678118654752f)); }
+__device__ __forceinline__ float gelu_grad_f(float z) {
+  const float cdf = 0.5f * (1.f + erff(z * 0.70710678118654752f));
+  const float pdf = 0.39894228040143268f * __expf(-0.5f * z * z);
+  return cdf + z * pdf;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) bias_gelu_fwd_kernel(const T* __restrict__ x, const T* __restrict__ bias,
+                                                            T* __restrict__ out, size_t n_vec, int F) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t e = i * 8;
+    const int col = (int)(e % F);
+    float a[8], b[8];
+    load8(x + e, a);
+    load8(bias + col, b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = gelu_f(a[j] + b[j]);
+    store8(out + e, a);
+  }
+}
+
+// grid = (ceil(F/8/128), row_chunks); a thread owns 8 columns and walks the rows of its chunk
+template <typename T>
+__global__ void __launch_bounds__(128) bias_gelu_bwd_kernel(const T* __restrict__ da, const T* __restrict__ x,
+                                                            const T* __restrict__ bias, T* __restrict__ dx,
+                                                            float* __restrict__ acc, unsigned* __restrict__ counter,
+                                                            T* __restrict__ dbias, int rows, int F) {
+  const int col = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  float b[8], s[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s[j] = 0.f;
+  if (col < F) {
+    load8(bias + col, b);
+    for (int r = blockIdx.y; r < rows; r += gridDim.y) {
+      float a[8], g[8];
+      load8(x + (size_t)r * F + col, a);
+      load8(da + (size_t)r * F + col, g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        g[j] = round_through<T>(g[j] * gelu_grad_f(a[j] + b[j]));
+        s[j] += g[j];
+      }
+      store8(dx + (size_t)r * F + col, g);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) atomicAdd(acc + col + j, s[j]);
+  }
+  finalize_columns<T>(acc, counter, 1, F, dbias, nullptr, nullptr);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) colsum_kernel(const T* __restrict__ x, float* __restrict__ acc,
+                                                     unsigned* __restrict__ counter, T* __restrict__ out,
+                                                     int rows, int N) {
+  const int col = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (col < N) {
+    float s[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s[j] = 0.f;
+    for (int r = blockIdx.y; r < rows; r += gridDim.y) {
+      float a[8];
+      load8(x + (size_t)r * N + col, a);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s[j] += a[j];
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) atomicAdd(acc + col + j, s[j]);
+  }
+  finalize_columns<T>(acc, counter, 1, N, out, nullptr, nullptr);
+}
+
+// ------------------------------------------------------------------------------------ pooling
+// grid = b, block covers H/8 vectors
+template <typename T>
+__global__ void pool_fwd_kernel(const T* __restrict__ h, const int* __restrict__ mask, float* __restrict__ out,
+                                int S, int H, int cls) {
+  const int b = blockIdx.x;
+  for (int col = threadIdx.x * 8; col < H; col += blockDim.x * 8) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    if (cls) {
+      load8(h + (size_t)b * S * H + col, acc);
+    } else {
+      float cnt = 0.f;
+      for (int s = 0; s < S; ++s) {
+        if (mask[b * S + s] != 0) {
+          float a[8];
+          load8(h + ((size_t)b * S + s) * H + col, a);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += a[j];
+          cnt += 1.f;
+        }
+      }
+      const float inv = 1.f / fmaxf(cnt, 1e-9f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] *= inv;
+    }
+    store8(out + (size_t)b * H + col, acc);
+  }
+}
+
+// grid = b*S rows
+template <typename T>
+__global__ void pool_bwd_kernel(const float* __restrict__ de, const int* __restrict__ mask, T* __restrict__ dh,
+                                int S, int H, int cls) {
+  const int row = blockIdx.x;
+  const int b = row / S, s = row % S;
+  float w;
+  if (cls) {
+    w = (s == 0) ? 1.f : 0.f;
+  } else {
+    float cnt = 0.f;
+    for (int t = 0; t < S; ++t) cnt += mask[b * S + t] != 0 ? 1.f : 0.f;
+    w = mask[b * S + s] != 0 ? 1.f / fmaxf(cnt, 1e-9f) : 0.f;
+  }
+  for (int col = threadIdx.x * 8; col < H; col += blockDim.x * 8) {
+    float a[8];
+    load8(de + (size_t)b * H + col, a);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] *= w;
+    store8(dh + (size_t)row * H + col, a);
+  }
+}
+
+// ------------------------------------------------------------------------------------ dropout on [n] elements
+template <typename TI, typename TO>
+__global__ void dropout_kernel(const TI* __restrict__ x, TO* __restrict__ out, size_t n, float p,
+                               const int* __restrict__ seed_ptr, uint32_t stream) {
+  const uint32_t seed = p > 0.f ? (uint32_t)(*seed_ptr) : 0u;
+  const float inv_keep = p > 0.f ? 1.f / (1.f - p) : 1.f;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float v = to_f(x[i]);
+    if (p > 0.f) v = keep(seed, stream, (uint32_t)i, p) ? v * inv_keep : 0.f;
+    out[i] = from_f<TO>(v);
+  }
+}
+
+}  // namespace rb
+
+using namespace rb;
+
+#define DISPATCH_T(dtype, ...)                                                     \
+  switch (dtype) {                                                                 \
+    case RB_F32: { using T = float; __VA_ARGS__; break; }                          \
+    case RB_BF16: { using T = __nv_bfloat16; __VA_ARGS__; break; }                 \
+    case RB_F16: { using T = __half; __VA_ARGS__; break; }                         \
+    default: return -1;                                                            \
+  }
+
+#define DISPATCH_NV(H, ...)                                                        \
+  {                                                                                \
+    const int nv_ = ((H) + 255) / 256;                                             \
+    if (nv_ <= 1) { constexpr int NV = 1; __VA_ARGS__; }                           \
+    else if (nv_ <= 2) { constexpr int NV = 2; __VA_ARGS__; }                      \
+    else if (nv_ <= 3) { constexpr int NV = 3; __VA_ARGS__; }                      \
+    else if (nv_ <= 4) { constexpr int NV = 4; __VA_ARGS__; }                      \
+    else if (nv_ <= 8) { constexpr int NV = 8; __VA_ARGS__; }                      \
+    else return -2;                                                                \
+  }
+
+RB_API int rb_bias_dropout_add_ln_fwd(int dtype, const void* x, const void* bias, const void* resid, const void* gamma,
+                                      const void* beta, void* y, void* pre, float* mean, float* rstd, int rows, int H,
+                                      float eps, float p, const int* seed, unsigned stream_id, cudaStream_t st) {
+  if (H % 8) return -3;
+  const int blocks = (rows + 3) / 4;
+  DISPATCH_T(dtype, DISPATCH_NV(H, (bias_dropout_add_ln_fwd_kernel<T, NV><<<blocks, 128, 0, st>>>(
+      (const T*)x, (const T*)bias, (const T*)resid, (const T*)gamma, (const T*)beta, (T*)y, (T*)pre, mean, rstd,
+      rows, H, eps, p, seed, stream_id))));
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+RB_API int rb_embed_ln_fwd(int dtype, const int* ids, const void* word, const void* pos, const void* gamma,
+                           const void* beta, void* y, float* mean, float* rstd, int rows, int H, int S, float eps,
+                           float p, const int* seed, unsigned stream_id, cudaStream_t st) {
+  if (H % 8) return -3;
+  const int blocks = (rows + 3) / 4;
+  DISPATCH_T(dtype, DISPATCH_NV(H, (embed_ln_fwd_kernel<T, NV><<<blocks, 128, 0, st>>>(
+      ids, (const T*)word, (const T*)pos, (const T*)gamma, (const T*)beta, (T*)y, mean, rstd, rows, H, S, eps, p,
+      seed, stream_id))));
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+static int ln_bwd_blocks(int rows, int S, bool embed) {
+  int blocks = (rows + 3) / 4;
+  if (blocks > 592) blocks = 592;
+  if (embed) {  // total warps (4 per block) must be a multiple of S: round blocks to a multiple of S
+    blocks = (blocks / S) * S;
+    if (blocks == 0) blocks = S;
+  }
+  return blocks;
+}
+
+RB_API int rb_bias_dropout_add_ln_bwd(int dtype, const void* dy, const void* pre, const void* gamma, const float* mean,
+                                      const float* rstd, void* d_pre, void* d_branch, float* acc, unsigned* counter,
+                                      void* dgamma, void* dbeta, void* dbias, int rows, int H, float p, const int* seed,
+                                      unsigned stream_id, cudaStream_t st) {
+  if (H % 8) return -3;
+  const int blocks = ln_bwd_blocks(rows, 1, false);
+  const size_t smem = 3 * (size_t)H * sizeof(float);
+  DISPATCH_T(dtype, DISPATCH_NV(H, (ln_bwd_kernel<T, NV, false><<<blocks, 128, smem, st>>>(
+      (const T*)dy, (const T*)pre, nullptr, nullptr, nullptr, (const T*)gamma, mean, rstd, (T*)d_pre, (T*)d_branch,
+      nullptr, nullptr, acc, counter, (T*)dgamma, (T*)dbeta, (T*)dbias, rows, H, 1, 0, p, seed, stream_id))));
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+RB_API int rb_embed_ln_bwd(int dtype, const void* dy, const int* ids, const void* word, const void* pos,
+                           const void* gamma, const float* mean, const float* rstd, void* dword, void* dpos,
+                           float* acc, unsigned* counter, void* dgamma, void* dbeta, int rows, int H, int S, int pad_id,
+                           float p, const int* seed, unsigned stream_id, cudaStream_t st) {
+  if (H % 8) return -3;
+  const int blocks = ln_bwd_blocks(rows, S, true);
+  const size_t smem = 3 * (size_t)H * sizeof(float);
+  DISPATCH_T(dtype, DISPATCH_NV(H, (ln_bwd_kernel<T, NV, true><<<blocks, 128, smem, st>>>(
+      (const T*)dy, nullptr, ids, (const T*)word, (const T*)pos, (const T*)gamma, mean, rstd, nullptr, nullptr,
+      (T*)dword, (T*)dpos, acc, counter, (T*)dgamma, (T*)dbeta, nullptr, rows, H, S, pad_id, p, seed, stream_id))));
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+RB_API int rb_bias_gelu_fwd(int dtype, const void* x, const void* bias, void* out, int rows, int F, cudaStream_t st) {
+  if (F % 8) return -3;
+  const size_t n_vec = (size_t)rows * F / 8;
+  int blocks = (int)((n_vec + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  DISPATCH_T(dtype, (bias_gelu_fwd_kernel<T><<<blocks, 256, 0, st>>>((const T*)x, (const T*)bias, (T*)out, n_vec, F)));
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+RB_API int rb_bias_gelu_bwd(int dtype, const void* da, const void* x, const void* bias, void* dx, float* acc,
+                            unsigned* counter, void* dbias, int rows, int F, cudaStream_t st) {
+  if (F % 8) return -3;
+  dim3 grid((F / 8 + 127) / 128, rows < 192 ? rows : 192);
+  DISPATCH_T(dtype, (bias_gelu_bwd_kernel<T><<<grid, 128, 0, st>>>((const T*)da, (const T*)x, (const T*)bias, (T*)dx,
+                                                                    acc, counter, (T*)dbias, rows, F)));
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+RB_API int rb_colsum(int dtype, const void* x, float* acc, unsigned* counter, void* out, int rows, int N,
+                     cudaStream_t st) {
+  if (N % 8) return -3;
+  dim3 grid((N / 8 + 127) / 128, rows < 192 ? rows : 192);
+  DISPATCH_T(dtype, (colsum_kernel<T><<<grid, 128, 0, st>>>((const T*)x, acc, counter, (T*)out, rows, N)));
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+RB_API int rb_pool_fwd(int dtype, const void* h, const int* mask, float* out, int b, int S, int H, int cls,
+                       cudaStream_t st) {
+  if (H % 8) return -3;
+  DISPATCH_T(dtype, (pool_fwd_kernel<T><<<b, 128, 0, st>>>((const T*)h, mask, out, S, H, cls)));
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+RB_API int rb_pool_bwd(int dtype, const float* de, const int* mask, void* dh, int b, int S, int H, int cls,
+                       cudaStream_t st) {
+  if (H % 8) return -3;
+  DISPATCH_T(dtype, (pool_bwd_kernel<T><<<b * S, 128, 0, st>>>(de, mask, (T*)dh, S, H, cls)));
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+// fp32 in → out dtype (fp32 / fp16 / bf16): classifier-input dropout + cast
+RB_API int rb_dropout_cast_fwd(int out_dtype, const float* x, void* out, long long n, float p, const int* seed,
+                               unsigned stream_id, cudaStream_t st) {
+  int blocks = (int)((n + 255) / 256);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  DISPATCH_T(out_dtype, (dropout_kernel<float, T><<<blocks, 256, 0, st>>>(x, (T*)out, (size_t)n, p, seed, stream_id)));
+  RB_LAUNCH_CHECK();
+  return 0;
+}

@@ -1,0 +1,379 @@
+// Extreme-classifier (XFC) step kernels for sm_100a: three tcgen05/TMEM GEMMs with fused epilogues.
+//
+//   logits_grad  Gt[l, b]  = sigmoid(sum_d W[l,d] X[b,d]) - Y[l,b]     (A = W K-major, B = X K-major)
+//                 epilogue: sigmoid in registers, fp16 store, positives patched from a label-sorted COO
+//                 list by binary search, optional sparse-BCE loss partials.  Logits never reach HBM.
+//   dx           dX[b, d] += scale * sum_l Gt[l,b] W[l,d]              (A = Gt MN-major, B = W MN-major)
+//                 split over label blocks, fp32 accumulation in TMEM, vector red.add into dX.
+//   dw_sgd       dW[l, d]  = sum_b Gt[l,b] X[b,d]                      (A = Gt K-major, B = X MN-major)
+//                 epilogue: g = dW + wd W; M = mo M + g; W -= lr M on the fp16 W / M tiles (dW never
+//                 stored).
+//
+// They replace, in the reference: torch.matmul/addmm through cuBLAS (dl_base.py:572, 606-608, 625-633),
+// the CUTLASS Volta sigmoid-GEMM / dW GEMM of xfc_gemm_kernel.cu:59-150, torch.sigmoid + index_put_
+// (dl_base.py:593-594), the sampled loss reductions (dl_base.py:579-583) and apex FusedSGD
+// (dl_base.py:343).
+//
+// Structure of every kernel: 192 threads; warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2..5 = epilogue (one TMEM lane quarter each).  4-stage smem ring, 128x{<=256}x64 tiles,
+// UMMA 128xNx16.  All waits are bounded (see tc.cuh).
+#include "tc.cuh"
+
+namespace rb {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kStages = 4;
+constexpr int kABytes = kBM * kBK * 2;          // 16 KB
+constexpr int kBBytesMax = 256 * kBK * 2;       // 32 KB
+constexpr int kStageBytes = kABytes + kBBytesMax;
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 256;
+
+enum Mode : int { MODE_LOGITS = 0, MODE_DX = 1, MODE_DW = 2, MODE_RAW = 3 };
+
+struct GemmParams {
+  int M;             // valid output rows   (labels for LOGITS/DW/RAW, batch rows for DX)
+  int N;             // valid output cols   (batch rows for LOGITS/RAW, D for DX/DW)
+  int BN;            // N tile (multiple of 16, <= 256)
+  int kb_total;      // number of 64-wide k blocks
+  int kb_per_split;  // k blocks handled by one blockIdx.z
+  int* status;
+  // LOGITS / RAW
+  __half* Gt; int ldG;
+  const int* pos_rows; const int* pos_labels; const int* nnz_ptr; int label0;
+  float* loss_acc;
+  // DX
+  float* dX; int ldX; const float* hp;
+  // DW
+  __half* W; __half* Mom; int ldW; float mo; float wd;
+  float* Zout;       // RAW: fp32 logits [M, ldG] (debug / top-k path)
+};
+
+__device__ __forceinline__ int lower_bound_i32(const int* a, int n, int key) {
+  int lo = 0, hi = n;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (a[mid] < key) lo = mid + 1; else hi = mid;
+  }
+  return lo;
+}
+
+__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+xfc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  constexpr bool A_MN = (MODE == MODE_DX);
+  constexpr bool B_MN = (MODE == MODE_DX || MODE == MODE_DW);
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tmem_full_bar = empty_bar + kStages;
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * kBM;
+  const int n0 = blockIdx.y * p.BN;
+  const int kb0 = blockIdx.z * p.kb_per_split;
+  const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+  const bool has_work = kb1 > kb0;
+  const uint32_t b_bytes = (uint32_t)p.BN * kBK * 2;
+
+  if (threadIdx.x == 0) {
+    tc::prefetch_tmap(&tmA);
+    tc::prefetch_tmap(&tmB);
+    for (int s = 0; s < kStages; ++s) { tc::mbar_init(full_bar + s, 1); tc::mbar_init(empty_bar + s, 1); }
+    tc::mbar_init(tmem_full_bar, 1);
+    tc::fence_barrier_init();
+  }
+  if (warp == 1) tc::tmem_alloc(tmem_ptr_smem, kTmemCols);
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+  bool aborted = false;
+
+  if (warp == 0 && lane == 0 && has_work) {
+    // ---------------- TMA producer
+    for (int kb = kb0, it = 0; kb < kb1; ++kb, ++it) {
+      const int s = it % kStages;
+      const uint32_t ph = (it / kStages) & 1;
+      if (!tc::mbar_wait(empty_bar + s, ph ^ 1, aborted, p.status, tc::SITE_EMPTY, kb)) break;
+      uint8_t* sA = smem + s * kStageBytes;
+      uint8_t* sB = sA + kABytes;
+      tc::mbar_expect_tx(full_bar + s, kABytes + b_bytes);
+      if (A_MN) {
+        tc::tma_load_2d(sA, &tmA, full_bar + s, m0, kb * kBK);
+        tc::tma_load_2d(sA + 8192, &tmA, full_bar + s, m0 + 64, kb * kBK);
+      } else {
+        tc::tma_load_2d(sA, &tmA, full_bar + s, kb * kBK, m0);
+      }
+      if (B_MN) {
+        for (int i = 0; i < p.BN / 64; ++i) tc::tma_load_2d(sB + i * 8192, &tmB, full_bar + s, n0 + 64 * i, kb * kBK);
+      } else {
+        tc::tma_load_2d(sB, &tmB, full_bar + s, kb * kBK, n0);
+      }
+    }
+  } else if (warp == 1 && lane == 0 && has_work) {
+    // ---------------- MMA issuer
+    const uint32_t idesc = tc::make_idesc(0, A_MN ? 1 : 0, B_MN ? 1 : 0, kBM, p.BN);
+    for (int kb = kb0, it = 0; kb < kb1; ++kb, ++it) {
+      const int s = it % kStages;
+      const uint32_t ph = (it / kStages) & 1;
+      if (!tc::mbar_wait(full_bar + s, ph, aborted, p.status, tc::SITE_FULL, kb)) break;
+      tc::tc_fence_after();
+      const uint32_t sA = tc::smem_u32(smem + s * kStageBytes);
+      const uint32_t sB = sA + kABytes;
+#pragma unroll
+      for (int k = 0; k < kBK / 16; ++k) {
+        const uint64_t ad = A_MN ? tc::make_smem_desc(sA + k * 2048, 8192, 1024) : tc::make_smem_desc(sA + k * 32, 16, 1024);
+        const uint64_t bd = B_MN ? tc::make_smem_desc(sB + k * 2048, 8192, 1024) : tc::make_smem_desc(sB + k * 32, 16, 1024);
+        tc::umma_f16(tmem_base, ad, bd, idesc, (it > 0 || k > 0) ? 1u : 0u);
+      }
+      tc::umma_commit(empty_bar + s);   // frees the smem stage once these MMAs have read it
+    }
+    if (!aborted) tc::umma_commit(tmem_full_bar);
+  } else if (warp >= 2 && has_work) {
+    // ---------------- epilogue: TMEM -> registers -> fused math -> global
+    const int quarter = warp & 3;                 // TMEM lane quarter this warp may read
+    const int r = quarter * 32 + lane;            // row of the 128-row tile
+    const int row = m0 + r;
+    const bool ok = tc::mbar_wait(tmem_full_bar, 0, aborted, p.status, tc::SITE_TMEM_FULL, 0);
+    tc::tc_fence_after();
+    if (ok) {
+      const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      float loss = 0.f;
+      float lr = 0.f, scale = 1.f;
+      if (MODE == MODE_DW) lr = p.hp[HP_LR_XFC];
+      if (MODE == MODE_DX) scale = p.hp[HP_SCALE];
+      for (int c0 = 0; c0 < p.BN; c0 += 32) {
+        float v[32];
+        tc::tmem_ld32(tbase + c0, v);
+        const int col0 = n0 + c0;
+        if (MODE == MODE_LOGITS) {
+          if (row < p.M) {
+            if (p.loss_acc != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) loss += fmaxf(v[j], 0.f) + log1pf(__expf(-fabsf(v[j])));
+            }
+#pragma unroll
+            for (int j8 = 0; j8 < 4; ++j8) {
+              const int c = col0 + 8 * j8;
+              if (c < p.ldG) {
+                uint4 pk;
+                __half2* h2 = reinterpret_cast<__half2*>(&pk);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float a = (c + 2 * j < p.N) ? 1.f / (1.f + __expf(-v[8 * j8 + 2 * j])) : 0.f;
+                  const float b = (c + 2 * j + 1 < p.N) ? 1.f / (1.f + __expf(-v[8 * j8 + 2 * j + 1])) : 0.f;
+                  h2[j] = __floats2half2_rn(a, b);
+                }
+                *reinterpret_cast<uint4*>(p.Gt + (size_t)row * p.ldG + c) = pk;
+              }
+            }
+          }
+        } else if (MODE == MODE_RAW) {
+          if (row < p.M) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) p.Zout[(size_t)row * p.ldG + col0 + j] = v[j];
+          }
+        } else if (MODE == MODE_DX) {
+          if (row < p.M) {
+#pragma unroll
+            for (int j4 = 0; j4 < 8; ++j4) {
+              const int c = col0 + 4 * j4;
+              if (c < p.N)
+                red_add_v4(p.dX + (size_t)row * p.ldX + c, v[4 * j4] * scale, v[4 * j4 + 1] * scale,
+                           v[4 * j4 + 2] * scale, v[4 * j4 + 3] * scale);
+            }
+          }
+        } else {  // MODE_DW: fused SGD with momentum and L2 weight decay on the fp16 tiles
+          if (row < p.M) {
+#pragma unroll
+            for (int j8 = 0; j8 < 4; ++j8) {
+              const int c = col0 + 8 * j8;
+              if (c < p.N) {
+                __half* wp = p.W + (size_t)row * p.ldW + c;
+                __half* mp = p.Mom + (size_t)row * p.ldW + c;
+                uint4 wr = *reinterpret_cast<const uint4*>(wp);
+                uint4 mr = *reinterpret_cast<const uint4*>(mp);
+                __half2* w2 = reinterpret_cast<__half2*>(&wr);
+                __half2* m2 = reinterpret_cast<__half2*>(&mr);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  float2 w = __half22float2(w2[j]);
+                  float2 m = __half22float2(m2[j]);
+                  const float g0 = v[8 * j8 + 2 * j] + p.wd * w.x;
+                  const float g1 = v[8 * j8 + 2 * j + 1] + p.wd * w.y;
+                  m.x = p.mo * m.x + g0;
+                  m.y = p.mo * m.y + g1;
+                  m2[j] = __floats2half2_rn(m.x, m.y);
+                  const float2 mr2 = __half22float2(m2[j]);   // the update uses the stored (rounded) momentum
+                  w2[j] = __floats2half2_rn(w.x - lr * mr2.x, w.y - lr * mr2.y);
+                }
+                *reinterpret_cast<uint4*>(wp) = wr;
+                *reinterpret_cast<uint4*>(mp) = mr;
+              }
+            }
+          }
+        }
+      }
+      if (MODE == MODE_LOGITS && p.loss_acc != nullptr) {
+        loss = warp_sum(loss);
+        if (lane == 0) atomicAdd(p.loss_acc, loss);
+      }
+    }
+    if (MODE == MODE_LOGITS) {
+      // all four epilogue warps have stored their rows: subtract 1 at this tile's positives
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (ok && p.pos_labels != nullptr) {
+        const int nnz = *p.nnz_ptr;
+        const int lab_lo = p.label0 + m0;
+        const int lab_hi = p.label0 + min(m0 + kBM, p.M);
+        const int e0 = lower_bound_i32(p.pos_labels, nnz, lab_lo);
+        const int e1 = lower_bound_i32(p.pos_labels, nnz, lab_hi);
+        for (int e = e0 + (int)threadIdx.x - 64; e < e1; e += 128) {
+          const int b = p.pos_rows[e];
+          if (b >= n0 && b < min(n0 + p.BN, p.N)) {
+            __half* g = p.Gt + (size_t)(p.pos_labels[e] - p.label0) * p.ldG + b;
+            *g = __float2half_rn(__half2float(*g) - 1.f);
+          }
+        }
+      }
+    }
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc::tc_fence_after();
+    tc::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// sum over positives of z = W[label] . X[row]  (only on loss-sampling steps): one warp per positive
+__global__ void xfc_pos_logit_sum_kernel(const __half* __restrict__ W, const __half* __restrict__ X, int D,
+                                         const int* __restrict__ pos_rows, const int* __restrict__ pos_labels,
+                                         const int* __restrict__ nnz_ptr, float* __restrict__ loss_acc) {
+  const int nnz = *nnz_ptr;
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  float total = 0.f;
+  for (int e = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; e < nnz; e += warps) {
+    const __half* w = W + (size_t)pos_labels[e] * D;
+    const __half* x = X + (size_t)pos_rows[e] * D;
+    float a = 0.f;
+    for (int d = lane * 2; d < D; d += 64) {
+      const float2 wf = __half22float2(*reinterpret_cast<const __half2*>(w + d));
+      const float2 xf = __half22float2(*reinterpret_cast<const __half2*>(x + d));
+      a += wf.x * xf.x + wf.y * xf.y;
+    }
+    total += warp_sum(a);
+  }
+  if (lane == 0 && total != 0.f) atomicAdd(loss_acc, -total);
+}
+
+}  // namespace rb
+
+using namespace rb;
+
+template <int MODE>
+static int launch_gemm(const CUtensorMap& a, const CUtensorMap& b, const GemmParams& p, dim3 grid, cudaStream_t st) {
+  static bool attr_set = false;
+  auto k = xfc_gemm_kernel<MODE>;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) return -5;
+    attr_set = true;
+  }
+  k<<<grid, kThreads, kSmemBytes, st>>>(a, b, p);
+  return 0;
+}
+
+static int round_up(int x, int m) { return (x + m - 1) / m * m; }
+
+// Gt[Lc, ldG] = sigmoid(W X^T) - Y for the label chunk W[Lc, D]; labels of the chunk are
+// label0 .. label0+Lc-1 in the numbering of pos_labels.  raw_out != null writes fp32 logits instead
+// (no sigmoid, no positives) into raw_out[Lc, ldG].
+RB_API int rb_xfc_logits_grad(const void* W, int Lc, int D, const void* X, int B, void* Gt, int ldG,
+                              const int* pos_rows, const int* pos_labels, const int* nnz_ptr, int label0,
+                              float* loss_acc, float* raw_out, int* status, cudaStream_t st) {
+  if (D % 8 || ldG % 8 || ldG < B || Lc < 1 || B < 1) return -3;
+  const int BN = B >= 256 ? 256 : round_up(B, 16);
+  CUtensorMap ta, tb;
+  int rc = tc::make_tmap_2d(&ta, W, Lc, D, D, 64, kBM, false);
+  if (rc) return rc;
+  rc = tc::make_tmap_2d(&tb, X, B, D, D, 64, BN, false);
+  if (rc) return rc;
+  GemmParams p{};
+  p.M = Lc; p.N = B; p.BN = BN; p.kb_total = (D + kBK - 1) / kBK; p.kb_per_split = p.kb_total; p.status = status;
+  p.Gt = (__half*)Gt; p.ldG = ldG; p.pos_rows = pos_rows; p.pos_labels = pos_labels; p.nnz_ptr = nnz_ptr;
+  p.label0 = label0; p.loss_acc = loss_acc; p.Zout = raw_out;
+  dim3 grid((Lc + kBM - 1) / kBM, (B + BN - 1) / BN, 1);
+  rc = raw_out ? launch_gemm<MODE_RAW>(ta, tb, p, grid, st) : launch_gemm<MODE_LOGITS>(ta, tb, p, grid, st);
+  if (rc) return rc;
+  RB_LAUNCH_CHECK();
+  if (loss_acc != nullptr && raw_out == nullptr && pos_labels != nullptr) {
+    // the positives' logits are subtracted once per step by the caller (rb_xfc_pos_logit_sum)
+  }
+  return 0;
+}
+
+RB_API int rb_xfc_pos_logit_sum(const void* W, const void* X, int D, const int* pos_rows, const int* pos_labels,
+                                const int* nnz_ptr, float* loss_acc, cudaStream_t st) {
+  if (D % 2) return -3;
+  xfc_pos_logit_sum_kernel<<<64, 128, 0, st>>>((const __half*)W, (const __half*)X, D, pos_rows, pos_labels, nnz_ptr,
+                                               loss_acc);
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+// dX[B, D] += hp[SCALE] * Gt^T W over the chunk (dX must have been zeroed before the first chunk)
+RB_API int rb_xfc_dx(const void* Gt, int ldG, const void* W, int Lc, int D, int B, float* dX, const float* hp,
+                     int splits, int* status, cudaStream_t st) {
+  if (D % 8 || ldG % 8 || Lc < 1) return -3;
+  const int BN = D >= 256 ? 256 : round_up(D, 64);
+  CUtensorMap ta, tb;
+  int rc = tc::make_tmap_2d(&ta, Gt, Lc, ldG, ldG, 64, 64, false);
+  if (rc) return rc;
+  rc = tc::make_tmap_2d(&tb, W, Lc, D, D, 64, 64, false);
+  if (rc) return rc;
+  GemmParams p{};
+  p.M = B; p.N = D; p.BN = BN; p.kb_total = (Lc + kBK - 1) / kBK; p.status = status;
+  if (splits < 1) splits = 1;
+  if (splits > p.kb_total) splits = p.kb_total;
+  p.kb_per_split = (p.kb_total + splits - 1) / splits;
+  splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
+  p.dX = dX; p.ldX = D; p.hp = hp;
+  dim3 grid((B + kBM - 1) / kBM, (D + BN - 1) / BN, splits);
+  rc = launch_gemm<MODE_DX>(ta, tb, p, grid, st);
+  if (rc) return rc;
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+// W, Mom [Lc, D] updated in place from dW = Gt X (never stored); lr read from hp[LR_XFC]
+RB_API int rb_xfc_dw_sgd(const void* Gt, int ldG, const void* X, int B, void* W, void* Mom, int Lc, int D,
+                         const float* hp, float mo, float wd, int* status, cudaStream_t st) {
+  if (D % 8 || ldG % 8 || Lc < 1) return -3;
+  const int BN = D >= 256 ? 256 : round_up(D, 64);
+  CUtensorMap ta, tb;
+  int rc = tc::make_tmap_2d(&ta, Gt, Lc, ldG, ldG, 64, kBM, false);
+  if (rc) return rc;
+  rc = tc::make_tmap_2d(&tb, X, B, D, D, 64, 64, false);
+  if (rc) return rc;
+  GemmParams p{};
+  p.M = Lc; p.N = D; p.BN = BN; p.kb_total = (B + kBK - 1) / kBK; p.kb_per_split = p.kb_total; p.status = status;
+  p.W = (__half*)W; p.Mom = (__half*)Mom; p.ldW = D; p.hp = hp; p.mo = mo; p.wd = wd;
+  dim3 grid((Lc + kBM - 1) / kBM, (D + BN - 1) / BN, 1);
+  rc = launch_gemm<MODE_DW>(ta, tb, p, grid, st);
+  if (rc) return rc;
+  RB_LAUNCH_CHECK();
+  return 0;
+}

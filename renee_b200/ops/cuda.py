@@ -1,0 +1,281 @@
+"""ctypes bindings of the in-tree sm_100a kernel library (``_kernels.so``).
+
+Loading fails loudly: a CUDA tensor reaching :mod:`renee_b200.ops` without a current library is an
+error, not a fallback.  Every wrapper launches on PyTorch's current stream and performs no
+allocation and no host synchronisation, so whole training steps can be captured in a CUDA graph.
+``launch_count()`` reports how many kernels of this library were launched (``bench.py`` uses it).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+from . import build as _build
+
+_LIB = None
+_LAUNCHES = 0
+_c = ctypes
+_VP, _I, _F, _LL, _U = _c.c_void_p, _c.c_int, _c.c_float, _c.c_longlong, _c.c_uint
+
+DT = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        if not _build.is_current():
+            if os.environ.get("RENEE_B200_NO_BUILD") == "1" or not _has_nvcc():
+                if not os.path.exists(_build.LIB):
+                    raise KernelError(f"{_build.LIB} is missing and cannot be built here; run "
+                                      "`python -m renee_b200.ops.build`")
+            else:
+                _build.build()
+        _LIB = ctypes.CDLL(_build.LIB)
+    return _LIB
+
+
+def _has_nvcc() -> bool:
+    try:
+        _build.nvcc_path()
+        return True
+    except RuntimeError:
+        return False
+
+
+def launch_count() -> int:
+    return _LAUNCHES
+
+
+def _stream():
+    return _VP(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t):
+    return _VP(0) if t is None else _VP(t.data_ptr())
+
+
+def _call(name, *args, launches=1):
+    global _LAUNCHES
+    rc = getattr(lib(), name)(*args)
+    if rc != 0:
+        raise KernelError(f"{name} failed with code {rc}")
+    _LAUNCHES += launches
+
+
+# ----------------------------------------------------------------------------- workspaces
+class _Workspace:
+    """Small per-device scratch: fp32 column accumulators (zero between calls by contract of the
+    kernels), block counters, and the status words the bounded waits write."""
+
+    def __init__(self, device):
+        self.colacc = torch.zeros(4 * 8192, dtype=torch.float32, device=device)
+        self.counters = torch.zeros(16, dtype=torch.int32, device=device)
+        self.status = torch.zeros(8, dtype=torch.int32, device=device)
+
+
+_WS: dict = {}
+
+
+def workspace(device) -> _Workspace:
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    if key not in _WS:
+        _WS[key] = _Workspace(torch.device("cuda", key))
+    return _WS[key]
+
+
+def check_status(device=None) -> None:
+    """Raise if any bounded device-side wait has timed out since the last check (synchronises)."""
+    ws = workspace(device if device is not None else torch.cuda.current_device())
+    st = ws.status.cpu().tolist()
+    if st[0] != 0:
+        ws.status.zero_()
+        raise KernelError(f"device-side wait timed out: code={st[0]} block={st[1]} site={st[2]} detail={st[3]}")
+
+
+# ----------------------------------------------------------------------------- encoder ops
+def embed_ln_fwd(ids, word, pos, gamma, beta, eps, S, p, rng, stream, out, mean, rstd):
+    T, H = out.shape
+    _call("rb_embed_ln_fwd", _I(DT[out.dtype]), _p(ids), _p(word), _p(pos), _p(gamma), _p(beta), _p(out), _p(mean),
+          _p(rstd), _I(T), _I(H), _I(S), _F(eps), _F(p), _p(rng.dev), _U(stream), _stream())
+
+
+def embed_ln_bwd(dy, ids, word, pos, gamma, mean, rstd, S, p, rng, stream, pad_id, dword, dpos, dgamma, dbeta):
+    T, H = dy.shape
+    ws = workspace(dy.device)
+    dword.zero_()
+    dpos.zero_()
+    _call("rb_embed_ln_bwd", _I(DT[dy.dtype]), _p(dy), _p(ids), _p(word), _p(pos), _p(gamma), _p(mean), _p(rstd),
+          _p(dword), _p(dpos), _p(ws.colacc), _p(ws.counters), _p(dgamma), _p(dbeta), _I(T), _I(H), _I(S), _I(pad_id),
+          _F(p), _p(rng.dev), _U(stream), _stream())
+
+
+def attention_fwd(qkv, bqkv, mask, nh, p, rng, stream, ctx_out, ws):
+    b, S = mask.shape
+    H = ctx_out.shape[1]
+    _call("rb_attention_fwd", _I(DT[qkv.dtype]), _p(qkv), _p(bqkv), _p(mask), _p(ctx_out), _p(ws["probs"]), _I(b), _I(S),
+          _I(H), _I(nh), _F(p), _p(rng.dev), _U(stream), _stream())
+
+
+def attention_bwd(dctx, qkv, bqkv, mask, nh, p, rng, stream, ws, dqkv_out, dbqkv_out):
+    b, S = mask.shape
+    H = dctx.shape[1]
+    _call("rb_attention_bwd", _I(DT[qkv.dtype]), _p(dctx), _p(qkv), _p(bqkv), _p(ws["probs"]), _p(dqkv_out), _I(b),
+          _I(S), _I(H), _I(nh), _F(p), _p(rng.dev), _U(stream), _stream())
+    colsum(dqkv_out, dbqkv_out)
+
+
+def bias_dropout_add_ln_fwd(x, bias, resid, gamma, beta, eps, p, rng, stream, y_out, pre_out, mean, rstd):
+    T, H = x.shape
+    _call("rb_bias_dropout_add_ln_fwd", _I(DT[x.dtype]), _p(x), _p(bias), _p(resid), _p(gamma), _p(beta), _p(y_out),
+          _p(pre_out), _p(mean), _p(rstd), _I(T), _I(H), _F(eps), _F(p), _p(rng.dev), _U(stream), _stream())
+
+
+def bias_dropout_add_ln_bwd(dy, pre, gamma, mean, rstd, p, rng, stream, dgamma, dbeta, dbias, dpre_out, dbranch_out):
+    T, H = dy.shape
+    ws = workspace(dy.device)
+    _call("rb_bias_dropout_add_ln_bwd", _I(DT[dy.dtype]), _p(dy), _p(pre), _p(gamma), _p(mean), _p(rstd), _p(dpre_out),
+          _p(dbranch_out if p > 0 else None), _p(ws.colacc), _p(ws.counters), _p(dgamma), _p(dbeta), _p(dbias),
+          _I(T), _I(H), _F(p), _p(rng.dev), _U(stream), _stream())
+    return (dpre_out, dbranch_out) if p > 0 else (dpre_out, dpre_out)
+
+
+def bias_gelu_fwd(x, bias, out):
+    T, Fd = x.shape
+    _call("rb_bias_gelu_fwd", _I(DT[x.dtype]), _p(x), _p(bias), _p(out), _I(T), _I(Fd), _stream())
+
+
+def bias_gelu_bwd(da, x, bias, dbias, dx_out):
+    T, Fd = x.shape
+    ws = workspace(x.device)
+    _call("rb_bias_gelu_bwd", _I(DT[x.dtype]), _p(da), _p(x), _p(bias), _p(dx_out), _p(ws.colacc), _p(ws.counters[1:]),
+          _p(dbias), _I(T), _I(Fd), _stream())
+
+
+def colsum(x, out):
+    T, N = x.shape
+    ws = workspace(x.device)
+    _call("rb_colsum", _I(DT[x.dtype]), _p(x), _p(ws.colacc), _p(ws.counters[2:]), _p(out), _I(T), _I(N), _stream())
+    return out
+
+
+def pool_fwd(h, mask, mode, out):
+    b, S, H = h.shape
+    _call("rb_pool_fwd", _I(DT[h.dtype]), _p(h), _p(mask), _p(out), _I(b), _I(S), _I(H), _I(1 if mode == "cls" else 0),
+          _stream())
+
+
+def pool_bwd(de, mask, mode, S, dh_out):
+    b, H = de.shape
+    _call("rb_pool_bwd", _I(DT[dh_out.dtype]), _p(de), _p(mask), _p(dh_out), _I(b), _I(S), _I(H),
+          _I(1 if mode == "cls" else 0), _stream())
+
+
+def dropout_cast_fwd(e, p, rng, stream, out):
+    _call("rb_dropout_cast_fwd", _I(DT[out.dtype]), _p(e), _p(out), _LL(e.numel()), _F(p), _p(rng.dev), _U(stream),
+          _stream())
+
+
+def dropout_bwd(dx, p, rng, stream, out):
+    _call("rb_dropout_cast_fwd", _I(DT[out.dtype]), _p(dx), _p(out), _LL(dx.numel()), _F(p), _p(rng.dev), _U(stream),
+          _stream())
+
+
+# ----------------------------------------------------------------------------- optimizer
+def grad_check(g, hp):
+    _call("rb_grad_check", _I(DT[g.dtype]), _p(g), _LL(g.numel()), _p(hp.buf), _stream())
+
+
+def adamw_step(p32, m, v, g, p16, hp, beta1, beta2, eps, wd, n_decay, grad_mult: float = 1.0):
+    _call("rb_adamw", _I(DT[g.dtype]), _p(p32), _p(m), _p(v), _p(g), _p(None if p16 is p32 else p16), _LL(p32.numel()),
+          _LL(n_decay), _p(hp.buf), _F(beta1), _F(beta2), _F(eps), _F(wd), _F(grad_mult), _stream())
+
+
+def scaler_update(buf, enabled, growth, backoff, interval):
+    _call("rb_scaler_update", _p(buf), _I(1 if enabled else 0), _F(growth), _F(backoff), _I(interval), _stream())
+
+
+# ----------------------------------------------------------------------------- classifier step
+def _ld_g(B: int) -> int:
+    return (B + 7) // 8 * 8
+
+
+def xfc_logits_grad(W, X, Gt, ldG, pos_rows, pos_labels, nnz, label0, loss_acc=None, raw_out=None):
+    Lc, D = W.shape
+    B = X.shape[0]
+    ws = workspace(W.device)
+    _call("rb_xfc_logits_grad", _p(W), _I(Lc), _I(D), _p(X), _I(B), _p(Gt), _I(ldG), _p(pos_rows), _p(pos_labels),
+          _p(nnz), _I(label0), _p(loss_acc), _p(raw_out), _p(ws.status), _stream())
+
+
+def xfc_dx(Gt, ldG, W, B, dX, hp_buf, splits):
+    Lc, D = W.shape
+    ws = workspace(W.device)
+    _call("rb_xfc_dx", _p(Gt), _I(ldG), _p(W), _I(Lc), _I(D), _I(B), _p(dX), _p(hp_buf), _I(splits), _p(ws.status),
+          _stream())
+
+
+def xfc_dw_sgd(Gt, ldG, X, W, M, hp_buf, mo, wd):
+    Lc, D = W.shape
+    B = X.shape[0]
+    ws = workspace(W.device)
+    _call("rb_xfc_dw_sgd", _p(Gt), _I(ldG), _p(X), _I(B), _p(W), _p(M), _I(Lc), _I(D), _p(hp_buf), _F(mo), _F(wd),
+          _p(ws.status), _stream())
+
+
+def dx_splits(B: int, D: int, Lc: int) -> int:
+    """Split-K factor of the dX GEMM so that the grid covers the 148 SMs about once."""
+    tiles = ((B + 127) // 128) * ((D + 255) // 256)
+    kb = (Lc + 63) // 64
+    return max(1, min(kb, (148 + tiles - 1) // tiles))
+
+
+def xfc_step(xfc, X, pos_rows, pos_labels, nnz, dX_out, hp, mo, wd, want_loss):
+    """Chunked K1 → K3 → K2 over the label shard (see :class:`renee_b200.models.xfc.XFCClassifier`)."""
+    B, D = X.shape
+    ldG = _ld_g(B)
+    sc = xfc.scratch(B)
+    Gt = sc["Gt"]
+    loss = None
+    if want_loss:
+        loss = sc.setdefault("loss", torch.zeros(1, dtype=torch.float32, device=X.device))
+        loss.zero_()
+    dX_out.zero_()
+    for l0 in range(0, xfc.Ls, xfc.chunk):
+        l1 = min(xfc.Ls, l0 + xfc.chunk)
+        Wc, Mc = xfc.W[l0:l1], xfc.M[l0:l1]
+        xfc_logits_grad(Wc, X, Gt, ldG, pos_rows, pos_labels, nnz, l0, loss_acc=loss)
+        xfc_dx(Gt, ldG, Wc, B, dX_out, hp.buf, dx_splits(B, D, l1 - l0))
+        xfc_dw_sgd(Gt, ldG, X, Wc, Mc, hp.buf, mo, wd)
+    if want_loss:
+        _call("rb_xfc_pos_logit_sum", _p(xfc.W), _p(X), _I(D), _p(pos_rows), _p(pos_labels), _p(nnz), _p(loss),
+              _stream())
+        return loss[0]
+    return None
+
+
+def xfc_topk(xfc, X, k):
+    """Local top-k of ``X Wᵀ``: fp32 logits of one label chunk at a time from the tcgen05 GEMM (raw
+    epilogue), reduced with a running top-k."""
+    B, D = X.shape
+    ldG = _ld_g(B)
+    chunk = min(xfc.chunk, max(128, (16 << 20) // (4 * ldG) // 128 * 128))
+    Z = torch.empty(chunk, ldG, dtype=torch.float32, device=X.device)
+    vals = idxs = None
+    for l0 in range(0, xfc.Ls, chunk):
+        l1 = min(xfc.Ls, l0 + chunk)
+        xfc_logits_grad(xfc.W[l0:l1], X, None, ldG, None, None, None, l0, raw_out=Z)
+        v, i = torch.topk(Z[: l1 - l0, :B].t(), min(k, l1 - l0), dim=1)
+        i = i + l0
+        if vals is None:
+            vals, idxs = v, i
+        else:
+            cv, ci = torch.cat([vals, v], 1), torch.cat([idxs, i], 1)
+            vals, sel = torch.topk(cv, min(k, cv.shape[1]), dim=1)
+            idxs = torch.gather(ci, 1, sel)
+    return vals, idxs

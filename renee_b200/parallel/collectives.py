@@ -63,15 +63,20 @@ class TorchCollectives:
         return out[: e - s]
 
     # ---- encoder gradients
-    def allreduce_grads(self, g: torch.Tensor, hp) -> None:
-        """Average the flat gradient buffer over ranks and raise ``hp``'s found-inf flag if any
-        element is non-finite."""
+    def allreduce_grads(self, g: torch.Tensor, hp) -> float:
+        """Sum the flat gradient buffer over ranks and raise ``hp``'s found-inf flag if any element is
+        non-finite.  Returns the factor the optimizer still has to apply to obtain the MEAN over ranks
+        (DDP semantics, reference main.py:161) — folded into the fused AdamW's unscale multiply."""
         from ..optim.hparams import HP
         if self.G > 1:
             dist.all_reduce(g)
-            g.mul_(1.0 / self.G)
-        bad = (~torch.isfinite(g)).any().to(torch.float32)
-        hp.buf[HP.FOUND_INF] = torch.maximum(hp.buf[HP.FOUND_INF], bad)
+        if g.is_cuda:
+            from ..ops import cuda as cu
+            cu.grad_check(g, hp)
+        else:
+            bad = (~torch.isfinite(g)).any().to(torch.float32)
+            hp.buf[HP.FOUND_INF] = torch.maximum(hp.buf[HP.FOUND_INF], bad)
+        return 1.0 / self.G
 
     # ---- small exchanges
     def allreduce_scalar(self, t: torch.Tensor) -> torch.Tensor:

@@ -143,6 +143,9 @@ class XCTrainer:
         self.step_rng = ops.StepRNG(0, self.hp.seed_tensor())
         self.loss_sum = 0.0
         self.loss_steps = 0
+        self._graphs: dict = {}
+        self._graph_warm: dict = {}
+        self._pending_loss = None
         if cfg.default_impl:
             self._init_default()
         else:
@@ -193,7 +196,7 @@ class XCTrainer:
         self.max_nnz = cap
         self.buf["pos_rows"] = torch.zeros(cap, dtype=torch.int32, device=self.device)
         self.buf["pos_labels"] = torch.zeros(cap, dtype=torch.int32, device=self.device)
-        self._graph = None   # static addresses changed
+        self._graphs, self._graph_warm = {}, {}   # static addresses changed: captured graphs are stale
 
     # ------------------------------------------------------------------ one step (optimized)
     def _set_hparams(self) -> None:
@@ -218,23 +221,63 @@ class XCTrainer:
         return int(batch.input_ids.numel() * 4 + batch.attention_mask.numel() * 4 + batch.pos_rows.numel() * 8
                    + HP.HOST_SLOTS * 4)
 
+    def stage_batch(self, batch: XCBatch) -> None:
+        """Host→device part of a step: this step's hyper-parameters (32 bytes) and inputs."""
+        self._set_hparams()
+        b, nnz = self._upload(batch)
+        want_loss = (not self.cfg.noloss) and (self.count % LOSS_SAMPLE_FREQ == 0)
+        self._staged = (b, batch.batch_size, nnz, want_loss)
+
+    def device_step(self):
+        """Device part of a step on the staged batch: a CUDA-graph replay when one has been captured
+        for this shape, the same launch sequence issued eagerly otherwise."""
+        b, B, nnz, want_loss = self._staged
+        key = (b, B)
+        use_graph = (self.cfg.cuda_graph and self.device.type == "cuda" and not want_loss
+                     and getattr(self.comm, "graph_safe", self.G == 1))
+        if use_graph:
+            g = self._graphs.get(key)
+            if g is not None:
+                g.replay()
+                return None
+            seen = self._graph_warm.get(key, 0)
+            self._graph_warm[key] = seen + 1
+            if seen >= 2:
+                self._capture(key, b, B, nnz)
+                self._graphs[key].replay()
+                return None
+        return self._device_step(b, B, nnz, want_loss)
+
+    def _capture(self, key, b: int, B: int, nnz: int) -> None:
+        from .ops import cuda as cu
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        n0 = cu.launch_count()
+        with torch.cuda.graph(graph):
+            self._device_step(b, B, nnz, False)
+        self._graph_launches = cu.launch_count() - n0
+        self._graphs[key] = graph
+
+    def graph_active(self) -> bool:
+        return bool(self._graphs)
+
+    def launches_per_step(self) -> int:
+        return int(getattr(self, "_graph_launches", 0))
+
     def train_step(self, batch: XCBatch) -> torch.Tensor | None:
         """Runs one optimized step; returns the sampled loss tensor (device, un-normalised) on
         sampling steps, else ``None``.  No host synchronisation happens here."""
         if self.cfg.default_impl:
             return self.default_step(batch)
-        cfg = self.cfg
-        self._set_hparams()
-        b, nnz = self._upload(batch)
-        B = batch.batch_size
-        want_loss = (not cfg.noloss) and (self.count % LOSS_SAMPLE_FREQ == 0)
-        loss = self._device_step(b, B, nnz, want_loss)
+        self.stage_batch(batch)
+        want_loss = self._staged[3]
+        loss = self.device_step()
         self.count += 1
         self.rng.advance()
         self.xfc_sched.step()
         self.tf_sched.step()
         if want_loss:
-            self._pending_loss = (loss, B)
+            self._pending_loss = (loss, batch.batch_size)
         return loss
 
     def _device_step(self, b: int, B: int, nnz: int, want_loss: bool):
@@ -253,8 +296,9 @@ class XCTrainer:
         de = bf["de"][:b]
         ops.dropout_bwd(dx_local, cfg.dropout, self.step_rng, _S_CLS_DROPOUT, de)
         enc.backward(de)
-        self.comm.allreduce_grads(enc.g, self.hp)
-        ops.adamw_step(enc.p32, enc.m, enc.v, enc.g, enc.p16, self.hp, 0.9, 0.999, cfg.adam_eps, cfg.wd2, enc.n_decay)
+        grad_mult = self.comm.allreduce_grads(enc.g, self.hp)
+        ops.adamw_step(enc.p32, enc.m, enc.v, enc.g, enc.p16, self.hp, 0.9, 0.999, cfg.adam_eps, cfg.wd2, enc.n_decay,
+                       grad_mult)
         self.hp.update_scale()
         return loss
 
