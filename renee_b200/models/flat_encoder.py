@@ -49,7 +49,7 @@ class _Slot:
 
 class FlatEncoder:
     def __init__(self, cfg: EncoderConfig, device, act_dtype=torch.bfloat16, pooling: str = "mean",
-                 bottleneck_dims: int = 0, seed: int = 0, grad_buffer: torch.Tensor | None = None):
+                 bottleneck_dims: int = 0, seed: int = 0, grad_alloc=None):
         self.cfg = cfg
         self.device = torch.device(device)
         self.act_dtype = act_dtype
@@ -94,9 +94,9 @@ class FlatEncoder:
         dev = self.device
         self.p32 = torch.zeros(off, dtype=torch.float32, device=dev)
         self.p16 = self.p32 if act_dtype == torch.float32 else torch.zeros(off, dtype=act_dtype, device=dev)
-        if grad_buffer is not None:
-            assert grad_buffer.numel() >= off and grad_buffer.dtype == act_dtype
-            self.g = grad_buffer[:off]
+        if grad_alloc is not None and act_dtype != torch.float32:
+            # the gradient buffer lives where the collective backend wants it (symmetric peer memory)
+            self.g = grad_alloc(off, act_dtype)[:off]
         else:
             self.g = torch.zeros(off, dtype=act_dtype, device=dev)
         self.m = torch.zeros(off, dtype=torch.float32, device=dev)

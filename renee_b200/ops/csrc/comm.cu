@@ -1,0 +1,252 @@
+// Collectives over NVLink peer memory, written as plain kernels that load from / store to the other
+// GPUs' buffers (P2P mappings of a symmetric allocation) and synchronise through step-tagged flags:
+//
+//   ag_push         classifier-input dropout + fp16 cast of this rank's embeddings, stored straight into
+//                   every rank's gathered-X buffer, then "rows of rank r are in" flags     (signals)
+//                   -> the logits GEMM's producer warp waits for the flags (xfc.cu)        (waits)
+//   rs_pull         waits for every rank's "my dX partial is complete" flag (raised by the last CTA of
+//                   its dX GEMM, xfc.cu), sums this rank's rows over all ranks' partials and applies the
+//                   dropout backward                                                       (waits)
+//   signal          raises one flag on every rank after a system-scope fence               (signals)
+//   grad_allreduce  two-shot all-reduce of a range of the flat encoder-gradient buffer: this rank sums
+//                   its 1/G slice over all ranks (fp32 accumulation, non-finite detection) and stores the
+//                   result into every rank's buffer                         (waits on A, signals B)
+//   wait_flags      waits for "all ranks have pushed their slices" and folds the non-finite words into
+//                   the found-inf flag                                                     (waits)
+//   step_inc        advances the device-resident step counter the tags are derived from
+//
+// They replace NCCL all_gather / all_reduce / the DDP bucket all-reduce of the reference
+// (dl_base.py:547-555, 617, main.py:161).  For a given flag class a kernel either signals or waits,
+// never both, so emulated ranks can be run one after another on a single GPU in tests.  Every wait is
+// bounded: on expiry it records a status word and the kernel finishes normally.  Buffers written by
+// peers are double-buffered by step parity on the host side.
+#include "peer.cuh"
+
+namespace rb {
+
+// All threads of the block learn whether flags[0..n) have all reached `want`.
+__device__ __forceinline__ bool block_wait_flags(const uint32_t* flags, int n, uint32_t want, int* status, int detail) {
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < n) {
+    if (!wait_flag(flags + threadIdx.x, want, status, detail * 100 + (int)threadIdx.x)) ok_s = 0;
+  }
+  __syncthreads();
+  return ok_s != 0;
+}
+
+__global__ void step_inc_kernel(uint32_t* step) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) *step += 1u;
+}
+
+// ------------------------------------------------------------------------------------ all-gather push
+// grid = (G, nblk).  Block (peer, j) writes its share of this rank's rows into `peer`'s X buffer.
+__global__ void __launch_bounds__(256) ag_push_kernel(const float* __restrict__ e, int b, int D, float p,
+                                                      const int* __restrict__ seed_ptr, uint32_t stream, PeerPtrs xbuf,
+                                                      int row0, PeerPtrs flags, int flag_base, int my_rank, StepTag tag,
+                                                      unsigned* __restrict__ counters) {
+  const int peer = blockIdx.x;
+  __half* dst = reinterpret_cast<__half*>(xbuf.p[peer]) + (size_t)row0 * D;
+  const uint32_t seed = p > 0.f ? (uint32_t)(*seed_ptr) : 0u;
+  const float inv_keep = p > 0.f ? 1.f / (1.f - p) : 1.f;
+  const size_t n_vec = (size_t)b * D / 8;
+  for (size_t i = (size_t)blockIdx.y * blockDim.x + threadIdx.x; i < n_vec; i += (size_t)gridDim.y * blockDim.x) {
+    float v[8];
+    load8(e + i * 8, v);
+    if (p > 0.f) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = keep(seed, stream, (uint32_t)(i * 8 + j), p) ? v[j] * inv_keep : 0.f;
+    }
+    store8(dst + i * 8, v);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned done = atomicAdd(counters + peer, 1u);
+    if (done == gridDim.y - 1) {
+      counters[peer] = 0u;
+      __threadfence_system();
+      st_release_sys(reinterpret_cast<uint32_t*>(flags.p[peer]) + flag_base + my_rank, tag.value());
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------ reduce-scatter pull
+// grid = rows of this rank; de[r, :] = dropout_bwd( sum_q partial_q[row0 + r, :] )
+__global__ void __launch_bounds__(128) rs_pull_kernel(PeerPtrs partials, int G, int row0, int b, int D,
+                                                      float* __restrict__ de, const uint32_t* __restrict__ my_flags,
+                                                      StepTag tag, float p, const int* __restrict__ seed_ptr,
+                                                      uint32_t stream, int* status) {
+  const bool ok = block_wait_flags(my_flags, G, tag.value(), status, 2);
+  const int r = blockIdx.x;
+  if (r >= b) return;
+  const uint32_t seed = p > 0.f ? (uint32_t)(*seed_ptr) : 0u;
+  const float inv_keep = p > 0.f ? 1.f / (1.f - p) : 1.f;
+  for (int c = threadIdx.x * 4; c < D; c += blockDim.x * 4) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (ok) {
+      for (int q = 0; q < G; ++q) {
+        const float* src = reinterpret_cast<const float*>(partials.p[q]) + (size_t)(row0 + r) * D + c;
+        const uint4 raw = ld_sys_v4(src);
+        acc.x += __uint_as_float(raw.x); acc.y += __uint_as_float(raw.y);
+        acc.z += __uint_as_float(raw.z); acc.w += __uint_as_float(raw.w);
+      }
+    }
+    if (p > 0.f) {
+      const uint32_t base = (uint32_t)(r * D + c);
+      acc.x = keep(seed, stream, base, p) ? acc.x * inv_keep : 0.f;
+      acc.y = keep(seed, stream, base + 1, p) ? acc.y * inv_keep : 0.f;
+      acc.z = keep(seed, stream, base + 2, p) ? acc.z * inv_keep : 0.f;
+      acc.w = keep(seed, stream, base + 3, p) ? acc.w * inv_keep : 0.f;
+    }
+    *reinterpret_cast<float4*>(de + (size_t)r * D + c) = acc;
+  }
+}
+
+// ------------------------------------------------------------------------------------ generic signal / wait
+__global__ void signal_kernel(PeerPtrs flags, int G, int flag_base, int my_rank, StepTag tag) {
+  __threadfence_system();
+  if ((int)threadIdx.x < G)
+    st_release_sys(reinterpret_cast<uint32_t*>(flags.p[threadIdx.x]) + flag_base + my_rank, tag.value());
+}
+
+// waits for flags[0..G) >= tag; then ORs the peers' non-finite words into hp[FOUND_INF] and clears them
+__global__ void wait_flags_kernel(const uint32_t* my_flags, int G, StepTag tag, uint32_t* found_words, float* hp,
+                                  int* status) {
+  block_wait_flags(my_flags, G, tag.value(), status, 3);
+  if (threadIdx.x == 0 && found_words != nullptr) {
+    uint32_t any = 0;
+    for (int q = 0; q < G; ++q) { any |= ld_acquire_sys(found_words + q); found_words[q] = 0u; }
+    if (any) hp[HP_FOUND_INF] = 1.0f;
+  }
+}
+
+// ------------------------------------------------------------------------------------ gradient all-reduce
+// Range [lo, hi) of the flat gradient buffer (element offsets, multiples of 8).  This rank reduces the
+// G-th part `my_rank` of the range and stores the sums into every rank's buffer.
+template <typename T>
+__global__ void __launch_bounds__(256) grad_allreduce_kernel(PeerPtrs grads, long long lo, long long hi, int G, int my_rank,
+                                                             const uint32_t* __restrict__ my_flags_a, StepTag tag_a,
+                                                             PeerPtrs flags, int flag_b_base, int found_base, StepTag tag_b,
+                                                             unsigned* __restrict__ counter, int* status) {
+  const bool ok = block_wait_flags(my_flags_a, G, tag_a.value(), status, 4);
+  const long long n_vec = (hi - lo) / 8;
+  const long long per = (n_vec + G - 1) / G;
+  const long long v0 = min(n_vec, per * my_rank), v1 = min(n_vec, per * (my_rank + 1));
+  bool bad = false;
+  if (ok) {
+    for (long long i = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < v1; i += (long long)gridDim.x * blockDim.x) {
+      const size_t e = (size_t)(lo + i * 8);
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int q = 0; q < G; ++q) {
+        const uint4 raw = ld_sys_v4(reinterpret_cast<const T*>(grads.p[q]) + e);
+        const T* h = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += to_f(h[j]);
+      }
+      uint4 out;
+      T* o = reinterpret_cast<T*>(&out);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { bad |= !isfinite(acc[j]); o[j] = from_f<T>(acc[j]); }
+      for (int q = 0; q < G; ++q) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(grads.p[q]) + e) = out;
+    }
+  }
+  if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) {
+    for (int q = 0; q < G; ++q) reinterpret_cast<uint32_t*>(flags.p[q])[found_base + my_rank] = 1u;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned done = atomicAdd(counter, 1u);
+    if (done == gridDim.x - 1) {
+      *counter = 0u;
+      __threadfence_system();
+      const uint32_t v = tag_b.value();
+      for (int q = 0; q < G; ++q) st_release_sys(reinterpret_cast<uint32_t*>(flags.p[q]) + flag_b_base + my_rank, v);
+    }
+  }
+}
+
+}  // namespace rb
+
+using namespace rb;
+
+static PeerPtrs make_ptrs(void* const* arr, int G) {
+  PeerPtrs p{};
+  for (int i = 0; i < G && i < kMaxPeers; ++i) p.p[i] = arr[i];
+  return p;
+}
+
+RB_API int rb_step_inc(unsigned* step, cudaStream_t st) {
+  step_inc_kernel<<<1, 32, 0, st>>>(step);
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+RB_API int rb_ag_push(const float* e, int b, int D, float p, const int* seed, unsigned stream_id, void* const* xbufs,
+                      int row0, void* const* flags, int flag_base, int my_rank, int G, const unsigned* step_ptr,
+                      unsigned* counters, cudaStream_t st) {
+  if (G > kMaxPeers || (b * (long long)D) % 8) return -3;
+  const long long n_vec = (long long)b * D / 8;
+  int nblk = (int)((n_vec + 255) / 256);
+  if (nblk > 16) nblk = 16;
+  if (nblk < 1) nblk = 1;
+  dim3 grid(G, nblk);
+  ag_push_kernel<<<grid, 256, 0, st>>>(e, b, D, p, seed, stream_id, make_ptrs(xbufs, G), row0, make_ptrs(flags, G),
+                                       flag_base, my_rank, StepTag{step_ptr, 1u, 0u}, counters);
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+RB_API int rb_rs_pull(void* const* partials, int G, int row0, int b, int D, float* de, const unsigned* my_flags,
+                      const unsigned* step_ptr, float p, const int* seed, unsigned stream_id, int* status,
+                      cudaStream_t st) {
+  if (G > kMaxPeers || D % 4) return -3;
+  rs_pull_kernel<<<b > 0 ? b : 1, 128, 0, st>>>(make_ptrs(partials, G), G, row0, b, D, de, my_flags,
+                                                 StepTag{step_ptr, 1u, 0u}, p, seed, stream_id, status);
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+RB_API int rb_signal(void* const* flags, int G, int flag_base, int my_rank, const unsigned* step_ptr, unsigned mul,
+                     unsigned add, cudaStream_t st) {
+  if (G > kMaxPeers) return -3;
+  signal_kernel<<<1, 32, 0, st>>>(make_ptrs(flags, G), G, flag_base, my_rank, StepTag{step_ptr, mul, add});
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+RB_API int rb_wait_flags(const unsigned* my_flags, int G, const unsigned* step_ptr, unsigned mul, unsigned add,
+                         unsigned* found_words, float* hp, int* status, cudaStream_t st) {
+  if (G > kMaxPeers) return -3;
+  wait_flags_kernel<<<1, 32, 0, st>>>(my_flags, G, StepTag{step_ptr, mul, add}, found_words, hp, status);
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+RB_API int rb_grad_allreduce(int dtype, void* const* grads, long long lo, long long hi, int G, int my_rank,
+                             const unsigned* my_flags_a, void* const* flags, int flag_b_base, int found_base,
+                             const unsigned* step_ptr, unsigned mul, unsigned add, unsigned* counter, int blocks,
+                             int* status, cudaStream_t st) {
+  if (G > kMaxPeers || lo % 8 || hi % 8 || hi < lo) return -3;
+  if (blocks < 1) blocks = 1;
+  PeerPtrs g = make_ptrs(grads, G), f = make_ptrs(flags, G);
+  const StepTag tag{step_ptr, mul, add};
+  switch (dtype) {
+    case RB_BF16:
+      grad_allreduce_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(g, lo, hi, G, my_rank, my_flags_a, tag, f, flag_b_base,
+                                                                   found_base, tag, counter, status);
+      break;
+    case RB_F16:
+      grad_allreduce_kernel<__half><<<blocks, 256, 0, st>>>(g, lo, hi, G, my_rank, my_flags_a, tag, f, flag_b_base,
+                                                            found_base, tag, counter, status);
+      break;
+    default:
+      return -1;  // fp32 encoders use the library all-reduce
+  }
+  RB_LAUNCH_CHECK();
+  return 0;
+}

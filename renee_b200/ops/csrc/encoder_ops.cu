@@ -14,7 +14,6 @@
 
 namespace rb {
 
-constexpr int kMaxNV = 8;  // hidden sizes up to 2048
 
 template <typename T> __device__ __forceinline__ void atomic_add8(T* p, const float (&v)[8]);
 template <> __device__ __forceinline__ void atomic_add8<float>(float* p, const float (&v)[8]) {
@@ -32,8 +31,17 @@ template <> __device__ __forceinline__ void atomic_add8<__half>(__half* p, const
     atomicAdd(reinterpret_cast<__half2*>(p) + i, __floats2half2_rn(v[2 * i], v[2 * i + 1]));
 }
 
-// Last-block-done column reduction epilogue.  Every block has already added its partial sums to
-// acc[n_vec][H] (fp32, global).  The last block converts acc to the outputs and clears it.
+// Last-block-done column reduction epilogue.  Every block has already added its partial sums to one of
+// kCopies replicas of acc[n_vec][H] (fp32, global; replica = block index mod kCopies, which divides the
+// same-address atomic traffic by kCopies).  The last block sums the replicas, converts to the outputs
+// and clears the accumulator.
+constexpr int kCopies = 8;
+
+__device__ __forceinline__ float* acc_replica(float* acc, int n_vec, int H) {
+  const unsigned blk = blockIdx.y * gridDim.x + blockIdx.x;
+  return acc + (size_t)(blk % kCopies) * n_vec * H;
+}
+
 template <typename T>
 __device__ void finalize_columns(float* acc, unsigned* counter, int n_vec, int H, T* o0, T* o1, T* o2) {
   __shared__ bool last;
@@ -46,15 +54,29 @@ __device__ void finalize_columns(float* acc, unsigned* counter, int n_vec, int H
   __syncthreads();
   if (!last) return;
   __threadfence();
-  T* outs[3] = {o0, o1, o2};
-  for (int v = 0; v < n_vec; ++v) {
-    if (outs[v] == nullptr) continue;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) {
-      float s = __ldcg(acc + (size_t)v * H + c);
-      outs[v][c] = from_f<T>(s);
+  const int tot = n_vec * H;
+  // four column groups per round so that 32 independent loads are in flight per thread
+  for (int base = 0; base < tot; base += 4 * blockDim.x) {
+    float v[4][kCopies];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = base + u * blockDim.x + threadIdx.x;
+#pragma unroll
+      for (int k = 0; k < kCopies; ++k) v[u][k] = (i < tot) ? __ldcg(acc + (size_t)k * tot + i) : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = base + u * blockDim.x + threadIdx.x;
+      if (i < tot) {
+        float s = 0.f;
+#pragma unroll
+        for (int k = 0; k < kCopies; ++k) { s += v[u][k]; acc[(size_t)k * tot + i] = 0.f; }
+        const int which = i / H;
+        T* o = which == 0 ? o0 : (which == 1 ? o1 : o2);
+        if (o != nullptr) o[i - which * H] = from_f<T>(s);
+      }
     }
   }
-  for (int i = threadIdx.x; i < n_vec * H; i += blockDim.x) acc[i] = 0.f;
   if (threadIdx.x == 0) *counter = 0u;
 }
 
@@ -298,7 +320,8 @@ __global__ void __launch_bounds__(128) ln_bwd_kernel(
   }
   __syncthreads();
   const int nvec = EMBED ? 2 : 3;
-  for (int i = threadIdx.x; i < nvec * H; i += blockDim.x) atomicAdd(acc + i, sm[i]);
+  float* my_acc = acc_replica(acc, nvec, H);
+  for (int i = threadIdx.x; i < nvec * H; i += blockDim.x) atomicAdd(my_acc + i, sm[i]);
   finalize_columns<T>(acc, counter, nvec, H, dgamma, dbeta, EMBED ? nullptr : dbias);
 }
 
@@ -310,18 +333,26 @@ __device__ __forceinline__ float gelu_grad_f(float z) {
   return cdf + z * pdf;
 }
 
+// grid = (ceil(F/8/128), row_chunks): a thread owns 8 columns (its bias stays in registers) and walks rows
 template <typename T>
-__global__ void __launch_bounds__(256) bias_gelu_fwd_kernel(const T* __restrict__ x, const T* __restrict__ bias,
-                                                            T* __restrict__ out, size_t n_vec, int F) {
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (size_t)gridDim.x * blockDim.x) {
-    const size_t e = i * 8;
-    const int col = (int)(e % F);
-    float a[8], b[8];
-    load8(x + e, a);
-    load8(bias + col, b);
+__global__ void __launch_bounds__(128) bias_gelu_fwd_kernel(const T* __restrict__ x, const T* __restrict__ bias,
+                                                            T* __restrict__ out, int rows, int F) {
+  const int col = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (col >= F) return;
+  float b[8];
+  load8(bias + col, b);
+  for (int r = blockIdx.y; r < rows; r += 4 * gridDim.y) {
+    float a[4][8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) a[j] = gelu_f(a[j] + b[j]);
-    store8(out + e, a);
+    for (int u = 0; u < 4; ++u)
+      if (r + u * gridDim.y < rows) load8(x + (size_t)(r + u * gridDim.y) * F + col, a[u]);
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (r + u * gridDim.y < rows) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[u][j] = gelu_f(a[u][j] + b[j]);
+        store8(out + (size_t)(r + u * gridDim.y) * F + col, a[u]);
+      }
   }
 }
 
@@ -337,19 +368,29 @@ __global__ void __launch_bounds__(128) bias_gelu_bwd_kernel(const T* __restrict_
   for (int j = 0; j < 8; ++j) s[j] = 0.f;
   if (col < F) {
     load8(bias + col, b);
-    for (int r = blockIdx.y; r < rows; r += gridDim.y) {
-      float a[8], g[8];
-      load8(x + (size_t)r * F + col, a);
-      load8(da + (size_t)r * F + col, g);
+    for (int r = blockIdx.y; r < rows; r += 4 * gridDim.y) {
+      float a[4][8], g[4][8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        g[j] = round_through<T>(g[j] * gelu_grad_f(a[j] + b[j]));
-        s[j] += g[j];
+      for (int u = 0; u < 4; ++u) {
+        const int rr = r + u * gridDim.y;
+        if (rr < rows) { load8(x + (size_t)rr * F + col, a[u]); load8(da + (size_t)rr * F + col, g[u]); }
       }
-      store8(dx + (size_t)r * F + col, g);
-    }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) atomicAdd(acc + col + j, s[j]);
+      for (int u = 0; u < 4; ++u) {
+        const int rr = r + u * gridDim.y;
+        if (rr < rows) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            g[u][j] = round_through<T>(g[u][j] * gelu_grad_f(a[u][j] + b[j]));
+            s[j] += g[u][j];
+          }
+          store8(dx + (size_t)rr * F + col, g[u]);
+        }
+      }
+    }
+    float* my_acc = acc_replica(acc, 1, F);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) atomicAdd(my_acc + col + j, s[j]);
   }
   finalize_columns<T>(acc, counter, 1, F, dbias, nullptr, nullptr);
 }
@@ -363,14 +404,21 @@ __global__ void __launch_bounds__(128) colsum_kernel(const T* __restrict__ x, fl
     float s[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) s[j] = 0.f;
-    for (int r = blockIdx.y; r < rows; r += gridDim.y) {
-      float a[8];
-      load8(x + (size_t)r * N + col, a);
+    for (int r = blockIdx.y; r < rows; r += 4 * gridDim.y) {
+      float a[4][8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) s[j] += a[j];
+      for (int u = 0; u < 4; ++u)
+        if (r + u * gridDim.y < rows) load8(x + (size_t)(r + u * gridDim.y) * N + col, a[u]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (r + u * gridDim.y < rows) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) s[j] += a[u][j];
+        }
     }
+    float* my_acc = acc_replica(acc, 1, N);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) atomicAdd(acc + col + j, s[j]);
+    for (int j = 0; j < 8; ++j) atomicAdd(my_acc + col + j, s[j]);
   }
   finalize_columns<T>(acc, counter, 1, N, out, nullptr, nullptr);
 }
@@ -529,10 +577,12 @@ RB_API int rb_embed_ln_bwd(int dtype, const void* dy, const int* ids, const void
 
 RB_API int rb_bias_gelu_fwd(int dtype, const void* x, const void* bias, void* out, int rows, int F, cudaStream_t st) {
   if (F % 8) return -3;
-  const size_t n_vec = (size_t)rows * F / 8;
-  int blocks = (int)((n_vec + 255) / 256);
-  if (blocks > 148 * 16) blocks = 148 * 16;
-  DISPATCH_T(dtype, (bias_gelu_fwd_kernel<T><<<blocks, 256, 0, st>>>((const T*)x, (const T*)bias, (T*)out, n_vec, F)));
+  const int cb = (F / 8 + 127) / 128;
+  int rc = 148 * 12 / cb;
+  if (rc > (rows + 3) / 4) rc = (rows + 3) / 4;
+  if (rc < 1) rc = 1;
+  dim3 grid(cb, rc);
+  DISPATCH_T(dtype, (bias_gelu_fwd_kernel<T><<<grid, 128, 0, st>>>((const T*)x, (const T*)bias, (T*)out, rows, F)));
   RB_LAUNCH_CHECK();
   return 0;
 }
@@ -540,7 +590,11 @@ RB_API int rb_bias_gelu_fwd(int dtype, const void* x, const void* bias, void* ou
 RB_API int rb_bias_gelu_bwd(int dtype, const void* da, const void* x, const void* bias, void* dx, float* acc,
                             unsigned* counter, void* dbias, int rows, int F, cudaStream_t st) {
   if (F % 8) return -3;
-  dim3 grid((F / 8 + 127) / 128, rows < 192 ? rows : 192);
+  const int cb = (F / 8 + 127) / 128;
+  int rc = 148 * 12 / cb;
+  if (rc > (rows + 3) / 4) rc = (rows + 3) / 4;
+  if (rc < 1) rc = 1;
+  dim3 grid(cb, rc);
   DISPATCH_T(dtype, (bias_gelu_bwd_kernel<T><<<grid, 128, 0, st>>>((const T*)da, (const T*)x, (const T*)bias, (T*)dx,
                                                                     acc, counter, (T*)dbias, rows, F)));
   RB_LAUNCH_CHECK();
@@ -550,7 +604,11 @@ RB_API int rb_bias_gelu_bwd(int dtype, const void* da, const void* x, const void
 RB_API int rb_colsum(int dtype, const void* x, float* acc, unsigned* counter, void* out, int rows, int N,
                      cudaStream_t st) {
   if (N % 8) return -3;
-  dim3 grid((N / 8 + 127) / 128, rows < 192 ? rows : 192);
+  const int cb = (N / 8 + 127) / 128;
+  int rc = 148 * 12 / cb;
+  if (rc > (rows + 3) / 4) rc = (rows + 3) / 4;
+  if (rc < 1) rc = 1;
+  dim3 grid(cb, rc);
   DISPATCH_T(dtype, (colsum_kernel<T><<<grid, 128, 0, st>>>((const T*)x, acc, counter, (T*)out, rows, N)));
   RB_LAUNCH_CHECK();
   return 0;

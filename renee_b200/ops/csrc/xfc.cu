@@ -17,7 +17,7 @@
 // Structure of every kernel: 192 threads; warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
 // warps 2..5 = epilogue (one TMEM lane quarter each).  4-stage smem ring, 128x{<=256}x64 tiles,
 // UMMA 128xNx16.  All waits are bounded (see tc.cuh).
-#include "tc.cuh"
+#include "peer.cuh"
 
 namespace rb {
 
@@ -49,6 +49,9 @@ struct GemmParams {
   // DW
   __half* W; __half* Mom; int ldW; float mo; float wd;
   float* Zout;       // RAW: fp32 logits [M, ldG] (debug / top-k path)
+  // multi-GPU fusion (null / 0 when unused)
+  const uint32_t* wait_flags; int wait_n; StepTag tag;   // LOGITS: X rows of every rank have landed
+  unsigned* done_counter; PeerPtrs peer_flags; int n_peers; int flag_index;   // DX: last CTA raises "partial complete"
 };
 
 __device__ __forceinline__ int lower_bound_i32(const int* a, int n, int key) {
@@ -101,7 +104,15 @@ xfc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
   if (warp == 0 && lane == 0 && has_work) {
     // ---------------- TMA producer
-    for (int kb = kb0, it = 0; kb < kb1; ++kb, ++it) {
+    if (MODE == MODE_LOGITS && p.wait_flags != nullptr) {
+      // all-gather prologue: every rank has pushed its rows of X into this GPU's buffer and raised its
+      // flag; the loads below go through the async proxy, hence the proxy fence after the acquire
+      const uint32_t want = p.tag.value();
+      for (int q = 0; q < p.wait_n; ++q)
+        if (!wait_flag(p.wait_flags + q, want, p.status, 100 + q)) aborted = true;
+      asm volatile("fence.proxy.async;" ::: "memory");
+    }
+    for (int kb = kb0, it = 0; kb < kb1 && !aborted; ++kb, ++it) {
       const int s = it % kStages;
       const uint32_t ph = (it / kStages) & 1;
       if (!tc::mbar_wait(empty_bar + s, ph ^ 1, aborted, p.status, tc::SITE_EMPTY, kb)) break;
@@ -250,11 +261,24 @@ xfc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
     }
   }
+  if (MODE == MODE_DX && p.done_counter != nullptr) __threadfence_system();   // this CTA's red.adds are visible
   tc::tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc::tc_fence_after();
     tc::tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (MODE == MODE_DX && p.done_counter != nullptr && threadIdx.x == 0) {
+    // reduce-scatter epilogue: the last CTA of this rank's dX GEMM tells every rank that the partial
+    // sums in this rank's buffer are complete
+    const unsigned total = gridDim.x * gridDim.y * gridDim.z;
+    if (atomicAdd(p.done_counter, 1u) == total - 1) {
+      *p.done_counter = 0u;
+      __threadfence_system();
+      const uint32_t v = p.tag.value();
+      for (int q = 0; q < p.n_peers; ++q)
+        st_release_sys(reinterpret_cast<uint32_t*>(p.peer_flags.p[q]) + p.flag_index, v);
+    }
   }
 }
 
@@ -303,7 +327,8 @@ static int round_up(int x, int m) { return (x + m - 1) / m * m; }
 // (no sigmoid, no positives) into raw_out[Lc, ldG].
 RB_API int rb_xfc_logits_grad(const void* W, int Lc, int D, const void* X, int B, void* Gt, int ldG,
                               const int* pos_rows, const int* pos_labels, const int* nnz_ptr, int label0,
-                              float* loss_acc, float* raw_out, int* status, cudaStream_t st) {
+                              float* loss_acc, float* raw_out, const unsigned* wait_flags, int wait_n,
+                              const unsigned* step_ptr, int* status, cudaStream_t st) {
   if (D % 8 || ldG % 8 || ldG < B || Lc < 1 || B < 1) return -3;
   const int BN = B >= 256 ? 256 : round_up(B, 16);
   CUtensorMap ta, tb;
@@ -315,13 +340,11 @@ RB_API int rb_xfc_logits_grad(const void* W, int Lc, int D, const void* X, int B
   p.M = Lc; p.N = B; p.BN = BN; p.kb_total = (D + kBK - 1) / kBK; p.kb_per_split = p.kb_total; p.status = status;
   p.Gt = (__half*)Gt; p.ldG = ldG; p.pos_rows = pos_rows; p.pos_labels = pos_labels; p.nnz_ptr = nnz_ptr;
   p.label0 = label0; p.loss_acc = loss_acc; p.Zout = raw_out;
+  p.wait_flags = wait_flags; p.wait_n = wait_n; p.tag = StepTag{step_ptr, 1u, 0u};
   dim3 grid((Lc + kBM - 1) / kBM, (B + BN - 1) / BN, 1);
   rc = raw_out ? launch_gemm<MODE_RAW>(ta, tb, p, grid, st) : launch_gemm<MODE_LOGITS>(ta, tb, p, grid, st);
   if (rc) return rc;
   RB_LAUNCH_CHECK();
-  if (loss_acc != nullptr && raw_out == nullptr && pos_labels != nullptr) {
-    // the positives' logits are subtracted once per step by the caller (rb_xfc_pos_logit_sum)
-  }
   return 0;
 }
 
@@ -335,8 +358,11 @@ RB_API int rb_xfc_pos_logit_sum(const void* W, const void* X, int D, const int* 
 }
 
 // dX[B, D] += hp[SCALE] * Gt^T W over the chunk (dX must have been zeroed before the first chunk)
+// With done_counter != null the last CTA stores the step tag into word flag_index of every peer's flag
+// array (the fused reduce-scatter signal; pass it on the final label chunk only).
 RB_API int rb_xfc_dx(const void* Gt, int ldG, const void* W, int Lc, int D, int B, float* dX, const float* hp,
-                     int splits, int* status, cudaStream_t st) {
+                     int splits, unsigned* done_counter, void* const* peer_flags, int n_peers, int flag_index,
+                     const unsigned* step_ptr, int* status, cudaStream_t st) {
   if (D % 8 || ldG % 8 || Lc < 1) return -3;
   const int BN = D >= 256 ? 256 : round_up(D, 64);
   CUtensorMap ta, tb;
@@ -351,6 +377,11 @@ RB_API int rb_xfc_dx(const void* Gt, int ldG, const void* W, int Lc, int D, int 
   p.kb_per_split = (p.kb_total + splits - 1) / splits;
   splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
   p.dX = dX; p.ldX = D; p.hp = hp;
+  if (done_counter != nullptr) {
+    if (n_peers > kMaxPeers) return -3;
+    p.done_counter = done_counter; p.n_peers = n_peers; p.flag_index = flag_index; p.tag = StepTag{step_ptr, 1u, 0u};
+    for (int q = 0; q < n_peers; ++q) p.peer_flags.p[q] = peer_flags[q];
+  }
   dim3 grid((B + kBM - 1) / kBM, (D + BN - 1) / BN, splits);
   rc = launch_gemm<MODE_DX>(ta, tb, p, grid, st);
   if (rc) return rc;

@@ -74,7 +74,7 @@ class _Workspace:
     kernels), block counters, and the status words the bounded waits write."""
 
     def __init__(self, device):
-        self.colacc = torch.zeros(4 * 8192, dtype=torch.float32, device=device)
+        self.colacc = torch.zeros(8 * 3 * 8192, dtype=torch.float32, device=device)   # 8 replicas x 3 vectors x max width
         self.counters = torch.zeros(16, dtype=torch.int32, device=device)
         self.status = torch.zeros(8, dtype=torch.int32, device=device)
 
@@ -205,19 +205,28 @@ def _ld_g(B: int) -> int:
     return (B + 7) // 8 * 8
 
 
-def xfc_logits_grad(W, X, Gt, ldG, pos_rows, pos_labels, nnz, label0, loss_acc=None, raw_out=None):
+def xfc_logits_grad(W, X, Gt, ldG, pos_rows, pos_labels, nnz, label0, loss_acc=None, raw_out=None, wait=None):
+    """``wait = (flags_tensor, n, step_tensor)``: the producer warp waits until ``flags[0:n] >= *step``
+    (the all-gather of X has landed) before its first load."""
     Lc, D = W.shape
     B = X.shape[0]
     ws = workspace(W.device)
+    wf, wn, wstep = (wait if wait is not None else (None, 0, None))
     _call("rb_xfc_logits_grad", _p(W), _I(Lc), _I(D), _p(X), _I(B), _p(Gt), _I(ldG), _p(pos_rows), _p(pos_labels),
-          _p(nnz), _I(label0), _p(loss_acc), _p(raw_out), _p(ws.status), _stream())
+          _p(nnz), _I(label0), _p(loss_acc), _p(raw_out), _p(wf), _I(wn), _p(wstep), _p(ws.status), _stream())
 
 
-def xfc_dx(Gt, ldG, W, B, dX, hp_buf, splits):
+def xfc_dx(Gt, ldG, W, B, dX, hp_buf, splits, signal=None):
+    """``signal = (counter_tensor, peer_flag_ptr_array, n_peers, flag_index, step_tensor)``: the last CTA
+    stores ``*step`` into word ``flag_index`` of every peer's flag array (reduce-scatter signal)."""
     Lc, D = W.shape
     ws = workspace(W.device)
-    _call("rb_xfc_dx", _p(Gt), _I(ldG), _p(W), _I(Lc), _I(D), _I(B), _p(dX), _p(hp_buf), _I(splits), _p(ws.status),
-          _stream())
+    if signal is None:
+        cnt, ptrs, n, idx, step = None, None, 0, 0, None
+    else:
+        cnt, ptrs, n, idx, step = signal
+    _call("rb_xfc_dx", _p(Gt), _I(ldG), _p(W), _I(Lc), _I(D), _I(B), _p(dX), _p(hp_buf), _I(splits), _p(cnt),
+          ptrs if ptrs is not None else _VP(0), _I(n), _I(idx), _p(step), _p(ws.status), _stream())
 
 
 def xfc_dw_sgd(Gt, ldG, X, W, M, hp_buf, mo, wd):
@@ -235,8 +244,10 @@ def dx_splits(B: int, D: int, Lc: int) -> int:
     return max(1, min(kb, (148 + tiles - 1) // tiles))
 
 
-def xfc_step(xfc, X, pos_rows, pos_labels, nnz, dX_out, hp, mo, wd, want_loss):
-    """Chunked K1 → K3 → K2 over the label shard (see :class:`renee_b200.models.xfc.XFCClassifier`)."""
+def xfc_step(xfc, X, pos_rows, pos_labels, nnz, dX_out, hp, mo, wd, want_loss, wait=None, signal=None):
+    """Chunked K1 → K3 → K2 over the label shard (see :class:`renee_b200.models.xfc.XFCClassifier`).
+    ``wait`` is handed to the first logits GEMM (all-gather prologue), ``signal`` to the last dX GEMM
+    (reduce-scatter epilogue)."""
     B, D = X.shape
     ldG = _ld_g(B)
     sc = xfc.scratch(B)
@@ -246,17 +257,19 @@ def xfc_step(xfc, X, pos_rows, pos_labels, nnz, dX_out, hp, mo, wd, want_loss):
         loss = sc.setdefault("loss", torch.zeros(1, dtype=torch.float32, device=X.device))
         loss.zero_()
     dX_out.zero_()
-    for l0 in range(0, xfc.Ls, xfc.chunk):
+    chunks = list(range(0, xfc.Ls, xfc.chunk))
+    for ci, l0 in enumerate(chunks):
         l1 = min(xfc.Ls, l0 + xfc.chunk)
         Wc, Mc = xfc.W[l0:l1], xfc.M[l0:l1]
-        xfc_logits_grad(Wc, X, Gt, ldG, pos_rows, pos_labels, nnz, l0, loss_acc=loss)
-        xfc_dx(Gt, ldG, Wc, B, dX_out, hp.buf, dx_splits(B, D, l1 - l0))
+        xfc_logits_grad(Wc, X, Gt, ldG, pos_rows, pos_labels, nnz, l0, loss_acc=loss, wait=wait if ci == 0 else None)
+        if want_loss and ci == 0:
+            # minus the logits at the positives, taken before any chunk's weights are updated (and after
+            # the first GEMM's wait, so X is complete)
+            _call("rb_xfc_pos_logit_sum", _p(xfc.W), _p(X), _I(D), _p(pos_rows), _p(pos_labels), _p(nnz), _p(loss),
+                  _stream())
+        xfc_dx(Gt, ldG, Wc, B, dX_out, hp.buf, dx_splits(B, D, l1 - l0), signal=signal if ci == len(chunks) - 1 else None)
         xfc_dw_sgd(Gt, ldG, X, Wc, Mc, hp.buf, mo, wd)
-    if want_loss:
-        _call("rb_xfc_pos_logit_sum", _p(xfc.W), _p(X), _I(D), _p(pos_rows), _p(pos_labels), _p(nnz), _p(loss),
-              _stream())
-        return loss[0]
-    return None
+    return loss[0] if want_loss else None
 
 
 def xfc_topk(xfc, X, k):
@@ -279,3 +292,42 @@ def xfc_topk(xfc, X, k):
             vals, sel = torch.topk(cv, min(k, cv.shape[1]), dim=1)
             idxs = torch.gather(ci, 1, sel)
     return vals, idxs
+
+
+# ----------------------------------------------------------------------------- peer-memory collectives
+def ptr_array(ptrs):
+    """ctypes ``void*[n]`` from a list of integer device addresses (kept alive by the caller)."""
+    return (_VP * len(ptrs))(*[_VP(int(x)) for x in ptrs])
+
+
+def step_inc(step):
+    _call("rb_step_inc", _p(step), _stream())
+
+
+def ag_push(e, p, rng, stream_id, xbuf_ptrs, row0, flag_ptrs, flag_base, my_rank, G, step, counters):
+    b, D = e.shape
+    _call("rb_ag_push", _p(e), _I(b), _I(D), _F(p), _p(rng.dev), _U(stream_id), xbuf_ptrs, _I(row0), flag_ptrs,
+          _I(flag_base), _I(my_rank), _I(G), _p(step), _p(counters), _stream())
+
+
+def rs_pull(partial_ptrs, G, row0, b, D, de, my_flags, step, p, rng, stream_id):
+    ws = workspace(de.device)
+    _call("rb_rs_pull", partial_ptrs, _I(G), _I(row0), _I(b), _I(D), _p(de), _p(my_flags), _p(step), _F(p), _p(rng.dev),
+          _U(stream_id), _p(ws.status), _stream())
+
+
+def signal(flag_ptrs, G, flag_base, my_rank, step, mul=1, add=0):
+    _call("rb_signal", flag_ptrs, _I(G), _I(flag_base), _I(my_rank), _p(step), _U(mul), _U(add), _stream())
+
+
+def wait_flags(my_flags, G, step, mul=1, add=0, found_words=None, hp_buf=None):
+    ws = workspace(my_flags.device)
+    _call("rb_wait_flags", _p(my_flags), _I(G), _p(step), _U(mul), _U(add), _p(found_words), _p(hp_buf), _p(ws.status),
+          _stream())
+
+
+def grad_allreduce(g_dtype, grad_ptrs, lo, hi, G, my_rank, my_flags_a, flag_ptrs, flag_b_base, found_base, step, mul, add,
+                   counter, blocks):
+    ws = workspace(my_flags_a.device)
+    _call("rb_grad_allreduce", _I(DT[g_dtype]), grad_ptrs, _LL(lo), _LL(hi), _I(G), _I(my_rank), _p(my_flags_a), flag_ptrs,
+          _I(flag_b_base), _I(found_base), _p(step), _U(mul), _U(add), _p(counter), _I(blocks), _p(ws.status), _stream())

@@ -30,6 +30,48 @@ class TorchCollectives:
         self.G = ctx.world_size
         self.rank = ctx.rank
 
+    # ---- step protocol used by the trainer (the fused backend overrides these)
+    @property
+    def graph_safe(self) -> bool:
+        """Whether the step may be replayed from a CUDA graph: yes on one rank (no collectives at all);
+        the library collectives of several ranks are launched eagerly."""
+        return self.G == 1
+
+    def setup(self, B_max: int, D: int) -> None:
+        pass
+
+    def host_begin(self) -> None:
+        pass
+
+    def device_begin(self) -> None:
+        pass
+
+    @property
+    def parity(self) -> int:
+        return 0
+
+    def embeddings_to_X(self, emb, B, p, rng, stream_id, bufs):
+        """Classifier-input dropout + cast of this rank's pooled embeddings, then the all-gather.
+        Returns ``(X [B, D], wait)``; ``wait`` is what the logits GEMM must wait for (``None`` here:
+        the library collective has completed in stream order)."""
+        from .. import ops
+        b = emb.shape[0]
+        x_local = bufs["x_local"][:b]
+        ops.dropout_cast_fwd(emb, p, rng, stream_id, x_local)
+        return self.gather_embeddings(x_local, B, bufs["X"]), None
+
+    def dx_buffer(self, B, bufs):
+        """Buffer the dX GEMM accumulates into, and the signal its last CTA has to raise (none)."""
+        return bufs["dX"][:B], None
+
+    def dx_to_local(self, dX, B, p, rng, stream_id, bufs):
+        """Sum of dX over ranks restricted to this rank's rows, with the dropout backward applied."""
+        from .. import ops
+        dx_local = self.reduce_scatter_dx(dX, B, bufs["dx_local"])
+        de = bufs["de"][: dx_local.shape[0]]
+        ops.dropout_bwd(dx_local, p, rng, stream_id, de)
+        return de
+
     # ---- embeddings
     def gather_embeddings(self, x_local: torch.Tensor, B: int, out: torch.Tensor) -> torch.Tensor:
         """``x_local [b_r, D]`` → ``out[:B]`` with rank r's rows at ``batch_row_range(B, G, r)``."""

@@ -1,0 +1,143 @@
+"""Collectives fused into the compute kernels over NVLink peer memory.
+
+:class:`PeerCollectives` keeps the interface of :class:`~renee_b200.parallel.collectives.TorchCollectives`
+but moves the per-step data path off NCCL:
+
+==========================  ==================================================================
+exchange                    realisation
+==========================  ==================================================================
+all-gather of embeddings    the pooling/dropout kernel of each rank stores its fp16 rows straight
+                            into EVERY rank's ``X`` buffer and raises a flag; the logits GEMM's
+                            producer warp waits for the flags before its first TMA load
+reduce-scatter of ``dX``    the dX GEMM accumulates into this rank's partial buffer; its last CTA
+                            raises a flag on every rank; a pull kernel sums this rank's rows over
+                            all partials (and applies the dropout backward)
+encoder-gradient all-reduce signal → two-shot kernel (each rank sums its 1/G slice over all ranks
+                            and stores the result into every rank's gradient buffer, detecting
+                            non-finite values) → wait; the mean's 1/G goes into the fused AdamW
+==========================  ==================================================================
+
+Buffers that peers write or read (``X``, the ``dX`` partials) are double-buffered by step parity;
+flags carry the step number read from a device-resident counter, so the launch sequence is identical
+every step and can be replayed from a CUDA graph (two graphs, one per parity).  The symmetric
+allocations and their peer mappings come from ``torch.distributed._symmetric_memory``; NCCL remains
+for bootstrap, evaluation merges and scalars.  No NVLS/multimem and no TMA multicast is used.
+
+Safety of the buffer reuse (rank r at step n+2 may overwrite what rank q read at step n): r can only
+reach step n+2's overwrite after finishing its own pull of step n+1, which waited for q's step-(n+1)
+dX flag, which q raised after its step-n pull in stream order.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..utils.sharding import batch_row_range
+from .collectives import TorchCollectives
+from .dist import DistContext
+
+# word offsets of the flag classes inside the symmetric flag array (16 words each)
+F_AG, F_RS, F_ARA, F_ARB, F_FOUND = 0, 16, 32, 48, 64
+FLAG_WORDS = 128
+
+
+class PeerCollectives(TorchCollectives):
+    graph_safe = True
+
+    def __init__(self, ctx: DistContext, group=None):
+        super().__init__(ctx)
+        if ctx.device.type != "cuda":
+            raise RuntimeError("PeerCollectives needs CUDA devices")
+        if self.G > 16:
+            raise RuntimeError("at most 16 peers")
+        self.group = group if group is not None else dist.group.WORLD
+        self._handles = []
+        self._ready = False
+        self.grad = None
+        self.host_step = 0
+
+    # ------------------------------------------------------------------ allocation
+    def _symm(self, numel: int, dtype):
+        import torch.distributed._symmetric_memory as symm_mem
+        t = symm_mem.empty(numel, dtype=dtype, device=self.ctx.device)
+        hdl = symm_mem.rendezvous(t, self.group)
+        self._handles.append(hdl)
+        return t, [int(p) for p in hdl.buffer_ptrs]
+
+    def setup(self, B_max: int, D: int) -> None:
+        from ..ops import cuda as cu
+        if self._ready:
+            return
+        dev = self.ctx.device
+        rows = B_max + self.G
+        self.D = D
+        self.flags, flag_ptrs = self._symm(FLAG_WORDS, torch.int32)
+        self.flags.zero_()
+        self.X, self.dXp, self._x_ptrs, self._dx_ptrs = [], [], [], []
+        for _ in range(2):
+            x, xp = self._symm(rows * D, torch.float16)
+            d, dp = self._symm(rows * D, torch.float32)
+            x.zero_(); d.zero_()
+            self.X.append(x.view(rows, D)); self.dXp.append(d.view(rows, D))
+            self._x_ptrs.append(cu.ptr_array(xp)); self._dx_ptrs.append(cu.ptr_array(dp))
+        self._flag_ptrs = cu.ptr_array(flag_ptrs)
+        self.step = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.counters = torch.zeros(64, dtype=torch.int32, device=dev)
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        self._ready = True
+
+    def alloc_grad(self, numel: int, dtype) -> torch.Tensor:
+        """Flat encoder-gradient buffer in symmetric memory (peers read and write it)."""
+        from ..ops import cuda as cu
+        n = (numel + 1023) // 1024 * 1024
+        self.grad, gp = self._symm(n, dtype)
+        self.grad.zero_()
+        self._grad_ptrs = cu.ptr_array(gp)
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        return self.grad
+
+    # ------------------------------------------------------------------ per-step protocol
+    @property
+    def parity(self) -> int:
+        return self.host_step & 1
+
+    def host_begin(self) -> None:
+        """Host side of a new step: flips the buffer parity.  Must be called once per step, whether the
+        device work is then launched eagerly or replayed from a graph."""
+        self.host_step += 1
+
+    def device_begin(self) -> None:
+        """Device side of a new step: advances the step counter the flag tags derive from."""
+        from ..ops import cuda as cu
+        cu.step_inc(self.step)
+
+    def embeddings_to_X(self, emb, B, p, rng, stream_id, bufs):
+        from ..ops import cuda as cu
+        s, e = batch_row_range(B, self.G, self.rank)
+        cu.ag_push(emb, p, rng, stream_id, self._x_ptrs[self.parity], s, self._flag_ptrs, F_AG, self.rank, self.G,
+                   self.step, self.counters)
+        X = self.X[self.parity][:B]
+        return X, (self.flags[F_AG:], self.G, self.step)
+
+    def dx_buffer(self, B, bufs):
+        return self.dXp[self.parity][:B], (self.counters[32:], self._flag_ptrs, self.G, F_RS + self.rank, self.step)
+
+    def dx_to_local(self, dX, B, p, rng, stream_id, bufs):
+        from ..ops import cuda as cu
+        s, e = batch_row_range(B, self.G, self.rank)
+        de = bufs["de"][: e - s]
+        cu.rs_pull(self._dx_ptrs[self.parity], self.G, s, e - s, self.D, de, self.flags[F_RS:], self.step, p, rng, stream_id)
+        return de
+
+    def allreduce_grads(self, g: torch.Tensor, hp) -> float:
+        from ..ops import cuda as cu
+        if self.grad is None or g.data_ptr() != self.grad.data_ptr() or g.dtype == torch.float32:
+            return super().allreduce_grads(g, hp)
+        n = g.numel() // 8 * 8
+        cu.signal(self._flag_ptrs, self.G, F_ARA, self.rank, self.step)
+        cu.grad_allreduce(g.dtype, self._grad_ptrs, 0, n, self.G, self.rank, self.flags[F_ARA:], self._flag_ptrs, F_ARB,
+                          F_FOUND, self.step, 1, 0, self.counters[48:], 148 * 2)
+        cu.wait_flags(self.flags[F_ARB:], self.G, self.step, 1, 0, self.flags[F_FOUND:], hp.buf)
+        return 1.0 / self.G

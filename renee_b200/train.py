@@ -165,9 +165,9 @@ class XCTrainer:
         cfg = self.cfg
         D = cfg.bottleneck_dims if cfg.bottleneck_dims > 0 else self.enc_cfg.dim
         self.D = D
+        self.comm.setup(self.B, D)
         self.encoder = FlatEncoder(self.enc_cfg, self.device, self.act_dtype, cfg.pooling, cfg.bottleneck_dims,
-                                   seed=cfg.seed, grad_buffer=self.comm.grad_buffer(self.act_dtype, self.enc_cfg, cfg)
-                                   if hasattr(self.comm, "grad_buffer") else None)
+                                   seed=cfg.seed, grad_alloc=getattr(self.comm, "alloc_grad", None))
         self.xfc = XFCClassifier(self.Ls, D, self.device, cfg.fp16xfc,
                                  rank=self.rank, seed=cfg.seed, max_batch=self.B, accum=cfg.accum,
                                  stochastic_round=cfg.stochastic_round)
@@ -232,7 +232,8 @@ class XCTrainer:
         """Device part of a step on the staged batch: a CUDA-graph replay when one has been captured
         for this shape, the same launch sequence issued eagerly otherwise."""
         b, B, nnz, want_loss = self._staged
-        key = (b, B)
+        self.comm.host_begin()
+        key = (b, B, self.comm.parity)
         use_graph = (self.cfg.cuda_graph and self.device.type == "cuda" and not want_loss
                      and getattr(self.comm, "graph_safe", self.G == 1))
         if use_graph:
@@ -281,22 +282,20 @@ class XCTrainer:
         return loss
 
     def _device_step(self, b: int, B: int, nnz: int, want_loss: bool):
-        cfg, bf, enc = self.cfg, self.buf, self.encoder
+        cfg, bf, enc, comm = self.cfg, self.buf, self.encoder, self.comm
         ids, mask = bf["ids"][:b], bf["mask"][:b]
+        comm.device_begin()
         emb = enc.forward(ids, mask, self.step_rng, train=True)
-        x_local = bf["x_local"][:b]
-        ops.dropout_cast_fwd(emb, cfg.dropout, self.step_rng, _S_CLS_DROPOUT, x_local)
-        X = self.comm.gather_embeddings(x_local, B, bf["X"])
-        dX = bf["dX"][:B]
+        # classifier-input dropout + cast + all-gather (fused into one kernel on the peer-memory backend)
+        X, wait = comm.embeddings_to_X(emb, B, cfg.dropout, self.step_rng, _S_CLS_DROPOUT, bf)
+        dX, signal = comm.dx_buffer(B, bf)
         loss = self.xfc.step(X, bf["pos_rows"], bf["pos_labels"], bf["nnz"] if X.is_cuda else nnz, dX,
-                             self.hp, cfg.mo, cfg.wd1, want_loss)
+                             self.hp, cfg.mo, cfg.wd1, want_loss, wait=wait, signal=signal)
         if want_loss:
-            loss = self.comm.allreduce_scalar(loss.reshape(1))
-        dx_local = self.comm.reduce_scatter_dx(dX, B, bf["dx_local"])
-        de = bf["de"][:b]
-        ops.dropout_bwd(dx_local, cfg.dropout, self.step_rng, _S_CLS_DROPOUT, de)
+            loss = comm.allreduce_scalar(loss.reshape(1))
+        de = comm.dx_to_local(dX, B, cfg.dropout, self.step_rng, _S_CLS_DROPOUT, bf)
         enc.backward(de)
-        grad_mult = self.comm.allreduce_grads(enc.g, self.hp)
+        grad_mult = comm.allreduce_grads(enc.g, self.hp)
         ops.adamw_step(enc.p32, enc.m, enc.v, enc.g, enc.p16, self.hp, 0.9, 0.999, cfg.adam_eps, cfg.wd2, enc.n_decay,
                        grad_mult)
         self.hp.update_scale()

@@ -1,0 +1,139 @@
+"""Peer-memory collective kernels on ONE GPU with emulated ranks.
+
+Every kernel either signals or waits for a given flag class, so the emulated ranks' kernels can be run
+one after another on a single device (all signals of a phase first, then the waiters): nothing ever
+waits for a kernel that has not run yet.  Each emulated rank has its own buffers; the "peer pointer"
+tables simply point at the other rank's buffers on the same GPU.  The last test lets a bounded wait
+run out on a flag that nothing sets and checks that the kernel returns with a status code and that
+the context stays usable.
+"""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from renee_b200 import ops
+from renee_b200.ops import reference as ref
+from renee_b200.optim.hparams import HP, HyperParams
+from renee_b200.parallel.fused import F_AG, F_ARA, F_ARB, F_FOUND, F_RS, FLAG_WORDS
+from renee_b200.utils.sharding import batch_row_range
+
+
+def dev():
+    return torch.device("cuda", 0)
+
+
+def cu():
+    from renee_b200.ops import cuda
+    return cuda
+
+
+class Rank:
+    def __init__(self, r, G, rows, D, n_grad):
+        self.r = r
+        self.flags = torch.zeros(FLAG_WORDS, dtype=torch.int32, device=dev())
+        self.X = torch.zeros(rows, D, dtype=torch.float16, device=dev())
+        self.dXp = torch.zeros(rows, D, dtype=torch.float32, device=dev())
+        self.grad = torch.zeros(n_grad, dtype=torch.bfloat16, device=dev())
+        self.step = torch.ones(1, dtype=torch.int32, device=dev())
+        self.counters = torch.zeros(64, dtype=torch.int32, device=dev())
+        self.seed = torch.tensor([77 + r], dtype=torch.int32, device=dev())
+        self.rng = ops.StepRNG(77 + r, self.seed)
+
+
+@pytest.mark.parametrize("G,B", [(2, 64), (4, 250)])
+def test_allgather_logits_dx_reducescatter_emulated(G, B):
+    torch.manual_seed(0)
+    D, Ls, p = 128, 640, 0.3
+    ranks = [Rank(r, G, B + G, D, 1024) for r in range(G)]
+    x_ptrs = cu().ptr_array([k.X.data_ptr() for k in ranks])
+    f_ptrs = cu().ptr_array([k.flags.data_ptr() for k in ranks])
+    d_ptrs = cu().ptr_array([k.dXp.data_ptr() for k in ranks])
+    embs, want_rows = [], []
+    for k in ranks:
+        s, e = batch_row_range(B, G, k.r)
+        emb = torch.randn(e - s, D, device=dev())
+        embs.append(emb)
+        want_rows.append(ref.dropout_cast_fwd(emb, p, k.rng.seed, 5, torch.float16))
+        cu().ag_push(emb, p, k.rng, 5, x_ptrs, s, f_ptrs, F_AG, k.r, G, k.step, k.counters)
+    X_want = torch.cat(want_rows)
+    for k in ranks:
+        torch.testing.assert_close(k.X[:B], X_want, rtol=0, atol=0)
+        assert k.flags[F_AG:F_AG + G].tolist() == [1] * G
+    # every rank owns a label shard; the logits GEMM waits on the all-gather flags (already raised)
+    Ws = [(torch.randn(Ls, D, device=dev()) * 0.05).half() for _ in ranks]
+    hp = HyperParams(dev(), init_scale=8.0)
+    ldG = (B + 7) // 8 * 8
+    n0 = torch.zeros(1, dtype=torch.int32, device=dev())
+    empty = torch.zeros(1, dtype=torch.int32, device=dev())
+    partial_want = []
+    for k, W in zip(ranks, Ws):
+        Gt = torch.zeros(Ls, ldG, dtype=torch.float16, device=dev())
+        cu().xfc_logits_grad(W, k.X[:B], Gt, ldG, empty, empty, n0, 0, wait=(k.flags[F_AG:], G, k.step))
+        Gr, _ = ref.xfc_logit_grad(X_want, W, empty[:0], empty[:0])
+        torch.testing.assert_close(Gt[:, :B].float(), Gr.float(), rtol=2e-3, atol=2e-3)
+        cu().xfc_dx(Gt, ldG, W, B, k.dXp[:B], hp.buf, 3, signal=(k.counters[32:], f_ptrs, G, F_RS + k.r, k.step))
+        partial_want.append(ref.xfc_dx(Gr, W, 8.0))
+    cu().check_status()
+    total = sum(partial_want)
+    for k in ranks:
+        assert k.flags[F_RS:F_RS + G].tolist() == [1] * G
+        s, e = batch_row_range(B, G, k.r)
+        de = torch.empty(e - s, D, device=dev())
+        cu().rs_pull(d_ptrs, G, s, e - s, D, de, k.flags[F_RS:], k.step, p, k.rng, 5)
+        want = ref.dropout_bwd(total[s:e], p, k.rng.seed, 5)
+        torch.testing.assert_close(de, want, rtol=2e-3, atol=8.0 * 2e-3)
+    cu().check_status()
+
+
+def test_grad_allreduce_emulated_and_found_inf():
+    G, n = 4, 8 * 1000 + 8 * 3
+    torch.manual_seed(1)
+    ranks = [Rank(r, G, 8, 8, n) for r in range(G)]
+    for k in ranks:
+        k.grad.copy_((torch.randn(n, device=dev()) * 3).bfloat16())
+    want = sum(k.grad.float() for k in ranks)
+    g_ptrs = cu().ptr_array([k.grad.data_ptr() for k in ranks])
+    f_ptrs = cu().ptr_array([k.flags.data_ptr() for k in ranks])
+    hps = [HyperParams(dev()) for _ in ranks]
+    for rnd in range(2):
+        if rnd == 1:
+            for k in ranks:
+                k.step += 1
+                k.grad.copy_((torch.randn(n, device=dev()) * 3).bfloat16())
+            ranks[2].grad[n - 5] = float("inf")      # lands in the last rank's slice
+            want = sum(k.grad.float() for k in ranks)
+        for k in ranks:
+            cu().signal(f_ptrs, G, F_ARA, k.r, k.step)
+        for k in ranks:
+            cu().grad_allreduce(torch.bfloat16, g_ptrs, 0, n, G, k.r, k.flags[F_ARA:], f_ptrs, F_ARB, F_FOUND, k.step,
+                                1, 0, k.counters[48:], 7)
+        for k, hp in zip(ranks, hps):
+            cu().wait_flags(k.flags[F_ARB:], G, k.step, 1, 0, k.flags[F_FOUND:], hp.buf)
+        cu().check_status()
+        for k, hp in zip(ranks, hps):
+            got = k.grad.float()
+            fin = torch.isfinite(want)
+            torch.testing.assert_close(got[fin], want[fin], rtol=1e-2, atol=5e-2)
+            assert float(hp.buf[HP.FOUND_INF]) == float(rnd)
+            assert k.flags[F_FOUND:F_FOUND + G].abs().sum().item() == 0      # words cleared for the next step
+            assert k.flags[F_ARB:F_ARB + G].tolist() == [rnd + 1] * G
+
+
+def test_bounded_wait_times_out_with_status_and_context_survives():
+    """A flag that nothing sets: the pull kernel gives up after its time budget, writes a status
+    word, produces zeros, and later launches on the same context still work."""
+    G, b, D = 2, 4, 64
+    k = Rank(0, G, 8, D, 8)
+    k.step.fill_(5)
+    k.flags[F_RS] = 5                     # rank 0's flag is there, rank 1's never arrives
+    d_ptrs = cu().ptr_array([k.dXp.data_ptr(), k.dXp.data_ptr()])
+    de = torch.full((b, D), 3.0, device=dev())
+    cu().rs_pull(d_ptrs, G, 0, b, D, de, k.flags[F_RS:], k.step, 0.0, k.rng, 5)
+    torch.cuda.synchronize()
+    with pytest.raises(cu().KernelError, match="timed out"):
+        cu().check_status()
+    assert float(de.abs().max()) == 0.0
+    cu().check_status()                   # status was cleared by the failed check
+    x = torch.ones(16, device=dev())
+    assert float((x * 2).sum()) == 32.0   # the context is still usable

@@ -1,0 +1,71 @@
+"""Real multi-GPU check (needs >= 2 devices): the peer-memory collectives fused into the kernels give
+the same training trajectory as the NCCL library collectives, eagerly and from CUDA graphs."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import numpy as np
+    from renee_b200.data import xcrepo
+    from renee_b200.data.collate import XCCollator
+    from renee_b200.data.synthetic import SyntheticSpec, SyntheticXC
+    from renee_b200.models.encoder import EncoderConfig
+    from renee_b200.ops import cuda as cu
+    from renee_b200.parallel.dist import init_distributed, shutdown
+    from renee_b200.parallel.fused import PeerCollectives
+    from renee_b200.train import TrainConfig, XCTrainer
+    from renee_b200.utils.sharding import shard_labels
+
+    ctx = init_distributed(rank, world, rank, timeout_s=120)
+    enc = EncoderConfig(dim=256, n_layers=2, n_heads=4, hidden_dim=1024)
+    L, B, S = 4096, 64, 16
+    spec = SyntheticSpec(num_labels=L, seq_len=S, len_lo=4, len_hi=S, poisson_lam=2.0, seed=0)
+    ids, mask, lab = SyntheticXC(spec).rows(np.arange(B * 4))
+    ds = xcrepo.InMemoryDataset(ids, mask, lab)
+    sh = shard_labels(L, world)
+    coll = XCCollator(sh, ds, rank, 1, B, True)
+    batches = [coll(np.arange(i * B, (i + 1) * B)) for i in range(4)]
+    results = {}
+    for name, fused, graph in (("nccl", False, False), ("peer", True, False), ("peer_graph", True, True)):
+        cfg = TrainConfig(batch_size=B // world, epochs=1, seed=0, dropout=0.5, lr1=0.05, lr2=1e-4, warmup=2, wd1=1e-4,
+                          noloss=True, fp16xfc=True, maxlen=S, pooling="cls", cuda_graph=graph)
+        comm = PeerCollectives(ctx) if fused else None
+        tr = XCTrainer(cfg, enc, sh, ctx, steps_per_epoch=100, comm=comm)
+        for i in range(8):
+            tr.train_step(batches[i % 4])
+        torch.cuda.synchronize()
+        cu.check_status()
+        if graph:
+            assert tr.graph_active()
+        results[name] = {k: v.cpu() for k, v in tr.state_dict().items()}
+        torch.distributed.barrier()
+    torch.save(results, os.path.join(out_dir, f"r{rank}.pt"))
+    shutdown()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_peer_collectives_match_nccl(tmp_path):
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        res = torch.load(os.path.join(str(tmp_path), f"r{r}.pt"), weights_only=False)
+        for name in ("peer", "peer_graph"):
+            for k, v in res["nccl"].items():
+                torch.testing.assert_close(res[name][k], v, rtol=2e-2, atol=2e-3, msg=lambda m: f"{name}/{k}: {m}")
