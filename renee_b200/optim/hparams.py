@@ -46,12 +46,20 @@ class HyperParams:
         scale = float(init_scale) if enabled else 1.0
         self.buf[HP.SCALE] = scale
         self.buf[HP.INV_SCALE] = 1.0 / scale
-        self.host = torch.zeros(HP.HOST_SLOTS, dtype=torch.float32)
+        # The host block is copied asynchronously; the CPU may already be preparing a later step when
+        # the copy engine reads it, so each step gets its own pinned slot from a ring.
+        self._ring = torch.zeros(self.RING, HP.HOST_SLOTS, dtype=torch.float32)
         if self.device.type == "cuda":
-            self.host = self.host.pin_memory()
+            self._ring = self._ring.pin_memory()
+        self._slot = 0
+        self.host = self._ring[0]
 
     # -- host-written part -------------------------------------------------------------------
+    RING = 512
+
     def set_step(self, lr_xfc: float, lr_enc: float, seed: int) -> None:
+        self._slot = (self._slot + 1) % self.RING
+        self.host = self._ring[self._slot]
         self.host[HP.LR_XFC] = lr_xfc
         self.host[HP.LR_ENC] = lr_enc
         self.host.view(torch.int32)[HP.SEED] = int(seed) - (1 << 32) if int(seed) >= (1 << 31) else int(seed)
