@@ -10,6 +10,7 @@
 // 16-byte accesses; column reductions (dgamma, dbeta, dbias) are accumulated in registers across the
 // rows of a warp, combined per block in shared memory, added to an fp32 accumulator in global memory
 // and converted by the last block to finish, which also re-zeroes the accumulator for the next call.
+#include <cstdio>
 #include "common.cuh"
 
 namespace rb {
@@ -636,6 +637,58 @@ RB_API int rb_dropout_cast_fwd(int out_dtype, const float* x, void* out, long lo
   int blocks = (int)((n + 255) / 256);
   if (blocks > 148 * 8) blocks = 148 * 8;
   DISPATCH_T(out_dtype, (dropout_kernel<float, T><<<blocks, 256, 0, st>>>(x, (T*)out, (size_t)n, p, seed, stream_id)));
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------ allocation-free column sum
+// rb_colsum_noalloc: the column sum above for callers that must not allocate device memory (declared
+// and documented in renee_b200_noalloc.h).  Its fp32 accumulator replicas and its block counter live in
+// the two file-scope device arrays below instead of in a caller-provided workspace.  In host code these
+// names are only host-side handles of the symbols, so their device addresses are looked up once per
+// device with cudaGetSymbolAddress and those addresses are what the kernel receives.
+constexpr int kNoAllocMaxCols = 8192;
+static __device__ __align__(256) float g_colsum_scratch[rb::kCopies * kNoAllocMaxCols];
+static __device__ __align__(256) unsigned g_colsum_counter[64];
+
+namespace {
+struct NoAllocSlot { bool ready; float* scratch; unsigned* counter; };
+NoAllocSlot g_noalloc_slots[64];
+}  // namespace
+
+RB_API int rb_colsum_noalloc_max_cols(void) { return kNoAllocMaxCols; }
+
+RB_API int rb_colsum_noalloc(int dtype, const void* x, void* out, int rows, int N, cudaStream_t st) {
+  if (rows < 1 || N < 8 || N % 8) {
+    fprintf(stderr, "rb_colsum_noalloc: rows must be >= 1 and N a positive multiple of 8 (got rows=%d, N=%d)\n", rows, N);
+    return -3;
+  }
+  if (N > kNoAllocMaxCols) {
+    fprintf(stderr, "rb_colsum_noalloc: N=%d exceeds the built-in scratch (at most %d columns)\n", N, kNoAllocMaxCols);
+    return -10;
+  }
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return -11;
+  NoAllocSlot& slot = g_noalloc_slots[device];
+  if (!slot.ready) {
+    // first call on this device (keep it outside any stream capture): resolve the device addresses
+    void* s = nullptr;
+    void* c = nullptr;
+    if (cudaGetSymbolAddress(&s, g_colsum_scratch) != cudaSuccess) return -12;
+    if (cudaGetSymbolAddress(&c, g_colsum_counter) != cudaSuccess) return -12;
+    slot.scratch = static_cast<float*>(s);
+    slot.counter = static_cast<unsigned*>(c);
+    slot.ready = true;
+  }
+  // the arrays keep whatever the previous call (or an interrupted one) left: start from zero
+  if (cudaMemsetAsync(slot.scratch, 0, sizeof(float) * rb::kCopies * (size_t)N, st) != cudaSuccess) return -13;
+  if (cudaMemsetAsync(slot.counter, 0, sizeof(unsigned), st) != cudaSuccess) return -13;
+  const int cb = (N / 8 + 127) / 128;
+  int rc = 148 * 12 / cb;
+  if (rc > (rows + 3) / 4) rc = (rows + 3) / 4;
+  if (rc < 1) rc = 1;
+  dim3 grid(cb, rc);
+  DISPATCH_T(dtype, (colsum_kernel<T><<<grid, 128, 0, st>>>((const T*)x, slot.scratch, slot.counter, (T*)out, rows, N)));
   RB_LAUNCH_CHECK();
   return 0;
 }
