@@ -66,6 +66,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--no-fused-comm", dest="fused_comm", action="store_false", default=True)
     p.add_argument("--stochastic-round", action="store_true", default=False)
     p.add_argument("--cpu", action="store_true", default=False, help="force CPU (gloo) execution")
+    p.add_argument("--heartbeat-timeout", type=float, default=60.0,
+                   help="seconds without a peer heartbeat before a step is refused (0 disables the watchdog)")
     p.add_argument("--results-dir", type=str, default="./Results/Bert-XC/")
     return p
 
@@ -145,6 +147,11 @@ def start(local_device: int, ngpus_per_node: int, args) -> None:
         from .parallel.fused import PeerCollectives
         comm = PeerCollectives(ctx)
     trainer = XCTrainer(cfg, enc_cfg, sharding, ctx, steps_per_epoch=len(trn_loader), comm=comm)
+    if G > 1 and args.heartbeat_timeout > 0:
+        import torch.distributed as dist
+        from .parallel.watchdog import Heartbeat
+        store = dist.distributed_c10d._get_default_store()
+        trainer.watchdog = Heartbeat(store, rank, G, interval=1.0, timeout=args.heartbeat_timeout).start()
 
     init_sd = None
     if args.use_ngame_encoder:

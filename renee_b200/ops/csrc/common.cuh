@@ -63,6 +63,32 @@ __device__ __forceinline__ void store8(T* __restrict__ p, const float (&in)[8]) 
   }
 }
 
+// 8 elements kept in their storage format (4 registers for 16-bit types) and expanded on demand:
+// lets a kernel hold several vectors across a reduction without paying 8 registers per vector.
+template <typename T> struct Raw8 { uint4 v; };
+template <> struct Raw8<float> { float4 a, b; };
+
+template <typename T> __device__ __forceinline__ Raw8<T> load_raw8(const T* __restrict__ p) {
+  Raw8<T> r;
+  r.v = *reinterpret_cast<const uint4*>(p);
+  return r;
+}
+template <> __device__ __forceinline__ Raw8<float> load_raw8<float>(const float* __restrict__ p) {
+  Raw8<float> r;
+  r.a = *reinterpret_cast<const float4*>(p);
+  r.b = *reinterpret_cast<const float4*>(p + 4);
+  return r;
+}
+template <typename T> __device__ __forceinline__ void unpack8(const Raw8<T>& r, float (&out)[8]) {
+  const T* e = reinterpret_cast<const T*>(&r.v);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) out[i] = to_f(e[i]);
+}
+template <> __device__ __forceinline__ void unpack8<float>(const Raw8<float>& r, float (&out)[8]) {
+  out[0] = r.a.x; out[1] = r.a.y; out[2] = r.a.z; out[3] = r.a.w;
+  out[4] = r.b.x; out[5] = r.b.y; out[6] = r.b.z; out[7] = r.b.w;
+}
+
 // Rounds through T (what a store followed by a load would give)
 template <typename T> __device__ __forceinline__ float round_through(float x) { return to_f(from_f<T>(x)); }
 
@@ -75,6 +101,33 @@ __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
+}
+
+// One 16-byte reduction instead of four 4-byte ones (p must be 16-byte aligned)
+__device__ __forceinline__ void red_add_f32x4(float* p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// erf by a rational minimax approximation on [-4, 4] (|error| < 4e-7, i.e. fp32 round-off): one
+// reciprocal and 13 FMAs, about half the instructions of erff, which matters because the GELU kernels
+// are otherwise bound by the math pipes rather than by HBM.
+__device__ __forceinline__ float fast_erf(float x) {
+  x = fminf(fmaxf(x, -4.f), 4.f);
+  const float x2 = x * x;
+  float p = -2.72614225801306e-10f;
+  p = fmaf(p, x2, 2.77068142495902e-08f);
+  p = fmaf(p, x2, -2.10102402082508e-06f);
+  p = fmaf(p, x2, -5.69250639462346e-05f);
+  p = fmaf(p, x2, -7.34990630326855e-04f);
+  p = fmaf(p, x2, -2.95459980854025e-03f);
+  p = fmaf(p, x2, -1.60960333262415e-02f);
+  p *= x;
+  float q = -1.45660718464996e-05f;
+  q = fmaf(q, x2, -2.13374055278905e-04f);
+  q = fmaf(q, x2, -1.68282697438203e-03f);
+  q = fmaf(q, x2, -7.37332916720468e-03f);
+  q = fmaf(q, x2, -1.42647390514189e-02f);
+  return __fdividef(p, q);
 }
 
 // Counter-based dropout RNG; must stay bit-identical to renee_b200/ops/rng.py::mix32

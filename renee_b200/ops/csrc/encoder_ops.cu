@@ -206,8 +206,18 @@ __global__ void __launch_bounds__(128) embed_ln_fwd_kernel(
 // EMBED = true : inputs dy (dropout re-applied to it), ids/word/pos to rebuild the LN input; outputs
 //                dgamma, dbeta and gradients scattered into dword (atomic, pad id skipped) and dpos.
 //                The launch makes the total warp count a multiple of S so a warp sees one position.
+// Column sums are accumulated per warp in shared memory (a lane only touches its own columns, so no
+// atomics are needed there), which keeps the register count low enough for 4+ CTAs per SM.
+__device__ __forceinline__ void smem_add8(float* p, const float (&v)[8]) {
+  float4 a = *reinterpret_cast<float4*>(p), b = *reinterpret_cast<float4*>(p + 4);
+  a.x += v[0]; a.y += v[1]; a.z += v[2]; a.w += v[3];
+  b.x += v[4]; b.y += v[5]; b.z += v[6]; b.w += v[7];
+  *reinterpret_cast<float4*>(p) = a;
+  *reinterpret_cast<float4*>(p + 4) = b;
+}
+
 template <typename T, int NV, bool EMBED>
-__global__ void __launch_bounds__(128) ln_bwd_kernel(
+__global__ void __launch_bounds__(128, 6) ln_bwd_kernel(
     const T* __restrict__ dy, const T* __restrict__ pre, const int* __restrict__ ids,
     const T* __restrict__ word, const T* __restrict__ pos, const T* __restrict__ gamma,
     const float* __restrict__ mean, const float* __restrict__ rstd,
@@ -215,27 +225,30 @@ __global__ void __launch_bounds__(128) ln_bwd_kernel(
     float* __restrict__ acc, unsigned* __restrict__ counter, T* __restrict__ dgamma, T* __restrict__ dbeta,
     T* __restrict__ dbias, int rows, int H, int S, int pad_id, float p, const int* __restrict__ seed_ptr,
     uint32_t stream) {
-  extern __shared__ float sm[];  // [3][H]
+  extern __shared__ __align__(16) float sm[];  // [warps][3][H]
   const int lane = threadIdx.x & 31;
+  const int wib = threadIdx.x >> 5;
   const int wpb = blockDim.x >> 5;
-  const int warp = blockIdx.x * wpb + (threadIdx.x >> 5);
+  const int warp = blockIdx.x * wpb + wib;
   const int total_warps = gridDim.x * wpb;
   const uint32_t seed = p > 0.f ? (uint32_t)(*seed_ptr) : 0u;
   const float inv_keep = p > 0.f ? 1.f / (1.f - p) : 1.f;
-  for (int i = threadIdx.x; i < 3 * H; i += blockDim.x) sm[i] = 0.f;
+  for (int i = threadIdx.x; i < wpb * 3 * H; i += blockDim.x) sm[i] = 0.f;
   __syncthreads();
+  float* s_dg = sm + (size_t)wib * 3 * H;
+  float* s_db = s_dg + H;
+  float* s_x = s_db + H;    // dbias (resid mode) or position-embedding gradient (embed mode)
 
-  float gam[NV][8], a_dg[NV][8], a_db[NV][8], a_bias[NV][8];
+  Raw8<T> gam[NV];
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int col = (lane + 32 * i) * 8;
-    if (col < H) load8(gamma + col, gam[i]);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { a_dg[i][j] = 0.f; a_db[i][j] = 0.f; a_bias[i][j] = 0.f; }
+    if (col < H) gam[i] = load_raw8<T>(gamma + col);
   }
   for (int row = warp; row < rows; row += total_warps) {
     const float mu = mean[row], rs = rstd[row];
-    float xh[NV][8], g[NV][8];
+    // dy and the LN input stay packed across the two warp reductions
+    Raw8<T> rd[NV], rx[NV], rb[NV];
     float s1 = 0.f, s2 = 0.f;
     int id = 0;
     if (EMBED) id = ids[row];
@@ -243,29 +256,42 @@ __global__ void __launch_bounds__(128) ln_bwd_kernel(
     for (int i = 0; i < NV; ++i) {
       const int col = (lane + 32 * i) * 8;
       if (col < H) {
-        float d[8], x[8];
-        load8(dy + (size_t)row * H + col, d);
+        rd[i] = load_raw8<T>(dy + (size_t)row * H + col);
+        if (EMBED) {
+          rx[i] = load_raw8<T>(word + (size_t)id * H + col);
+          rb[i] = load_raw8<T>(pos + (size_t)(row % S) * H + col);
+        } else {
+          rx[i] = load_raw8<T>(pre + (size_t)row * H + col);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int col = (lane + 32 * i) * 8;
+      if (col < H) {
+        float d[8], x[8], gm[8], dgv[8];
+        unpack8<T>(rd[i], d);
+        unpack8<T>(rx[i], x);
+        unpack8<T>(gam[i], gm);
         if (EMBED) {
           float b[8];
-          load8(word + (size_t)id * H + col, x);
-          load8(pos + (size_t)(row % S) * H + col, b);
+          unpack8<T>(rb[i], b);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             x[j] += b[j];
             if (p > 0.f) d[j] = keep(seed, stream, (uint32_t)(row * H + col + j), p) ? d[j] * inv_keep : 0.f;
           }
-        } else {
-          load8(pre + (size_t)row * H + col, x);
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          xh[i][j] = (x[j] - mu) * rs;
-          g[i][j] = d[j] * gam[i][j];
-          s1 += g[i][j];
-          s2 += g[i][j] * xh[i][j];
-          a_dg[i][j] += d[j] * xh[i][j];
-          a_db[i][j] += d[j];
+          const float xh = (x[j] - mu) * rs;
+          const float g = d[j] * gm[j];
+          s1 += g;
+          s2 += g * xh;
+          dgv[j] = d[j] * xh;
         }
+        smem_add8(s_dg + col, dgv);
+        smem_add8(s_db + col, d);
       }
     }
     s1 = warp_sum(s1) / H;
@@ -274,62 +300,76 @@ __global__ void __launch_bounds__(128) ln_bwd_kernel(
     for (int i = 0; i < NV; ++i) {
       const int col = (lane + 32 * i) * 8;
       if (col < H) {
-        float dx[8];
+        float d[8], x[8], gm[8], dx[8];
+        unpack8<T>(rd[i], d);
+        unpack8<T>(rx[i], x);
+        unpack8<T>(gam[i], gm);
+        if (EMBED) {
+          float b[8];
+          unpack8<T>(rb[i], b);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) dx[j] = (g[i][j] - s1 - xh[i][j] * s2) * rs;
+          for (int j = 0; j < 8; ++j) {
+            x[j] += b[j];
+            if (p > 0.f) d[j] = keep(seed, stream, (uint32_t)(row * H + col + j), p) ? d[j] * inv_keep : 0.f;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xh = (x[j] - mu) * rs;
+          dx[j] = (d[j] * gm[j] - s1 - xh * s2) * rs;
+        }
         if (EMBED) {
           if (id != pad_id) atomic_add8(dword + (size_t)id * H + col, dx);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) a_bias[i][j] += dx[j];   // position-embedding gradient of this warp's position
+          smem_add8(s_x + col, dx);
         } else {
           store8(d_pre + (size_t)row * H + col, dx);
+          float db[8];
           if (p > 0.f) {
-            float db[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              db[j] = keep(seed, stream, (uint32_t)(row * H + col + j), p) ? dx[j] * inv_keep : 0.f;
-              a_bias[i][j] += round_through<T>(db[j]);
-            }
+            for (int j = 0; j < 8; ++j)
+              db[j] = round_through<T>(keep(seed, stream, (uint32_t)(row * H + col + j), p) ? dx[j] * inv_keep : 0.f);
             store8(d_branch + (size_t)row * H + col, db);
           } else {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) a_bias[i][j] += round_through<T>(dx[j]);
+            for (int j = 0; j < 8; ++j) db[j] = round_through<T>(dx[j]);
           }
+          smem_add8(s_x + col, db);
         }
       }
     }
   }
+  __syncwarp();
   if (EMBED && warp < rows) {
     const int s = warp % S;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int col = (lane + 32 * i) * 8;
-      if (col < H) atomic_add8(dpos + (size_t)s * H + col, a_bias[i]);
-    }
-  }
+      if (col < H) {
+        float v[8];
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int col = (lane + 32 * i) * 8;
-    if (col < H) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        atomicAdd(&sm[col + j], a_dg[i][j]);
-        atomicAdd(&sm[H + col + j], a_db[i][j]);
-        if (!EMBED) atomicAdd(&sm[2 * H + col + j], a_bias[i][j]);
+        for (int j = 0; j < 8; ++j) v[j] = s_x[col + j];
+        atomic_add8(dpos + (size_t)s * H + col, v);
       }
     }
   }
   __syncthreads();
   const int nvec = EMBED ? 2 : 3;
   float* my_acc = acc_replica(acc, nvec, H);
-  for (int i = threadIdx.x; i < nvec * H; i += blockDim.x) atomicAdd(my_acc + i, sm[i]);
+  for (int i = threadIdx.x * 4; i < nvec * H; i += blockDim.x * 4) {
+    float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int w = 0; w < wpb; ++w) {
+      const float4 v = *reinterpret_cast<const float4*>(sm + (size_t)w * 3 * H + i);
+      t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
+    }
+    red_add_f32x4(my_acc + i, t.x, t.y, t.z, t.w);
+  }
   finalize_columns<T>(acc, counter, nvec, H, dgamma, dbeta, EMBED ? nullptr : dbias);
 }
 
 // ------------------------------------------------------------------------------------ GELU
-__device__ __forceinline__ float gelu_f(float z) { return 0.5f * z * (1.f + erff(z * 0.70710678118654752f)); }
+__device__ __forceinline__ float gelu_f(float z) { return 0.5f * z * (1.f + fast_erf(z * 0.70710678118654752f)); }
 __device__ __forceinline__ float gelu_grad_f(float z) {
-  const float cdf = 0.5f * (1.f + erff(z * 0.70710678118654752f));
+  const float cdf = 0.5f * (1.f + fast_erf(z * 0.70710678118654752f));
   const float pdf = 0.39894228040143268f * __expf(-0.5f * z * z);
   return cdf + z * pdf;
 }
@@ -369,15 +409,15 @@ __global__ void __launch_bounds__(128) bias_gelu_bwd_kernel(const T* __restrict_
   for (int j = 0; j < 8; ++j) s[j] = 0.f;
   if (col < F) {
     load8(bias + col, b);
-    for (int r = blockIdx.y; r < rows; r += 4 * gridDim.y) {
-      float a[4][8], g[4][8];
+    for (int r = blockIdx.y; r < rows; r += 2 * gridDim.y) {
+      float a[2][8], g[2][8];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < 2; ++u) {
         const int rr = r + u * gridDim.y;
         if (rr < rows) { load8(x + (size_t)rr * F + col, a[u]); load8(da + (size_t)rr * F + col, g[u]); }
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < 2; ++u) {
         const int rr = r + u * gridDim.y;
         if (rr < rows) {
 #pragma unroll
@@ -390,8 +430,8 @@ __global__ void __launch_bounds__(128) bias_gelu_bwd_kernel(const T* __restrict_
       }
     }
     float* my_acc = acc_replica(acc, 1, F);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) atomicAdd(my_acc + col + j, s[j]);
+    red_add_f32x4(my_acc + col, s[0], s[1], s[2], s[3]);
+    red_add_f32x4(my_acc + col + 4, s[4], s[5], s[6], s[7]);
   }
   finalize_columns<T>(acc, counter, 1, F, dbias, nullptr, nullptr);
 }
@@ -418,8 +458,8 @@ __global__ void __launch_bounds__(128) colsum_kernel(const T* __restrict__ x, fl
         }
     }
     float* my_acc = acc_replica(acc, 1, N);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) atomicAdd(my_acc + col + j, s[j]);
+    red_add_f32x4(my_acc + col, s[0], s[1], s[2], s[3]);
+    red_add_f32x4(my_acc + col + 4, s[4], s[5], s[6], s[7]);
   }
   finalize_columns<T>(acc, counter, 1, N, out, nullptr, nullptr);
 }
@@ -540,7 +580,7 @@ RB_API int rb_embed_ln_fwd(int dtype, const int* ids, const void* word, const vo
 
 static int ln_bwd_blocks(int rows, int S, bool embed) {
   int blocks = (rows + 3) / 4;
-  if (blocks > 592) blocks = 592;
+  if (blocks > 148 * 4) blocks = 148 * 4;
   if (embed) {  // total warps (4 per block) must be a multiple of S: round blocks to a multiple of S
     blocks = (blocks / S) * S;
     if (blocks == 0) blocks = S;
@@ -554,8 +594,9 @@ RB_API int rb_bias_dropout_add_ln_bwd(int dtype, const void* dy, const void* pre
                                       unsigned stream_id, cudaStream_t st) {
   if (H % 8) return -3;
   const int blocks = ln_bwd_blocks(rows, 1, false);
-  const size_t smem = 3 * (size_t)H * sizeof(float);
-  DISPATCH_T(dtype, DISPATCH_NV(H, (ln_bwd_kernel<T, NV, false><<<blocks, 128, smem, st>>>(
+  const size_t smem = 4 * 3 * (size_t)H * sizeof(float);
+  DISPATCH_T(dtype, DISPATCH_NV(H, (cudaFuncSetAttribute(ln_bwd_kernel<T, NV, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                                    ln_bwd_kernel<T, NV, false><<<blocks, 128, smem, st>>>(
       (const T*)dy, (const T*)pre, nullptr, nullptr, nullptr, (const T*)gamma, mean, rstd, (T*)d_pre, (T*)d_branch,
       nullptr, nullptr, acc, counter, (T*)dgamma, (T*)dbeta, (T*)dbias, rows, H, 1, 0, p, seed, stream_id))));
   RB_LAUNCH_CHECK();
@@ -568,8 +609,9 @@ RB_API int rb_embed_ln_bwd(int dtype, const void* dy, const int* ids, const void
                            float p, const int* seed, unsigned stream_id, cudaStream_t st) {
   if (H % 8) return -3;
   const int blocks = ln_bwd_blocks(rows, S, true);
-  const size_t smem = 3 * (size_t)H * sizeof(float);
-  DISPATCH_T(dtype, DISPATCH_NV(H, (ln_bwd_kernel<T, NV, true><<<blocks, 128, smem, st>>>(
+  const size_t smem = 4 * 3 * (size_t)H * sizeof(float);
+  DISPATCH_T(dtype, DISPATCH_NV(H, (cudaFuncSetAttribute(ln_bwd_kernel<T, NV, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                                    ln_bwd_kernel<T, NV, true><<<blocks, 128, smem, st>>>(
       (const T*)dy, nullptr, ids, (const T*)word, (const T*)pos, (const T*)gamma, mean, rstd, nullptr, nullptr,
       (T*)dword, (T*)dpos, acc, counter, (T*)dgamma, (T*)dbeta, nullptr, rows, H, S, pad_id, p, seed, stream_id))));
   RB_LAUNCH_CHECK();
@@ -579,7 +621,7 @@ RB_API int rb_embed_ln_bwd(int dtype, const void* dy, const int* ids, const void
 RB_API int rb_bias_gelu_fwd(int dtype, const void* x, const void* bias, void* out, int rows, int F, cudaStream_t st) {
   if (F % 8) return -3;
   const int cb = (F / 8 + 127) / 128;
-  int rc = 148 * 12 / cb;
+  int rc = 148 * 5 / cb;
   if (rc > (rows + 3) / 4) rc = (rows + 3) / 4;
   if (rc < 1) rc = 1;
   dim3 grid(cb, rc);
@@ -592,7 +634,7 @@ RB_API int rb_bias_gelu_bwd(int dtype, const void* da, const void* x, const void
                             unsigned* counter, void* dbias, int rows, int F, cudaStream_t st) {
   if (F % 8) return -3;
   const int cb = (F / 8 + 127) / 128;
-  int rc = 148 * 12 / cb;
+  int rc = 148 * 5 / cb;
   if (rc > (rows + 3) / 4) rc = (rows + 3) / 4;
   if (rc < 1) rc = 1;
   dim3 grid(cb, rc);
@@ -606,7 +648,7 @@ RB_API int rb_colsum(int dtype, const void* x, float* acc, unsigned* counter, vo
                      cudaStream_t st) {
   if (N % 8) return -3;
   const int cb = (N / 8 + 127) / 128;
-  int rc = 148 * 12 / cb;
+  int rc = 148 * 5 / cb;
   if (rc > (rows + 3) / 4) rc = (rows + 3) / 4;
   if (rc < 1) rc = 1;
   dim3 grid(cb, rc);
@@ -684,7 +726,7 @@ RB_API int rb_colsum_noalloc(int dtype, const void* x, void* out, int rows, int 
   if (cudaMemsetAsync(slot.scratch, 0, sizeof(float) * rb::kCopies * (size_t)N, st) != cudaSuccess) return -13;
   if (cudaMemsetAsync(slot.counter, 0, sizeof(unsigned), st) != cudaSuccess) return -13;
   const int cb = (N / 8 + 127) / 128;
-  int rc = 148 * 12 / cb;
+  int rc = 148 * 5 / cb;
   if (rc > (rows + 3) / 4) rc = (rows + 3) / 4;
   if (rc < 1) rc = 1;
   dim3 grid(cb, rc);

@@ -282,6 +282,146 @@ xfc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   }
 }
 
+// ------------------------------------------------------------------------------------ dW + SGD, W/M tiles staged by TMA
+// Same math as xfc_gemm_kernel<MODE_DW>, restructured because the kernel is bound by the W / momentum
+// traffic, not by the MMA: the producer warp first issues TMA loads of this CTA's [128 x <=256] tiles of W
+// and M into shared memory (they arrive while the short K loop over the batch runs), the epilogue updates
+// them in place from the TMEM accumulator (16-byte accesses on the 128-byte-swizzled panels, conflict
+// free), and one thread writes both tiles back with TMA stores.  Every global access is a full-line
+// bulk copy instead of 16-byte pieces at a 1.5 KB stride.
+constexpr int kDwStages = 2;
+constexpr int kPanelBytes = kBM * 64 * 2;                        // 128 rows x 64 fp16 = 16 KB
+constexpr int kDwTileBytes = 4 * kPanelBytes;                     // 64 KB per tensor
+constexpr int kDwSmemBytes = kDwStages * kStageBytes + 2 * kDwTileBytes + 1024 + 128;
+
+__global__ void __launch_bounds__(kThreads, 1)
+xfc_dw_sgd_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmM,
+                      const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sW = smem + kDwStages * kStageBytes;
+  uint8_t* sM = sW + kDwTileBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sM + kDwTileBytes);
+  uint64_t* empty_bar = full_bar + kDwStages;
+  uint64_t* tmem_full_bar = empty_bar + kDwStages;
+  uint64_t* wm_full_bar = tmem_full_bar + 1;
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(wm_full_bar + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * kBM;
+  const int n0 = blockIdx.y * p.BN;
+  const int panels = p.BN / 64;
+  const uint32_t b_bytes = (uint32_t)p.BN * kBK * 2;
+
+  if (threadIdx.x == 0) {
+    tc::prefetch_tmap(&tmA); tc::prefetch_tmap(&tmB); tc::prefetch_tmap(&tmW); tc::prefetch_tmap(&tmM);
+    for (int s = 0; s < kDwStages; ++s) { tc::mbar_init(full_bar + s, 1); tc::mbar_init(empty_bar + s, 1); }
+    tc::mbar_init(tmem_full_bar, 1);
+    tc::mbar_init(wm_full_bar, 1);
+    tc::fence_barrier_init();
+  }
+  if (warp == 1) tc::tmem_alloc(tmem_ptr_smem, kTmemCols);
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+  bool aborted = false;
+
+  if (warp == 0 && lane == 0) {
+    tc::mbar_expect_tx(wm_full_bar, (uint32_t)panels * 2 * kPanelBytes);
+    for (int q = 0; q < panels; ++q) {
+      tc::tma_load_2d(sW + q * kPanelBytes, &tmW, wm_full_bar, n0 + 64 * q, m0);
+      tc::tma_load_2d(sM + q * kPanelBytes, &tmM, wm_full_bar, n0 + 64 * q, m0);
+    }
+    for (int kb = 0; kb < p.kb_total; ++kb) {
+      const int s = kb % kDwStages;
+      const uint32_t ph = (kb / kDwStages) & 1;
+      if (!tc::mbar_wait(empty_bar + s, ph ^ 1, aborted, p.status, tc::SITE_EMPTY, kb)) break;
+      uint8_t* sA = smem + s * kStageBytes;
+      uint8_t* sB = sA + kABytes;
+      tc::mbar_expect_tx(full_bar + s, kABytes + b_bytes);
+      tc::tma_load_2d(sA, &tmA, full_bar + s, kb * kBK, m0);
+      for (int i = 0; i < panels; ++i) tc::tma_load_2d(sB + i * 8192, &tmB, full_bar + s, n0 + 64 * i, kb * kBK);
+    }
+  } else if (warp == 1 && lane == 0) {
+    const uint32_t idesc = tc::make_idesc(0, 0, 1, kBM, p.BN);
+    for (int kb = 0; kb < p.kb_total; ++kb) {
+      const int s = kb % kDwStages;
+      const uint32_t ph = (kb / kDwStages) & 1;
+      if (!tc::mbar_wait(full_bar + s, ph, aborted, p.status, tc::SITE_FULL, kb)) break;
+      tc::tc_fence_after();
+      const uint32_t sA = tc::smem_u32(smem + s * kStageBytes);
+      const uint32_t sB = sA + kABytes;
+#pragma unroll
+      for (int k = 0; k < kBK / 16; ++k) {
+        const uint64_t ad = tc::make_smem_desc(sA + k * 32, 16, 1024);
+        const uint64_t bd = tc::make_smem_desc(sB + k * 2048, 8192, 1024);
+        tc::umma_f16(tmem_base, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+      }
+      tc::umma_commit(empty_bar + s);
+    }
+    if (!aborted) tc::umma_commit(tmem_full_bar);
+  } else if (warp >= 2) {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    bool ok = tc::mbar_wait(tmem_full_bar, 0, aborted, p.status, tc::SITE_TMEM_FULL, 0);
+    ok = tc::mbar_wait(wm_full_bar, 0, aborted, p.status, tc::SITE_FULL, 1000) && ok;
+    tc::tc_fence_after();
+    if (ok) {
+      const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      const float lr = p.hp[HP_LR_XFC];
+      for (int c0 = 0; c0 < p.BN; c0 += 32) {
+        float v[32];
+        tc::tmem_ld32(tbase + c0, v);
+        const int panel = c0 >> 6;
+        const int chunk0 = (c0 & 63) >> 3;            // first 16-byte chunk of this 32-column group in the panel row
+#pragma unroll
+        for (int j8 = 0; j8 < 4; ++j8) {
+          const int phys = (chunk0 + j8) ^ (r & 7);   // 128-byte swizzle: chunk index XOR row-in-group
+          const uint32_t off = (uint32_t)panel * kPanelBytes + (uint32_t)r * 128 + (uint32_t)phys * 16;
+          uint4 wr = *reinterpret_cast<const uint4*>(sW + off);
+          uint4 mr = *reinterpret_cast<const uint4*>(sM + off);
+          __half2* w2 = reinterpret_cast<__half2*>(&wr);
+          __half2* m2 = reinterpret_cast<__half2*>(&mr);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float2 w = __half22float2(w2[j]);
+            float2 m = __half22float2(m2[j]);
+            const float g0 = v[8 * j8 + 2 * j] + p.wd * w.x;
+            const float g1 = v[8 * j8 + 2 * j + 1] + p.wd * w.y;
+            m.x = p.mo * m.x + g0;
+            m.y = p.mo * m.y + g1;
+            m2[j] = __floats2half2_rn(m.x, m.y);
+            const float2 ms = __half22float2(m2[j]);
+            w2[j] = __floats2half2_rn(w.x - lr * ms.x, w.y - lr * ms.y);
+          }
+          *reinterpret_cast<uint4*>(sW + off) = wr;
+          *reinterpret_cast<uint4*>(sM + off) = mr;
+        }
+      }
+      tc::fence_proxy_async();     // the tiles were written through the generic proxy; TMA reads them through the async one
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (ok && threadIdx.x == 64) {
+      for (int q = 0; q < panels; ++q) {
+        if (n0 + 64 * q < p.N) {
+          tc::tma_store_2d(&tmW, sW + q * kPanelBytes, n0 + 64 * q, m0);
+          tc::tma_store_2d(&tmM, sM + q * kPanelBytes, n0 + 64 * q, m0);
+        }
+      }
+      tc::tma_store_commit_and_wait_read();
+    }
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc::tc_fence_after();
+    tc::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
 // sum over positives of z = W[label] . X[row]  (only on loss-sampling steps): one warp per positive
 __global__ void xfc_pos_logit_sum_kernel(const __half* __restrict__ W, const __half* __restrict__ X, int D,
                                          const int* __restrict__ pos_rows, const int* __restrict__ pos_labels,
@@ -390,8 +530,9 @@ RB_API int rb_xfc_dx(const void* Gt, int ldG, const void* W, int Lc, int D, int 
 }
 
 // W, Mom [Lc, D] updated in place from dW = Gt X (never stored); lr read from hp[LR_XFC]
+// use_tma_tiles != 0 selects the kernel that stages the W / M tiles through shared memory with TMA.
 RB_API int rb_xfc_dw_sgd(const void* Gt, int ldG, const void* X, int B, void* W, void* Mom, int Lc, int D,
-                         const float* hp, float mo, float wd, int* status, cudaStream_t st) {
+                         const float* hp, float mo, float wd, int use_tma_tiles, int* status, cudaStream_t st) {
   if (D % 8 || ldG % 8 || Lc < 1) return -3;
   const int BN = D >= 256 ? 256 : round_up(D, 64);
   CUtensorMap ta, tb;
@@ -403,8 +544,23 @@ RB_API int rb_xfc_dw_sgd(const void* Gt, int ldG, const void* X, int B, void* W,
   p.M = Lc; p.N = D; p.BN = BN; p.kb_total = (B + kBK - 1) / kBK; p.kb_per_split = p.kb_total; p.status = status;
   p.W = (__half*)W; p.Mom = (__half*)Mom; p.ldW = D; p.hp = hp; p.mo = mo; p.wd = wd;
   dim3 grid((Lc + kBM - 1) / kBM, (D + BN - 1) / BN, 1);
-  rc = launch_gemm<MODE_DW>(ta, tb, p, grid, st);
-  if (rc) return rc;
+  if (use_tma_tiles) {
+    CUtensorMap tw, tm;
+    rc = tc::make_tmap_2d(&tw, W, Lc, D, D, 64, kBM, false);
+    if (rc) return rc;
+    rc = tc::make_tmap_2d(&tm, Mom, Lc, D, D, 64, kBM, false);
+    if (rc) return rc;
+    static bool attr_set = false;
+    if (!attr_set) {
+      if (cudaFuncSetAttribute(xfc_dw_sgd_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDwSmemBytes) != cudaSuccess)
+        return -5;
+      attr_set = true;
+    }
+    xfc_dw_sgd_tma_kernel<<<grid, kThreads, kDwSmemBytes, st>>>(ta, tb, tw, tm, p);
+  } else {
+    rc = launch_gemm<MODE_DW>(ta, tb, p, grid, st);
+    if (rc) return rc;
+  }
   RB_LAUNCH_CHECK();
   return 0;
 }

@@ -118,14 +118,14 @@ def embed_ln_bwd(dy, ids, word, pos, gamma, mean, rstd, S, p, rng, stream, pad_i
 def attention_fwd(qkv, bqkv, mask, nh, p, rng, stream, ctx_out, ws):
     b, S = mask.shape
     H = ctx_out.shape[1]
-    _call("rb_attention_fwd", _I(DT[qkv.dtype]), _p(qkv), _p(bqkv), _p(mask), _p(ctx_out), _p(ws["probs"]), _I(b), _I(S),
+    _call("rb_attention_fwd" if qkv.dtype == torch.float32 else "rb_attention_fwd_tc", _I(DT[qkv.dtype]), _p(qkv), _p(bqkv), _p(mask), _p(ctx_out), _p(ws["probs"]), _I(b), _I(S),
           _I(H), _I(nh), _F(p), _p(rng.dev), _U(stream), _stream())
 
 
 def attention_bwd(dctx, qkv, bqkv, mask, nh, p, rng, stream, ws, dqkv_out, dbqkv_out):
     b, S = mask.shape
     H = dctx.shape[1]
-    _call("rb_attention_bwd", _I(DT[qkv.dtype]), _p(dctx), _p(qkv), _p(bqkv), _p(ws["probs"]), _p(dqkv_out), _I(b),
+    _call("rb_attention_bwd" if qkv.dtype == torch.float32 else "rb_attention_bwd_tc", _I(DT[qkv.dtype]), _p(dctx), _p(qkv), _p(bqkv), _p(ws["probs"]), _p(dqkv_out), _I(b),
           _I(S), _I(H), _I(nh), _F(p), _p(rng.dev), _U(stream), _stream())
     colsum(dqkv_out, dbqkv_out)
 
@@ -229,12 +229,12 @@ def xfc_dx(Gt, ldG, W, B, dX, hp_buf, splits, signal=None):
           ptrs if ptrs is not None else _VP(0), _I(n), _I(idx), _p(step), _p(ws.status), _stream())
 
 
-def xfc_dw_sgd(Gt, ldG, X, W, M, hp_buf, mo, wd):
+def xfc_dw_sgd(Gt, ldG, X, W, M, hp_buf, mo, wd, tma_tiles=True):
     Lc, D = W.shape
     B = X.shape[0]
     ws = workspace(W.device)
     _call("rb_xfc_dw_sgd", _p(Gt), _I(ldG), _p(X), _I(B), _p(W), _p(M), _I(Lc), _I(D), _p(hp_buf), _F(mo), _F(wd),
-          _p(ws.status), _stream())
+          _I(1 if tma_tiles else 0), _p(ws.status), _stream())
 
 
 def dx_splits(B: int, D: int, Lc: int) -> int:

@@ -146,6 +146,7 @@ class XCTrainer:
         self._graphs: dict = {}
         self._graph_warm: dict = {}
         self._pending_loss = None
+        self.watchdog = None        # optional parallel.watchdog.Heartbeat, consulted before each step's launches
         if cfg.default_impl:
             self._init_default()
         else:
@@ -268,6 +269,8 @@ class XCTrainer:
     def train_step(self, batch: XCBatch) -> torch.Tensor | None:
         """Runs one optimized step; returns the sampled loss tensor (device, un-normalised) on
         sampling steps, else ``None``.  No host synchronisation happens here."""
+        if self.watchdog is not None:
+            self.watchdog.check()       # a dead or failed peer is noticed on the host, before any kernel waits for it
         if self.cfg.default_impl:
             return self.default_step(batch)
         self.stage_batch(batch)
@@ -386,6 +389,7 @@ class XCTrainer:
                     self.loss_steps += 1
             if self.device.type == "cuda":
                 torch.cuda.synchronize()
+                self.check_device_status()
             mean_loss = self.loss_sum / self.loss_steps if self.loss_steps else 0.0
             if self.ctx.is_main:
                 log(f"mean loss after epoch {epoch} : {'%.4E' % mean_loss}")
@@ -398,6 +402,18 @@ class XCTrainer:
             if cfg.checkpoint_resume:
                 save_checkpoint(self, cfg.checkpoint_resume, mean_loss)
         self.epoch = cfg.epochs
+
+    def check_device_status(self) -> None:
+        """Raise (and tell the other ranks) if a bounded device-side wait has expired since the last check."""
+        if self.device.type != "cuda":
+            return
+        from .ops import cuda as cu
+        try:
+            cu.check_status(self.device)
+        except cu.KernelError as exc:
+            if self.watchdog is not None:
+                self.watchdog.post_failure(str(exc))
+            raise
 
     def save(self, out_dir: str | None = None) -> str:
         out_dir = out_dir or self.out_dir
