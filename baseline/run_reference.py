@@ -146,6 +146,10 @@ def run_reference(args, c) -> dict | None:
             state["clocks"] = state["sampler"].stop()
 
     dl_base.trange = timed_trange
+    # The reference opens its own tcp:// rendezvous with rank 0 as the store's host.  Under torchrun the
+    # variable below makes every rank connect as a client to a store the launcher is assumed to host on
+    # that port, and the rendezvous never completes — so it is cleared for this process.
+    os.environ.pop("TORCHELASTIC_USE_AGENT_STORE", None)
     port = int(os.environ.get("MASTER_PORT", "29500")) + 17
     ns = argparse.Namespace(
         data_dir=data, custom_cuda=bool(getattr(args, "custom_cuda", False)), default_impl=False, batch_size=B // G,

@@ -49,7 +49,7 @@ class _Slot:
 
 class FlatEncoder:
     def __init__(self, cfg: EncoderConfig, device, act_dtype=torch.bfloat16, pooling: str = "mean",
-                 bottleneck_dims: int = 0, seed: int = 0, grad_alloc=None):
+                 bottleneck_dims: int = 0, seed: int = 0, grad_alloc=None, p16_alloc=None):
         self.cfg = cfg
         self.device = torch.device(device)
         self.act_dtype = act_dtype
@@ -93,7 +93,12 @@ class FlatEncoder:
             raise ValueError(f"hidden size must be a multiple of {ALIGN}")
         dev = self.device
         self.p32 = torch.zeros(off, dtype=torch.float32, device=dev)
-        self.p16 = self.p32 if act_dtype == torch.float32 else torch.zeros(off, dtype=act_dtype, device=dev)
+        if act_dtype == torch.float32:
+            self.p16 = self.p32
+        elif p16_alloc is not None:
+            self.p16 = p16_alloc(off, act_dtype)[:off]
+        else:
+            self.p16 = torch.zeros(off, dtype=act_dtype, device=dev)
         if grad_alloc is not None and act_dtype != torch.float32:
             # the gradient buffer lives where the collective backend wants it (symmetric peer memory)
             self.g = grad_alloc(off, act_dtype)[:off]

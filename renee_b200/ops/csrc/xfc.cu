@@ -48,11 +48,21 @@ struct GemmParams {
   float* dX; int ldX; const float* hp;
   // DW
   __half* W; __half* Mom; int ldW; float mo; float wd;
-  float* Zout;       // RAW: fp32 logits [M, ldG] (debug / top-k path)
+  float* Zout;       // RAW: fp32 logits, batch-major Zt[N, ldG] (top-k path)
   // multi-GPU fusion (null / 0 when unused)
   const uint32_t* wait_flags; int wait_n; StepTag tag;   // LOGITS: X rows of every rank have landed
   unsigned* done_counter; PeerPtrs peer_flags; int n_peers; int flag_index;   // DX: last CTA raises "partial complete"
+  int stochastic_round;   // DW (TMA kernel): round the updated weights to fp16 stochastically
 };
+
+// fp32 -> fp16 with stochastic rounding: add uniform noise below the 13 mantissa bits fp16 drops, then
+// truncate.  Unbiased for values in fp16's normal range, which keeps updates smaller than half an ulp
+// of W from being lost systematically late in the learning-rate schedule.
+__device__ __forceinline__ __half sr_half(float x, uint32_t rnd) {
+  uint32_t b = __float_as_uint(x);
+  b = (b + (rnd & 0x1FFFu)) & ~0x1FFFu;
+  return __float2half_rz(__uint_as_float(b));
+}
 
 __device__ __forceinline__ int lower_bound_i32(const int* a, int n, int key) {
   int lo = 0, hi = n;
@@ -191,10 +201,11 @@ xfc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             }
           }
         } else if (MODE == MODE_RAW) {
+          // batch-major store Zt[b, label]: for a fixed j the 32 lanes write 32 consecutive labels
           if (row < p.M) {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) p.Zout[(size_t)row * p.ldG + col0 + j] = v[j];
+              if (col0 + j < p.N) p.Zout[(size_t)(col0 + j) * p.ldG + row] = v[j];
           }
         } else if (MODE == MODE_DX) {
           if (row < p.M) {
@@ -372,6 +383,7 @@ xfc_dw_sgd_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     if (ok) {
       const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16);
       const float lr = p.hp[HP_LR_XFC];
+      const uint32_t sr_seed = reinterpret_cast<const uint32_t*>(p.hp)[HP_SEED];
       for (int c0 = 0; c0 < p.BN; c0 += 32) {
         float v[32];
         tc::tmem_ld32(tbase + c0, v);
@@ -395,7 +407,13 @@ xfc_dw_sgd_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             m.y = p.mo * m.y + g1;
             m2[j] = __floats2half2_rn(m.x, m.y);
             const float2 ms = __half22float2(m2[j]);
-            w2[j] = __floats2half2_rn(w.x - lr * ms.x, w.y - lr * ms.y);
+            if (p.stochastic_round) {
+              const uint32_t e = (uint32_t)(m0 + r) * (uint32_t)p.ldW + (uint32_t)(n0 + c0 + 8 * j8 + 2 * j);
+              w2[j] = __halves2half2(sr_half(w.x - lr * ms.x, mix32(sr_seed, 0x5152u, e)),
+                                     sr_half(w.y - lr * ms.y, mix32(sr_seed, 0x5152u, e + 1)));
+            } else {
+              w2[j] = __floats2half2_rn(w.x - lr * ms.x, w.y - lr * ms.y);
+            }
           }
           *reinterpret_cast<uint4*>(sW + off) = wr;
           *reinterpret_cast<uint4*>(sM + off) = mr;
@@ -419,6 +437,66 @@ xfc_dw_sgd_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   if (warp == 1) {
     tc::tc_fence_after();
     tc::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------ row-wise top-k by radix select
+// One CTA per batch row scans that row of the batch-major logits chunk (L2 resident) five times: four
+// 8-bit histogram passes find the k-th largest key exactly, the fifth collects every element above it
+// plus as many ties as needed.  Output is unordered (the cross-chunk / cross-rank merge sorts k items).
+// Replaces torch.topk / the K passes of torch.max + index_put_ of the reference (dl_base.py:745-756).
+__device__ __forceinline__ uint32_t order_key(float x) {
+  const uint32_t u = __float_as_uint(x);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__global__ void __launch_bounds__(256) topk_rows_kernel(const float* __restrict__ Z, int ldZ, int n, int k, int label0,
+                                                        float* __restrict__ out_val, int* __restrict__ out_idx) {
+  __shared__ unsigned hist[256];
+  __shared__ uint32_t s_prefix, s_mask;
+  __shared__ int s_remaining, s_cnt_gt, s_cnt_eq;
+  const float* row = Z + (size_t)blockIdx.x * ldZ;
+  float* ov = out_val + (size_t)blockIdx.x * k;
+  int* oi = out_idx + (size_t)blockIdx.x * k;
+  const int kk = min(k, n);
+  if (threadIdx.x == 0) { s_prefix = 0u; s_mask = 0u; s_remaining = kk; s_cnt_gt = 0; s_cnt_eq = 0; }
+  for (int i = kk + (int)threadIdx.x; i < k; i += blockDim.x) { ov[i] = -3.0e38f; oi[i] = label0; }
+  __syncthreads();
+  for (int pass = 3; pass >= 0; --pass) {
+    hist[threadIdx.x] = 0u;
+    __syncthreads();
+    const uint32_t prefix = s_prefix, mask = s_mask;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const uint32_t key = order_key(row[i]);
+      if ((key & mask) == prefix) atomicAdd(&hist[(key >> (8 * pass)) & 0xFFu], 1u);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int remaining = s_remaining;
+      int d = 255;
+      for (; d > 0; --d) {
+        if ((int)hist[d] >= remaining) break;
+        remaining -= (int)hist[d];
+      }
+      s_remaining = remaining;
+      s_prefix = prefix | ((uint32_t)d << (8 * pass));
+      s_mask = mask | (0xFFu << (8 * pass));
+    }
+    __syncthreads();
+  }
+  const uint32_t T = s_prefix;
+  const int need_eq = s_remaining;
+  const int n_gt = kk - need_eq;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float x = row[i];
+    const uint32_t key = order_key(x);
+    if (key > T) {
+      const int slot = atomicAdd(&s_cnt_gt, 1);
+      if (slot < n_gt) { ov[slot] = x; oi[slot] = label0 + i; }
+    } else if (key == T) {
+      const int slot = atomicAdd(&s_cnt_eq, 1);
+      if (slot < need_eq) { ov[n_gt + slot] = x; oi[n_gt + slot] = label0 + i; }
+    }
   }
 }
 
@@ -464,12 +542,13 @@ static int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
 // Gt[Lc, ldG] = sigmoid(W X^T) - Y for the label chunk W[Lc, D]; labels of the chunk are
 // label0 .. label0+Lc-1 in the numbering of pos_labels.  raw_out != null writes fp32 logits instead
-// (no sigmoid, no positives) into raw_out[Lc, ldG].
+// (no sigmoid, no positives), batch-major, into raw_out[B, ldG] with ldG >= Lc.
 RB_API int rb_xfc_logits_grad(const void* W, int Lc, int D, const void* X, int B, void* Gt, int ldG,
                               const int* pos_rows, const int* pos_labels, const int* nnz_ptr, int label0,
                               float* loss_acc, float* raw_out, const unsigned* wait_flags, int wait_n,
                               const unsigned* step_ptr, int* status, cudaStream_t st) {
-  if (D % 8 || ldG % 8 || ldG < B || Lc < 1 || B < 1) return -3;
+  if (D % 8 || ldG % 8 || Lc < 1 || B < 1) return -3;
+  if (raw_out == nullptr ? ldG < B : ldG < Lc) return -3;
   const int BN = B >= 256 ? 256 : round_up(B, 16);
   CUtensorMap ta, tb;
   int rc = tc::make_tmap_2d(&ta, W, Lc, D, D, 64, kBM, false);
@@ -532,7 +611,8 @@ RB_API int rb_xfc_dx(const void* Gt, int ldG, const void* W, int Lc, int D, int 
 // W, Mom [Lc, D] updated in place from dW = Gt X (never stored); lr read from hp[LR_XFC]
 // use_tma_tiles != 0 selects the kernel that stages the W / M tiles through shared memory with TMA.
 RB_API int rb_xfc_dw_sgd(const void* Gt, int ldG, const void* X, int B, void* W, void* Mom, int Lc, int D,
-                         const float* hp, float mo, float wd, int use_tma_tiles, int* status, cudaStream_t st) {
+                         const float* hp, float mo, float wd, int use_tma_tiles, int stochastic_round, int* status,
+                         cudaStream_t st) {
   if (D % 8 || ldG % 8 || Lc < 1) return -3;
   const int BN = D >= 256 ? 256 : round_up(D, 64);
   CUtensorMap ta, tb;
@@ -543,6 +623,8 @@ RB_API int rb_xfc_dw_sgd(const void* Gt, int ldG, const void* X, int B, void* W,
   GemmParams p{};
   p.M = Lc; p.N = D; p.BN = BN; p.kb_total = (B + kBK - 1) / kBK; p.kb_per_split = p.kb_total; p.status = status;
   p.W = (__half*)W; p.Mom = (__half*)Mom; p.ldW = D; p.hp = hp; p.mo = mo; p.wd = wd;
+  p.stochastic_round = stochastic_round;
+  if (stochastic_round && !use_tma_tiles) return -3;
   dim3 grid((Lc + kBM - 1) / kBM, (D + BN - 1) / BN, 1);
   if (use_tma_tiles) {
     CUtensorMap tw, tm;
@@ -561,6 +643,15 @@ RB_API int rb_xfc_dw_sgd(const void* Gt, int ldG, const void* X, int B, void* W,
     rc = launch_gemm<MODE_DW>(ta, tb, p, grid, st);
     if (rc) return rc;
   }
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+// Unordered top-k of every row of the batch-major fp32 logits Z[B, ldZ] (first n columns valid).
+RB_API int rb_topk_rows(const float* Z, int ldZ, int B, int n, int k, int label0, float* out_val, int* out_idx,
+                        cudaStream_t st) {
+  if (B < 1 || n < 1 || k < 1) return -3;
+  topk_rows_kernel<<<B, 256, 0, st>>>(Z, ldZ, n, k, label0, out_val, out_idx);
   RB_LAUNCH_CHECK();
   return 0;
 }

@@ -229,12 +229,12 @@ def xfc_dx(Gt, ldG, W, B, dX, hp_buf, splits, signal=None):
           ptrs if ptrs is not None else _VP(0), _I(n), _I(idx), _p(step), _p(ws.status), _stream())
 
 
-def xfc_dw_sgd(Gt, ldG, X, W, M, hp_buf, mo, wd, tma_tiles=True):
+def xfc_dw_sgd(Gt, ldG, X, W, M, hp_buf, mo, wd, tma_tiles=True, stochastic_round=False):
     Lc, D = W.shape
     B = X.shape[0]
     ws = workspace(W.device)
     _call("rb_xfc_dw_sgd", _p(Gt), _I(ldG), _p(X), _I(B), _p(W), _p(M), _I(Lc), _I(D), _p(hp_buf), _F(mo), _F(wd),
-          _I(1 if tma_tiles else 0), _p(ws.status), _stream())
+          _I(1 if tma_tiles else 0), _I(1 if stochastic_round else 0), _p(ws.status), _stream())
 
 
 def dx_splits(B: int, D: int, Lc: int) -> int:
@@ -268,30 +268,36 @@ def xfc_step(xfc, X, pos_rows, pos_labels, nnz, dX_out, hp, mo, wd, want_loss, w
             _call("rb_xfc_pos_logit_sum", _p(xfc.W), _p(X), _I(D), _p(pos_rows), _p(pos_labels), _p(nnz), _p(loss),
                   _stream())
         xfc_dx(Gt, ldG, Wc, B, dX_out, hp.buf, dx_splits(B, D, l1 - l0), signal=signal if ci == len(chunks) - 1 else None)
-        xfc_dw_sgd(Gt, ldG, X, Wc, Mc, hp.buf, mo, wd)
+        xfc_dw_sgd(Gt, ldG, X, Wc, Mc, hp.buf, mo, wd, stochastic_round=xfc.stochastic_round)
     return loss[0] if want_loss else None
 
 
+def topk_rows(Z, n, k, label0, out_val, out_idx):
+    """Unordered top-k of each row of batch-major fp32 logits ``Z[B, ldZ]`` (first ``n`` columns valid)."""
+    B, ldZ = Z.shape
+    _call("rb_topk_rows", _p(Z), _I(ldZ), _I(B), _I(n), _I(k), _I(label0), _p(out_val), _p(out_idx), _stream())
+
+
 def xfc_topk(xfc, X, k):
-    """Local top-k of ``X Wᵀ``: fp32 logits of one label chunk at a time from the tcgen05 GEMM (raw
-    epilogue), reduced with a running top-k."""
+    """Local top-k of ``X Wᵀ`` over this rank's shard: per label chunk, the tcgen05 logits GEMM writes fp32
+    logits batch-major into an L2-sized buffer and a radix-select kernel extracts each row's k best; the
+    per-chunk candidates (k each) are merged at the end."""
     B, D = X.shape
-    ldG = _ld_g(B)
-    chunk = min(xfc.chunk, max(128, (16 << 20) // (4 * ldG) // 128 * 128))
-    Z = torch.empty(chunk, ldG, dtype=torch.float32, device=X.device)
-    vals = idxs = None
-    for l0 in range(0, xfc.Ls, chunk):
+    k_eff = min(k, xfc.Ls)
+    chunk = min(xfc.chunk, max(128, (32 << 20) // (4 * B) // 128 * 128))
+    ldZ = (min(chunk, xfc.Ls) + 7) // 8 * 8
+    Z = torch.empty(B, ldZ, dtype=torch.float32, device=X.device)
+    starts = list(range(0, xfc.Ls, chunk))
+    vals = torch.empty(len(starts), B, k_eff, dtype=torch.float32, device=X.device)
+    idxs = torch.empty(len(starts), B, k_eff, dtype=torch.int32, device=X.device)
+    for ci, l0 in enumerate(starts):
         l1 = min(xfc.Ls, l0 + chunk)
-        xfc_logits_grad(xfc.W[l0:l1], X, None, ldG, None, None, None, l0, raw_out=Z)
-        v, i = torch.topk(Z[: l1 - l0, :B].t(), min(k, l1 - l0), dim=1)
-        i = i + l0
-        if vals is None:
-            vals, idxs = v, i
-        else:
-            cv, ci = torch.cat([vals, v], 1), torch.cat([idxs, i], 1)
-            vals, sel = torch.topk(cv, min(k, cv.shape[1]), dim=1)
-            idxs = torch.gather(ci, 1, sel)
-    return vals, idxs
+        xfc_logits_grad(xfc.W[l0:l1], X, None, ldZ, None, None, None, l0, raw_out=Z)
+        topk_rows(Z, l1 - l0, k_eff, l0, vals[ci], idxs[ci])
+    cv = vals.permute(1, 0, 2).reshape(B, -1)
+    ci_ = idxs.permute(1, 0, 2).reshape(B, -1)
+    v, sel = torch.topk(cv, k_eff, dim=1)
+    return v, torch.gather(ci_, 1, sel).long()
 
 
 # ----------------------------------------------------------------------------- peer-memory collectives
@@ -331,3 +337,17 @@ def grad_allreduce(g_dtype, grad_ptrs, lo, hi, G, my_rank, my_flags_a, flag_ptrs
     ws = workspace(my_flags_a.device)
     _call("rb_grad_allreduce", _I(DT[g_dtype]), grad_ptrs, _LL(lo), _LL(hi), _I(G), _I(my_rank), _p(my_flags_a), flag_ptrs,
           _I(flag_b_base), _I(found_base), _p(step), _U(mul), _U(add), _p(counter), _I(blocks), _p(ws.status), _stream())
+
+
+def grad_reduce_scatter(g_dtype, grad_ptrs, n, G, my_rank, my_flags_a, step, gsum, flag_ptrs, flag_b_base, found_base,
+                        counter, blocks):
+    ws = workspace(my_flags_a.device)
+    _call("rb_grad_reduce_scatter", _I(DT[g_dtype]), grad_ptrs, _LL(n), _I(G), _I(my_rank), _p(my_flags_a), _p(step),
+          _p(gsum), flag_ptrs, _I(flag_b_base), _I(found_base), _p(counter), _I(blocks), _p(ws.status), _stream())
+
+
+def adamw_shard_push(p_dtype, p32, m, v, gsum, p16_ptrs, n, n_decay, G, my_rank, hp_buf, beta1, beta2, eps, wd, grad_mult,
+                     flag_ptrs, flag_c_base, step, counter, blocks):
+    _call("rb_adamw_shard_push", _I(DT[p_dtype]), _p(p32), _p(m), _p(v), _p(gsum), p16_ptrs, _LL(n), _LL(n_decay), _I(G),
+          _I(my_rank), _p(hp_buf), _F(beta1), _F(beta2), _F(eps), _F(wd), _F(grad_mult), flag_ptrs, _I(flag_c_base),
+          _p(step), _p(counter), _I(blocks), _stream())

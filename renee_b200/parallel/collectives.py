@@ -72,6 +72,16 @@ class TorchCollectives:
         ops.dropout_bwd(dx_local, p, rng, stream_id, de)
         return de
 
+    def optimizer_step(self, enc, hp, beta1, beta2, eps, wd) -> None:
+        """Reduce the encoder gradients over ranks and apply AdamW (here: all-reduce, then the full fused
+        AdamW on every rank).  The fused backend shards this step across ranks."""
+        from .. import ops
+        grad_mult = self.allreduce_grads(enc.g, hp)
+        ops.adamw_step(enc.p32, enc.m, enc.v, enc.g, enc.p16, hp, beta1, beta2, eps, wd, enc.n_decay, grad_mult)
+
+    def sync_master(self, enc) -> None:
+        """Make every rank's fp32 master weights complete (a no-op unless the optimizer is sharded)."""
+
     # ---- embeddings
     def gather_embeddings(self, x_local: torch.Tensor, B: int, out: torch.Tensor) -> torch.Tensor:
         """``x_local [b_r, D]`` → ``out[:B]`` with rank r's rows at ``batch_row_range(B, G, r)``."""

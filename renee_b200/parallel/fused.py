@@ -37,15 +37,18 @@ from .collectives import TorchCollectives
 from .dist import DistContext
 
 # word offsets of the flag classes inside the symmetric flag array (16 words each)
-F_AG, F_RS, F_ARA, F_ARB, F_FOUND = 0, 16, 32, 48, 64
+F_AG, F_RS, F_ARA, F_ARB, F_FOUND, F_ARC = 0, 16, 32, 48, 64, 80
 FLAG_WORDS = 128
 
 
 class PeerCollectives(TorchCollectives):
     graph_safe = True
 
-    def __init__(self, ctx: DistContext, group=None):
+    def __init__(self, ctx: DistContext, group=None, shard_optimizer: bool = True):
         super().__init__(ctx)
+        self.shard_optimizer = shard_optimizer
+        self.p16 = None
+        self.gsum = None
         if ctx.device.type != "cuda":
             raise RuntimeError("PeerCollectives needs CUDA devices")
         if self.G > 16:
@@ -97,6 +100,56 @@ class PeerCollectives(TorchCollectives):
         torch.cuda.synchronize()
         dist.barrier(group=self.group)
         return self.grad
+
+    def alloc_p16(self, numel: int, dtype) -> torch.Tensor:
+        """Low-precision compute copy of the encoder parameters in symmetric memory: with the sharded
+        optimizer every rank stores its freshly updated slice into every rank's copy."""
+        from ..ops import cuda as cu
+        n = (numel + 1023) // 1024 * 1024
+        self.p16, pp = self._symm(n, dtype)
+        self.p16.zero_()
+        self._p16_ptrs = cu.ptr_array(pp)
+        per = ((numel // 8) + self.G - 1) // self.G * 8
+        self.gsum = torch.zeros(per + 8, dtype=torch.float32, device=self.ctx.device)
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        return self.p16
+
+    def slice_range(self, numel: int, rank: int) -> tuple[int, int]:
+        n_vec = numel // 8
+        per = (n_vec + self.G - 1) // self.G
+        return min(n_vec, per * rank) * 8, min(n_vec, per * (rank + 1)) * 8
+
+    def _sharded(self, enc) -> bool:
+        return (self.shard_optimizer and self.p16 is not None and self.grad is not None
+                and enc.g.data_ptr() == self.grad.data_ptr() and enc.p16.data_ptr() == self.p16.data_ptr())
+
+    def optimizer_step(self, enc, hp, beta1, beta2, eps, wd) -> None:
+        """Sharded AdamW: reduce-scatter of the gradients, AdamW on this rank's slice of the masters, push of
+        the updated 16-bit slice into every rank's compute copy.  The found-inf decision is global because
+        the slice update only starts after every rank's reduction (and its non-finite report) has landed."""
+        from ..ops import cuda as cu
+        if not self._sharded(enc):
+            return super().optimizer_step(enc, hp, beta1, beta2, eps, wd)
+        n = enc.numel
+        cu.signal(self._flag_ptrs, self.G, F_ARA, self.rank, self.step)
+        cu.grad_reduce_scatter(enc.g.dtype, self._grad_ptrs, n, self.G, self.rank, self.flags[F_ARA:], self.step, self.gsum,
+                               self._flag_ptrs, F_ARB, F_FOUND, self.counters[48:], 148 * 2)
+        cu.wait_flags(self.flags[F_ARB:], self.G, self.step, 1, 0, self.flags[F_FOUND:], hp.buf)
+        cu.adamw_shard_push(enc.p16.dtype, enc.p32, enc.m, enc.v, self.gsum, self._p16_ptrs, n, enc.n_decay, self.G,
+                            self.rank, hp.buf, beta1, beta2, eps, wd, 1.0 / self.G, self._flag_ptrs, F_ARC, self.step,
+                            self.counters[52:], 148 * 2)
+        cu.wait_flags(self.flags[F_ARC:], self.G, self.step, 1, 0, None, None)
+
+    def sync_master(self, enc) -> None:
+        """Collective: after it, every rank holds the complete fp32 master weights (each rank owns the
+        up-to-date values of its slice only).  Called before state dicts are taken."""
+        if not self._sharded(enc):
+            return
+        for r in range(self.G):
+            lo, hi = self.slice_range(enc.numel, r)
+            if hi > lo:
+                dist.broadcast(enc.p32[lo:hi], src=r, group=self.group)
 
     # ------------------------------------------------------------------ per-step protocol
     @property

@@ -168,7 +168,8 @@ class XCTrainer:
         self.D = D
         self.comm.setup(self.B, D)
         self.encoder = FlatEncoder(self.enc_cfg, self.device, self.act_dtype, cfg.pooling, cfg.bottleneck_dims,
-                                   seed=cfg.seed, grad_alloc=getattr(self.comm, "alloc_grad", None))
+                                   seed=cfg.seed, grad_alloc=getattr(self.comm, "alloc_grad", None),
+                                   p16_alloc=getattr(self.comm, "alloc_p16", None))
         self.xfc = XFCClassifier(self.Ls, D, self.device, cfg.fp16xfc,
                                  rank=self.rank, seed=cfg.seed, max_batch=self.B, accum=cfg.accum,
                                  stochastic_round=cfg.stochastic_round)
@@ -298,9 +299,7 @@ class XCTrainer:
             loss = comm.allreduce_scalar(loss.reshape(1))
         de = comm.dx_to_local(dX, B, cfg.dropout, self.step_rng, _S_CLS_DROPOUT, bf)
         enc.backward(de)
-        grad_mult = comm.allreduce_grads(enc.g, self.hp)
-        ops.adamw_step(enc.p32, enc.m, enc.v, enc.g, enc.p16, self.hp, 0.9, 0.999, cfg.adam_eps, cfg.wd2, enc.n_decay,
-                       grad_mult)
+        comm.optimizer_step(enc, self.hp, 0.9, 0.999, cfg.adam_eps, cfg.wd2)
         self.hp.update_scale()
         return loss
 
@@ -346,6 +345,7 @@ class XCTrainer:
     def state_dict(self) -> dict:
         if self.cfg.default_impl:
             return {k: v.detach().clone() for k, v in self.model.state_dict().items()}
+        self.comm.sync_master(self.encoder)     # collective when the optimizer is sharded over ranks
         sd = {"xfc_weight": self.xfc.state_dict_weight()}
         for k, v in self.encoder.encoder_state_dict().items():
             sd[f"embed.0.transformer.{k}"] = v

@@ -137,3 +137,49 @@ def test_bounded_wait_times_out_with_status_and_context_survives():
     cu().check_status()                   # status was cleared by the failed check
     x = torch.ones(16, device=dev())
     assert float((x * 2).sum()) == 32.0   # the context is still usable
+
+
+def test_sharded_adamw_emulated_matches_full_adamw():
+    """Reduce-scatter + AdamW on each rank's slice + parameter push equals all-reduce + full AdamW."""
+    from renee_b200.parallel.fused import F_ARC
+    G, n, n_decay = 4, 8 * 1031, 8 * 500
+    torch.manual_seed(2)
+    ranks = [Rank(r, G, 8, 8, n) for r in range(G)]
+    p0 = torch.randn(n, device=dev())
+    m0, v0 = torch.rand(n, device=dev()) * 0.1, torch.rand(n, device=dev()) * 0.01
+    st = []
+    for k in ranks:
+        k.grad.copy_((torch.randn(n, device=dev()) * 64).bfloat16())
+        hp = HyperParams(dev(), init_scale=64.0)
+        hp.buf[HP.LR_ENC] = 1e-2
+        hp.buf[HP.ADAM_STEP] = 2
+        st.append(dict(p32=p0.clone(), m=m0.clone(), v=v0.clone(), p16=p0.bfloat16(), hp=hp,
+                       gsum=torch.zeros(n // G + 64, device=dev())))
+    gsum_all = sum(k.grad.float() for k in ranks)
+    rp, rm, rv = p0.clone(), m0.clone(), v0.clone()
+    ref.adamw_step(rp, rm, rv, gsum_all, None, 1e-2, 0.9, 0.999, 1e-6, 0.01, n_decay, 3.0, (1 / 64.0) / G, 0.0)
+    g_ptrs = cu().ptr_array([k.grad.data_ptr() for k in ranks])
+    f_ptrs = cu().ptr_array([k.flags.data_ptr() for k in ranks])
+    p_ptrs = cu().ptr_array([s["p16"].data_ptr() for s in st])
+    for k in ranks:
+        cu().signal(f_ptrs, G, F_ARA, k.r, k.step)
+    for k, s in zip(ranks, st):
+        cu().grad_reduce_scatter(torch.bfloat16, g_ptrs, n, G, k.r, k.flags[F_ARA:], k.step, s["gsum"], f_ptrs, F_ARB,
+                                 F_FOUND, k.counters[48:], 5)
+    for k, s in zip(ranks, st):
+        cu().wait_flags(k.flags[F_ARB:], G, k.step, 1, 0, k.flags[F_FOUND:], s["hp"].buf)
+    for k, s in zip(ranks, st):
+        cu().adamw_shard_push(torch.bfloat16, s["p32"], s["m"], s["v"], s["gsum"], p_ptrs, n, n_decay, G, k.r, s["hp"].buf,
+                              0.9, 0.999, 1e-6, 0.01, 1.0 / G, f_ptrs, F_ARC, k.step, k.counters[52:], 5)
+    for k in ranks:
+        cu().wait_flags(k.flags[F_ARC:], G, k.step, 1, 0, None, None)
+    cu().check_status()
+    per = ((n // 8) + G - 1) // G * 8
+    for k, s in zip(ranks, st):
+        lo, hi = min(n, per * k.r), min(n, per * (k.r + 1))
+        torch.testing.assert_close(s["p32"][lo:hi], rp[lo:hi], rtol=1e-5, atol=1e-6)
+        torch.testing.assert_close(s["m"][lo:hi], rm[lo:hi], rtol=1e-5, atol=1e-7)
+        torch.testing.assert_close(s["v"][lo:hi], rv[lo:hi], rtol=1e-5, atol=1e-7)
+        assert torch.equal(s["p32"][:lo], p0[:lo]) and torch.equal(s["p32"][hi:], p0[hi:])   # other slices untouched
+        torch.testing.assert_close(s["p16"].float(), rp, rtol=1e-2, atol=1e-2)                  # every slice arrived
+        assert k.flags[F_ARC:F_ARC + G].tolist() == [1] * G

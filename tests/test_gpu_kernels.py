@@ -208,9 +208,19 @@ def test_xfc_logits_grad(B, D, Lc, nnz):
     assert float(Gt[:, B:].abs().max()) == 0.0 if ldG > B else True
     zpos = (W.float() @ X.float().t())[labels.long(), rows.long()].sum()
     torch.testing.assert_close(loss[0], lr + zpos, rtol=2e-3, atol=1.0)
-    raw = torch.empty(Lc, ldG, device=dev())
-    cu().xfc_logits_grad(W, X, None, ldG, None, None, None, 0, raw_out=raw)
-    torch.testing.assert_close(raw[:, :B], W.float() @ X.float().t(), rtol=1e-3, atol=1e-3)
+    ldZ = (Lc + 7) // 8 * 8
+    raw = torch.empty(B, ldZ, device=dev())
+    cu().xfc_logits_grad(W, X, None, ldZ, None, None, None, 0, raw_out=raw)
+    Zr = X.float() @ W.float().t()
+    torch.testing.assert_close(raw[:, :Lc], Zr, rtol=1e-3, atol=1e-3)
+    for k in (5, 100):
+        kk = min(k, Lc)
+        ov = torch.empty(B, kk, device=dev())
+        oi = torch.empty(B, kk, dtype=torch.int32, device=dev())
+        cu().topk_rows(raw, Lc, kk, 7, ov, oi)
+        vr, _ = torch.topk(raw[:, :Lc], kk, dim=1)
+        torch.testing.assert_close(torch.sort(ov, dim=1, descending=True)[0], vr, rtol=0, atol=0)
+        torch.testing.assert_close(torch.gather(raw[:, :Lc], 1, (oi - 7).long()), ov, rtol=0, atol=0)
 
 
 @pytest.mark.parametrize("B,D,Lc,nnz", XFC_SHAPES)
@@ -304,3 +314,33 @@ def test_trainer_step_on_gpu_tracks_cpu_reference():
     sa, sb = a.state_dict(), b.state_dict()
     for k in sa:
         torch.testing.assert_close(sa[k].cpu(), sb[k], rtol=5e-3, atol=2e-4, msg=lambda m: f"{k}: {m}")
+
+
+def test_xfc_dw_sgd_both_kernels_agree_and_stochastic_rounding_is_unbiased():
+    B, D, Lc = 128, 768, 512
+    X, W, rows, labels = _xfc_problem(B, D, Lc, 200)
+    Gr, _ = ref.xfc_logit_grad(X, W, rows, labels)
+    Gt = Gr.contiguous()
+    M = (torch.randn(Lc, D, device=dev()) * 0.01).half()
+    hp = HyperParams(dev())
+    hp.buf[HP.LR_XFC] = 0.05
+    W1, M1, W2, M2 = W.clone(), M.clone(), W.clone(), M.clone()
+    cu().xfc_dw_sgd(Gt, B, X, W1, M1, hp.buf, 0.9, 1e-3, tma_tiles=True)
+    cu().xfc_dw_sgd(Gt, B, X, W2, M2, hp.buf, 0.9, 1e-3, tma_tiles=False)
+    cu().check_status()
+    assert torch.equal(W1, W2) and torch.equal(M1, M2)
+    # updates of a tenth of an ulp: round-to-nearest loses them all, stochastic rounding keeps their mean
+    Wc = torch.ones(Lc, D, dtype=torch.float16, device=dev())
+    Mc = torch.full((Lc, D), 1.0, dtype=torch.float16, device=dev())
+    Z = torch.zeros(Lc, B, dtype=torch.float16, device=dev())
+    hp.buf[HP.LR_XFC] = 1e-4
+    hp.set_step(1e-4, 0.0, 12345)
+    hp.upload()
+    Wn, Mn = Wc.clone(), Mc.clone()
+    cu().xfc_dw_sgd(Z, B, X, Wn, Mn, hp.buf, 1.0, 0.0)
+    assert torch.equal(Wn, Wc)
+    Ws, Ms = Wc.clone(), Mc.clone()
+    cu().xfc_dw_sgd(Z, B, X, Ws, Ms, hp.buf, 1.0, 0.0, stochastic_round=True)
+    delta = (Ws.float() - 1.0).mean().item()
+    assert abs(delta + 1e-4) < 2e-5, delta
+    assert set(torch.unique(Ws).tolist()) <= {1.0, 1.0 - 2.0 ** -11}
