@@ -165,6 +165,9 @@ def run_reference(args, c) -> dict | None:
     if G > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t[0])
+    if G > 1:
+        dist.barrier()
+        dist.destroy_process_group()
     if rank != 0:
         return None
     value = B * K / (ms / 1e3)

@@ -183,7 +183,7 @@ __global__ void __launch_bounds__(256) grad_reduce_scatter_kernel(PeerPtrs grads
                                                                   const uint32_t* __restrict__ my_flags_a, StepTag tag,
                                                                   float* __restrict__ gsum, PeerPtrs flags, int flag_b_base,
                                                                   int found_base, unsigned* __restrict__ counter,
-                                                                  int* status) {
+                                                                  int* status, const void* mc_grads) {
   const bool ok = block_wait_flags(my_flags_a, G, tag.value(), status, 5);
   const long long n_vec = n / 8;
   const long long per = (n_vec + G - 1) / G;
@@ -192,13 +192,21 @@ __global__ void __launch_bounds__(256) grad_reduce_scatter_kernel(PeerPtrs grads
   if (ok) {
     for (long long i = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < v1; i += (long long)gridDim.x * blockDim.x) {
       float acc[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-      for (int q = 0; q < G; ++q) {
-        const uint4 raw = ld_sys_v4(reinterpret_cast<const T*>(grads.p[q]) + i * 8);
+      if (mc_grads != nullptr) {
+        // in-switch reduction: one 16-byte load returns the sum of all ranks' 8 gradients
+        const uint4 raw = multimem_ld_reduce_v4<T>(reinterpret_cast<const T*>(mc_grads) + i * 8);
         const T* h = reinterpret_cast<const T*>(&raw);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] += to_f(h[j]);
+        for (int j = 0; j < 8; ++j) acc[j] = to_f(h[j]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int q = 0; q < G; ++q) {
+          const uint4 raw = ld_sys_v4(reinterpret_cast<const T*>(grads.p[q]) + i * 8);
+          const T* h = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += to_f(h[j]);
+        }
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) bad |= !isfinite(acc[j]);
@@ -227,7 +235,8 @@ __global__ void __launch_bounds__(256) adamw_shard_push_kernel(float* __restrict
                                                                PeerPtrs p16, long long n, long long n_decay, int G, int my_rank,
                                                                const float* __restrict__ hp, float beta1, float beta2,
                                                                float eps, float wd, float grad_mult, PeerPtrs flags,
-                                                               int flag_c_base, StepTag tag, unsigned* __restrict__ counter) {
+                                                               int flag_c_base, StepTag tag, unsigned* __restrict__ counter,
+                                                               void* mc_p16) {
   const long long n_vec = n / 8;
   const long long per = (n_vec + G - 1) / G;
   const long long v0 = min(n_vec, per * my_rank), v1 = min(n_vec, per * (my_rank + 1));
@@ -258,7 +267,11 @@ __global__ void __launch_bounds__(256) adamw_shard_push_kernel(float* __restrict
       T* o = reinterpret_cast<T*>(&out);
 #pragma unroll
       for (int j = 0; j < 8; ++j) o[j] = from_f<T>(pp[j]);
-      for (int q = 0; q < G; ++q) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p16.p[q]) + e) = out;
+      if (mc_p16 != nullptr) {
+        multimem_st_v4(reinterpret_cast<T*>(mc_p16) + e, out);       // one store, every rank's copy
+      } else {
+        for (int q = 0; q < G; ++q) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p16.p[q]) + e) = out;
+      }
     }
   }
   __threadfence_system();
@@ -358,15 +371,15 @@ RB_API int rb_grad_allreduce(int dtype, void* const* grads, long long lo, long l
 RB_API int rb_grad_reduce_scatter(int dtype, void* const* grads, long long n, int G, int my_rank,
                                   const unsigned* my_flags_a, const unsigned* step_ptr, float* gsum, void* const* flags,
                                   int flag_b_base, int found_base, unsigned* counter, int blocks, int* status,
-                                  cudaStream_t st) {
+                                  const void* mc_grads, cudaStream_t st) {
   if (G > kMaxPeers || n % 8) return -3;
   if (blocks < 1) blocks = 1;
   PeerPtrs g = make_ptrs(grads, G), f = make_ptrs(flags, G);
   const StepTag tag{step_ptr, 1u, 0u};
   if (dtype == RB_BF16)
-    grad_reduce_scatter_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(g, n, G, my_rank, my_flags_a, tag, gsum, f, flag_b_base, found_base, counter, status);
+    grad_reduce_scatter_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(g, n, G, my_rank, my_flags_a, tag, gsum, f, flag_b_base, found_base, counter, status, mc_grads);
   else if (dtype == RB_F16)
-    grad_reduce_scatter_kernel<__half><<<blocks, 256, 0, st>>>(g, n, G, my_rank, my_flags_a, tag, gsum, f, flag_b_base, found_base, counter, status);
+    grad_reduce_scatter_kernel<__half><<<blocks, 256, 0, st>>>(g, n, G, my_rank, my_flags_a, tag, gsum, f, flag_b_base, found_base, counter, status, mc_grads);
   else
     return -1;
   RB_LAUNCH_CHECK();
@@ -376,15 +389,15 @@ RB_API int rb_grad_reduce_scatter(int dtype, void* const* grads, long long n, in
 RB_API int rb_adamw_shard_push(int dtype, float* p32, float* m, float* v, const float* gsum, void* const* p16,
                                long long n, long long n_decay, int G, int my_rank, const float* hp, float beta1,
                                float beta2, float eps, float wd, float grad_mult, void* const* flags, int flag_c_base,
-                               const unsigned* step_ptr, unsigned* counter, int blocks, cudaStream_t st) {
+                               const unsigned* step_ptr, unsigned* counter, int blocks, void* mc_p16, cudaStream_t st) {
   if (G > kMaxPeers || n % 8 || n_decay % 8) return -3;
   if (blocks < 1) blocks = 1;
   PeerPtrs pp = make_ptrs(p16, G), f = make_ptrs(flags, G);
   const StepTag tag{step_ptr, 1u, 0u};
   if (dtype == RB_BF16)
-    adamw_shard_push_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(p32, m, v, gsum, pp, n, n_decay, G, my_rank, hp, beta1, beta2, eps, wd, grad_mult, f, flag_c_base, tag, counter);
+    adamw_shard_push_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(p32, m, v, gsum, pp, n, n_decay, G, my_rank, hp, beta1, beta2, eps, wd, grad_mult, f, flag_c_base, tag, counter, mc_p16);
   else if (dtype == RB_F16)
-    adamw_shard_push_kernel<__half><<<blocks, 256, 0, st>>>(p32, m, v, gsum, pp, n, n_decay, G, my_rank, hp, beta1, beta2, eps, wd, grad_mult, f, flag_c_base, tag, counter);
+    adamw_shard_push_kernel<__half><<<blocks, 256, 0, st>>>(p32, m, v, gsum, pp, n, n_decay, G, my_rank, hp, beta1, beta2, eps, wd, grad_mult, f, flag_c_base, tag, counter, mc_p16);
   else
     return -1;
   RB_LAUNCH_CHECK();

@@ -35,6 +35,26 @@ __device__ __forceinline__ uint4 ld_sys_v4(const void* p) {
   return v;
 }
 
+// NVLS: one load returns the sum over every GPU bound to the multicast address (reduced in the NVSwitch,
+// fp32 accumulation of packed 16-bit pairs); one store lands in every GPU's copy.
+template <typename T> __device__ __forceinline__ uint4 multimem_ld_reduce_v4(const void* mc_addr);
+template <> __device__ __forceinline__ uint4 multimem_ld_reduce_v4<__nv_bfloat16>(const void* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_addr) : "memory");
+  return v;
+}
+template <> __device__ __forceinline__ uint4 multimem_ld_reduce_v4<__half>(const void* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_v4(void* mc_addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+               ::"l"(mc_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
 // Bounded wait until *flag >= want (wrap-safe).  Returns false (and records status) on expiry.
 __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t want, int* status, int detail) {
   if ((int32_t)(ld_acquire_sys(flag) - want) >= 0) return true;

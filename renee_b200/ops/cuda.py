@@ -340,14 +340,15 @@ def grad_allreduce(g_dtype, grad_ptrs, lo, hi, G, my_rank, my_flags_a, flag_ptrs
 
 
 def grad_reduce_scatter(g_dtype, grad_ptrs, n, G, my_rank, my_flags_a, step, gsum, flag_ptrs, flag_b_base, found_base,
-                        counter, blocks):
+                        counter, blocks, mc_grads: int = 0):
     ws = workspace(my_flags_a.device)
     _call("rb_grad_reduce_scatter", _I(DT[g_dtype]), grad_ptrs, _LL(n), _I(G), _I(my_rank), _p(my_flags_a), _p(step),
-          _p(gsum), flag_ptrs, _I(flag_b_base), _I(found_base), _p(counter), _I(blocks), _p(ws.status), _stream())
+          _p(gsum), flag_ptrs, _I(flag_b_base), _I(found_base), _p(counter), _I(blocks), _p(ws.status), _VP(mc_grads),
+          _stream())
 
 
 def adamw_shard_push(p_dtype, p32, m, v, gsum, p16_ptrs, n, n_decay, G, my_rank, hp_buf, beta1, beta2, eps, wd, grad_mult,
-                     flag_ptrs, flag_c_base, step, counter, blocks):
+                     flag_ptrs, flag_c_base, step, counter, blocks, mc_p16: int = 0):
     _call("rb_adamw_shard_push", _I(DT[p_dtype]), _p(p32), _p(m), _p(v), _p(gsum), p16_ptrs, _LL(n), _LL(n_decay), _I(G),
           _I(my_rank), _p(hp_buf), _F(beta1), _F(beta2), _F(eps), _F(wd), _F(grad_mult), flag_ptrs, _I(flag_c_base),
-          _p(step), _p(counter), _I(blocks), _stream())
+          _p(step), _p(counter), _I(blocks), _VP(mc_p16), _stream())

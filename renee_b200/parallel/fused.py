@@ -44,9 +44,17 @@ FLAG_WORDS = 128
 class PeerCollectives(TorchCollectives):
     graph_safe = True
 
-    def __init__(self, ctx: DistContext, group=None, shard_optimizer: bool = True):
+    def __init__(self, ctx: DistContext, group=None, shard_optimizer: bool = True, use_nvls: bool | None = None):
         super().__init__(ctx)
         self.shard_optimizer = shard_optimizer
+        # NVLS (multimem loads/stores through the NVSwitch multicast mapping) for the gradient reduction
+        # and the parameter push when the symmetric allocation exposes a multicast address; pass
+        # use_nvls=False or set RENEE_B200_NVLS=0 to stay on plain peer loads/stores (do so in any run in
+        # which a rank may exit while the others keep going)
+        import os
+        self.use_nvls = (os.environ.get("RENEE_B200_NVLS", "1") != "0") if use_nvls is None else bool(use_nvls)
+        self._mc_grad = 0
+        self._mc_p16 = 0
         self.p16 = None
         self.gsum = None
         if ctx.device.type != "cuda":
@@ -65,6 +73,7 @@ class PeerCollectives(TorchCollectives):
         t = symm_mem.empty(numel, dtype=dtype, device=self.ctx.device)
         hdl = symm_mem.rendezvous(t, self.group)
         self._handles.append(hdl)
+        self._last_multicast = int(getattr(hdl, "multicast_ptr", 0) or 0) if self.use_nvls else 0
         return t, [int(p) for p in hdl.buffer_ptrs]
 
     def setup(self, B_max: int, D: int) -> None:
@@ -95,6 +104,7 @@ class PeerCollectives(TorchCollectives):
         from ..ops import cuda as cu
         n = (numel + 1023) // 1024 * 1024
         self.grad, gp = self._symm(n, dtype)
+        self._mc_grad = self._last_multicast
         self.grad.zero_()
         self._grad_ptrs = cu.ptr_array(gp)
         torch.cuda.synchronize()
@@ -107,6 +117,7 @@ class PeerCollectives(TorchCollectives):
         from ..ops import cuda as cu
         n = (numel + 1023) // 1024 * 1024
         self.p16, pp = self._symm(n, dtype)
+        self._mc_p16 = self._last_multicast
         self.p16.zero_()
         self._p16_ptrs = cu.ptr_array(pp)
         per = ((numel // 8) + self.G - 1) // self.G * 8
@@ -134,11 +145,11 @@ class PeerCollectives(TorchCollectives):
         n = enc.numel
         cu.signal(self._flag_ptrs, self.G, F_ARA, self.rank, self.step)
         cu.grad_reduce_scatter(enc.g.dtype, self._grad_ptrs, n, self.G, self.rank, self.flags[F_ARA:], self.step, self.gsum,
-                               self._flag_ptrs, F_ARB, F_FOUND, self.counters[48:], 148 * 2)
+                               self._flag_ptrs, F_ARB, F_FOUND, self.counters[48:], 148 * 2, mc_grads=self._mc_grad)
         cu.wait_flags(self.flags[F_ARB:], self.G, self.step, 1, 0, self.flags[F_FOUND:], hp.buf)
         cu.adamw_shard_push(enc.p16.dtype, enc.p32, enc.m, enc.v, self.gsum, self._p16_ptrs, n, enc.n_decay, self.G,
                             self.rank, hp.buf, beta1, beta2, eps, wd, 1.0 / self.G, self._flag_ptrs, F_ARC, self.step,
-                            self.counters[52:], 148 * 2)
+                            self.counters[52:], 148 * 2, mc_p16=self._mc_p16)
         cu.wait_flags(self.flags[F_ARC:], self.G, self.step, 1, 0, None, None)
 
     def sync_master(self, enc) -> None:

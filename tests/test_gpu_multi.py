@@ -46,7 +46,8 @@ def _worker(rank, world, port, out_dir):
     for name, fused, graph in (("nccl", False, False), ("peer", True, False), ("peer_graph", True, True)):
         cfg = TrainConfig(batch_size=B // world, epochs=1, seed=0, dropout=0.5, lr1=1e-3, lr2=1e-5, warmup=2, wd1=1e-4,
                           noloss=True, fp16xfc=True, maxlen=S, pooling="cls", cuda_graph=graph)
-        comm = PeerCollectives(ctx) if fused else None
+        # eager run on plain peer loads/stores, graph run with NVLS multimem where the allocation offers it
+        comm = PeerCollectives(ctx, use_nvls=graph) if fused else None
         tr = XCTrainer(cfg, enc, sh, ctx, steps_per_epoch=100, comm=comm)
         for i in range(6):
             tr.train_step(batches[i % 4])
@@ -54,6 +55,7 @@ def _worker(rank, world, port, out_dir):
         cu.check_status()
         if graph:
             assert tr.graph_active()
+            print(f"rank {rank}: multicast grad={comm._mc_grad != 0} p16={comm._mc_p16 != 0}", flush=True)
         results[name] = {k: v.cpu() for k, v in tr.state_dict().items()}
         torch.distributed.barrier()
     torch.save(results, os.path.join(out_dir, f"r{rank}.pt"))
