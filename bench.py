@@ -38,6 +38,10 @@ CONFIGS = {
 }
 
 
+# Reference samples/s measured on the same box type with `--impl reference`
+REFERENCE_MEASURED = {("131k-s32", 1): 22446.22, ("131k-s32", 2): 20270.47}
+
+
 class ClockSampler:
     """Samples ``nvidia-smi`` clocks and throttle reasons every 200 ms while the timed region runs."""
 
@@ -171,7 +175,10 @@ def run_ours(args) -> dict:
     value = B * K / (ms / 1e3)
     out = {"metric": "train samples/sec (device-timed, max over ranks)", "value": round(value, 2), "unit": "samples/s",
            "n_gpus": G, "steps": K, "warmup": W, "ms_per_step": round(ms / K, 4), "higher_is_better": True,
-           "scaling": "strong", "vs_baseline": None, "dtype": "bf16 encoder, fp16 classifier W+momentum",
+           "scaling": "strong",
+           "vs_baseline": (round(value / REFERENCE_MEASURED[(args.config, G)], 3)
+                           if (args.config, G) in REFERENCE_MEASURED else None),
+           "dtype": "bf16 encoder, fp16 classifier W+momentum",
            "data": "synthetic seeded (Zipf labels, Poisson positives), random-init weights", "impl": "ours",
            "config": {"model": f"DistilBERT-style 6x768 encoder + label-sharded XFC, L={c['labels']}",
                       "global_batch": B, "seq_len": c["seq"], "labels": c["labels"],
