@@ -159,6 +159,9 @@ def start(local_device: int, ngpus_per_node: int, args) -> None:
         init_sd = strip_ngame_prefix(torch.load(args.use_ngame_encoder, map_location="cpu"))
     elif args.encoder_weights:
         init_sd = torch.load(args.encoder_weights, map_location="cpu")
+    if init_sd is not None and any("attention.self.query.weight" in k for k in init_sd):
+        from .models.encoder import convert_bert_state_dict
+        init_sd = convert_bert_state_dict(init_sd, roberta="roberta" in args.tf.lower())   # BERT / RoBERTa / MiniLM keys
     if init_sd is not None:
         if args.default_impl:
             trainer.model.embed[0].transformer.load_state_dict(init_sd, strict=True)

@@ -37,6 +37,7 @@ class EncoderConfig:
     layer_norm_eps: float = 1e-12
     initializer_range: float = 0.02
     pad_token_id: int = 0
+    attn_output_dropout: float = 0.0   # BERT/RoBERTa drop the attention output projection; DistilBERT does not
 
     @property
     def hidden_size(self) -> int:  # HF alias used by the reference (main.py:149,152)
@@ -50,11 +51,13 @@ ENCODER_PRESETS = {
     # name fragments → config; any DistilBERT-family checkpoint name maps to the base shape
     "distilbert": EncoderConfig(),
     "tiny": EncoderConfig(dim=128, n_layers=2, n_heads=2, hidden_dim=512),
-    "minilm-l6": EncoderConfig(dim=384, n_layers=6, n_heads=12, hidden_dim=1536),
-    "minilm-l3": EncoderConfig(dim=384, n_layers=3, n_heads=12, hidden_dim=1536),
-    "distilroberta": EncoderConfig(vocab_size=50265, max_position_embeddings=514, layer_norm_eps=1e-5),
-    "roberta-large": EncoderConfig(vocab_size=50265, max_position_embeddings=514, dim=1024, n_layers=24,
-                                   n_heads=16, hidden_dim=4096, layer_norm_eps=1e-5),
+    "minilm-l6": EncoderConfig(dim=384, n_layers=6, n_heads=12, hidden_dim=1536, attn_output_dropout=0.1),
+    "minilm-l3": EncoderConfig(dim=384, n_layers=3, n_heads=12, hidden_dim=1536, attn_output_dropout=0.1),
+    "distilroberta": EncoderConfig(vocab_size=50265, max_position_embeddings=512, layer_norm_eps=1e-5,
+                                   attn_output_dropout=0.1, pad_token_id=1),
+    "roberta-large": EncoderConfig(vocab_size=50265, max_position_embeddings=512, dim=1024, n_layers=24,
+                                   n_heads=16, hidden_dim=4096, layer_norm_eps=1e-5, attn_output_dropout=0.1,
+                                   pad_token_id=1),
 }
 
 
@@ -136,9 +139,10 @@ class TransformerBlock(nn.Module):
         self.sa_layer_norm = nn.LayerNorm(cfg.dim, eps=cfg.layer_norm_eps)
         self.ffn = FFN(cfg)
         self.output_layer_norm = nn.LayerNorm(cfg.dim, eps=cfg.layer_norm_eps)
+        self.attn_dropout = nn.Dropout(cfg.attn_output_dropout)
 
     def forward(self, x: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
-        h = self.sa_layer_norm(self.attention(x, mask) + x)
+        h = self.sa_layer_norm(self.attn_dropout(self.attention(x, mask)) + x)
         return self.output_layer_norm(self.ffn(h) + h)
 
 
@@ -177,6 +181,44 @@ class DistilEncoder(nn.Module):
         for blk in self.transformer.layer:
             x = blk(x, attention_mask)
         return {"last_hidden_state": x}
+
+
+def convert_bert_state_dict(sd: dict, roberta: bool = False) -> dict:
+    """Map a HF BERT / RoBERTa / MiniLM (BERT-architecture) encoder state dict onto this module's
+    DistilBERT-style names.  The block math is identical (post-LayerNorm, erf GELU); the differences are
+    absorbed exactly for single-segment, right-padded inputs:
+
+    * ``token_type_embeddings[0]`` is added to every position embedding;
+    * RoBERTa numbers real tokens from ``padding_idx + 1 = 2``, so its position table is shifted by two.
+
+    (The reference takes any ``AutoModel``, main.py:126-129; its recipes use DistilBERT, DistilRoBERTa,
+    RoBERTa-large and MiniLM, scripts/train_commands.md.)"""
+    g = lambda k: sd[k] if k in sd else sd["bert." + k] if ("bert." + k) in sd else sd["roberta." + k]
+    out = {}
+    pos = g("embeddings.position_embeddings.weight").clone().float()
+    tt = g("embeddings.token_type_embeddings.weight")[0].float()
+    if roberta:
+        pos = pos[2:]
+    out["embeddings.word_embeddings.weight"] = g("embeddings.word_embeddings.weight")
+    out["embeddings.position_embeddings.weight"] = pos + tt[None]
+    out["embeddings.LayerNorm.weight"] = g("embeddings.LayerNorm.weight")
+    out["embeddings.LayerNorm.bias"] = g("embeddings.LayerNorm.bias")
+    l = 0
+    while True:
+        src = f"encoder.layer.{l}."
+        try:
+            g(src + "attention.self.query.weight")
+        except KeyError:
+            break
+        dst = f"transformer.layer.{l}."
+        for a, b in (("attention.self.query", "attention.q_lin"), ("attention.self.key", "attention.k_lin"),
+                     ("attention.self.value", "attention.v_lin"), ("attention.output.dense", "attention.out_lin"),
+                     ("attention.output.LayerNorm", "sa_layer_norm"), ("intermediate.dense", "ffn.lin1"),
+                     ("output.dense", "ffn.lin2"), ("output.LayerNorm", "output_layer_norm")):
+            for kind in ("weight", "bias"):
+                out[dst + b + "." + kind] = g(src + a + "." + kind)
+        l += 1
+    return out
 
 
 def strip_ngame_prefix(state_dict: dict) -> dict:

@@ -192,7 +192,8 @@ class FlatEncoder:
         P = self.p16
         pd = cfg.dropout if train else 0.0
         pa = cfg.attention_dropout if train else 0.0
-        self._fw = dict(ids=input_ids, mask=attention_mask, b=b, S=S, pd=pd, pa=pa, rng=rng)
+        po = cfg.attn_output_dropout if train else 0.0
+        self._fw = dict(ids=input_ids, mask=attention_mask, b=b, S=S, pd=pd, pa=pa, po=po, rng=rng)
         h = A["h0"][:T]
         ops.embed_ln_fwd(input_ids, self.view(P, "embeddings.word_embeddings.weight"),
                          self.view(P, "embeddings.position_embeddings.weight"),
@@ -209,10 +210,10 @@ class FlatEncoder:
             ao = L["ao"][:T]
             torch.mm(ctx, self.view(P, pre + "attention.out_lin.weight").t(), out=ao)
             h1 = L["h1"][:T]
-            # HF DistilBERT applies no dropout to the attention output projection
+            # HF DistilBERT applies no dropout to the attention output projection; BERT-family encoders do
             ops.bias_dropout_add_ln_fwd(ao, self.view(P, pre + "attention.out_lin.bias"), h,
                                         self.view(P, pre + "sa_layer_norm.weight"), self.view(P, pre + "sa_layer_norm.bias"),
-                                        cfg.layer_norm_eps, 0.0, rng, sb + _S_ATTN,
+                                        cfg.layer_norm_eps, po, rng, sb + _S_ATTN,
                                         h1, L["pre1"][:T], L["mean1"][:T], L["rstd1"][:T])
             f1 = L["f1"][:T]
             torch.mm(h1, self.view(P, pre + "ffn.lin1.weight").t(), out=f1)
@@ -282,7 +283,7 @@ class FlatEncoder:
             # ---- attention LN + attention
             d_pre1, d_ao = ops.bias_dropout_add_ln_bwd(
                 dh1, L["pre1"][:T], self.view(P, pre + "sa_layer_norm.weight"), L["mean1"][:T], L["rstd1"][:T],
-                0.0, rng, sb + _S_ATTN,
+                fw["po"], rng, sb + _S_ATTN,
                 self.view(G, pre + "sa_layer_norm.weight"), self.view(G, pre + "sa_layer_norm.bias"),
                 self.view(G, pre + "attention.out_lin.bias"), A["dh_b"][:T], L["ao"][:T])
             torch.mm(d_ao.t(), L["ctx"][:T], out=self.view(G, pre + "attention.out_lin.weight"))

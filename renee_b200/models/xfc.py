@@ -97,7 +97,8 @@ class XFCClassifier:
         return self._scratch
 
     def step(self, X: torch.Tensor, pos_rows: torch.Tensor, pos_labels: torch.Tensor, nnz,
-             dX_out: torch.Tensor, hp, mo: float, wd: float, want_loss: bool = False, wait=None, signal=None):
+             dX_out: torch.Tensor, hp, mo: float, wd: float, want_loss: bool = False, wait=None, signal=None,
+             side_stream=None):
         """One classifier step on this rank's shard.
 
         ``X [B, D]`` in the classifier dtype; ``pos_rows/pos_labels`` int32 sorted by label (only the
@@ -106,7 +107,7 @@ class XFCClassifier:
         scale are read from ``hp``.  Returns the sparse BCE loss sum (fp32 tensor) or ``None``."""
         if X.is_cuda and self.dtype == torch.float16:
             from ..ops import cuda as cu
-            return cu.xfc_step(self, X, pos_rows, pos_labels, nnz, dX_out, hp, mo, wd, want_loss, wait, signal)
+            return cu.xfc_step(self, X, pos_rows, pos_labels, nnz, dX_out, hp, mo, wd, want_loss, wait, signal, side_stream)
         if wait is not None or signal is not None:
             raise RuntimeError("the fused collectives need the fp16 classifier kernels (--fp16xfc on a GPU)")
         return self._step_reference(X, pos_rows, pos_labels, nnz, dX_out, hp, mo, wd, want_loss)

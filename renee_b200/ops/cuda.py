@@ -244,10 +244,13 @@ def dx_splits(B: int, D: int, Lc: int) -> int:
     return max(1, min(kb, (148 + tiles - 1) // tiles))
 
 
-def xfc_step(xfc, X, pos_rows, pos_labels, nnz, dX_out, hp, mo, wd, want_loss, wait=None, signal=None):
+def xfc_step(xfc, X, pos_rows, pos_labels, nnz, dX_out, hp, mo, wd, want_loss, wait=None, signal=None,
+             side_stream=None):
     """Chunked K1 → K3 → K2 over the label shard (see :class:`renee_b200.models.xfc.XFCClassifier`).
     ``wait`` is handed to the first logits GEMM (all-gather prologue), ``signal`` to the last dX GEMM
-    (reduce-scatter epilogue)."""
+    (reduce-scatter epilogue).  With ``side_stream`` the last chunk's dW+SGD kernel — HBM-bound, and
+    nothing downstream in this step depends on it — is issued on that stream so that it overlaps the
+    compute-bound encoder backward; the caller joins the stream before the step ends."""
     B, D = X.shape
     ldG = _ld_g(B)
     sc = xfc.scratch(B)
@@ -268,7 +271,13 @@ def xfc_step(xfc, X, pos_rows, pos_labels, nnz, dX_out, hp, mo, wd, want_loss, w
             _call("rb_xfc_pos_logit_sum", _p(xfc.W), _p(X), _I(D), _p(pos_rows), _p(pos_labels), _p(nnz), _p(loss),
                   _stream())
         xfc_dx(Gt, ldG, Wc, B, dX_out, hp.buf, dx_splits(B, D, l1 - l0), signal=signal if ci == len(chunks) - 1 else None)
-        xfc_dw_sgd(Gt, ldG, X, Wc, Mc, hp.buf, mo, wd, stochastic_round=xfc.stochastic_round)
+        if side_stream is not None and ci == len(chunks) - 1:
+            main = torch.cuda.current_stream()
+            side_stream.wait_stream(main)
+            with torch.cuda.stream(side_stream):
+                xfc_dw_sgd(Gt, ldG, X, Wc, Mc, hp.buf, mo, wd, stochastic_round=xfc.stochastic_round)
+        else:
+            xfc_dw_sgd(Gt, ldG, X, Wc, Mc, hp.buf, mo, wd, stochastic_round=xfc.stochastic_round)
     return loss[0] if want_loss else None
 
 

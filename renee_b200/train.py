@@ -146,6 +146,7 @@ class XCTrainer:
         self._graphs: dict = {}
         self._graph_warm: dict = {}
         self._pending_loss = None
+        self._side_stream = None
         self.watchdog = None        # optional parallel.watchdog.Heartbeat, consulted before each step's launches
         if cfg.default_impl:
             self._init_default()
@@ -188,6 +189,8 @@ class XCTrainer:
             loss=torch.zeros(1, dtype=torch.float32, device=dev),
         )
         self._ensure_pos_capacity(max(1024, self.B * 8))
+        if self.device.type == "cuda" and cfg.fp16xfc:
+            self._side_stream = torch.cuda.Stream(device=self.device)
 
     def _ensure_pos_capacity(self, n: int) -> None:
         if n <= self.max_nnz:
@@ -294,13 +297,16 @@ class XCTrainer:
         X, wait = comm.embeddings_to_X(emb, B, cfg.dropout, self.step_rng, _S_CLS_DROPOUT, bf)
         dX, signal = comm.dx_buffer(B, bf)
         loss = self.xfc.step(X, bf["pos_rows"], bf["pos_labels"], bf["nnz"] if X.is_cuda else nnz, dX,
-                             self.hp, cfg.mo, cfg.wd1, want_loss, wait=wait, signal=signal)
+                             self.hp, cfg.mo, cfg.wd1, want_loss, wait=wait, signal=signal,
+                             side_stream=self._side_stream)
         if want_loss:
             loss = comm.allreduce_scalar(loss.reshape(1))
         de = comm.dx_to_local(dX, B, cfg.dropout, self.step_rng, _S_CLS_DROPOUT, bf)
         enc.backward(de)
         comm.optimizer_step(enc, self.hp, 0.9, 0.999, cfg.adam_eps, cfg.wd2)
         self.hp.update_scale()
+        if self._side_stream is not None:
+            torch.cuda.current_stream().wait_stream(self._side_stream)   # the overlapped dW+SGD kernel joins here
         return loss
 
     def pop_loss(self) -> float | None:

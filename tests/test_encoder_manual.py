@@ -161,3 +161,31 @@ def test_gelu_and_pool_backward():
         else:
             h[:, 0].backward(de)
         _close(ref.pool_bwd(de, mask, mode, 5, torch.float64), h.grad)
+
+
+def test_bert_and_roberta_checkpoints_map_onto_the_engine():
+    """A HF BERT / RoBERTa encoder imported through convert_bert_state_dict gives the same hidden states."""
+    from transformers import BertConfig, BertModel, RobertaConfig, RobertaModel
+    from renee_b200.models.encoder import convert_bert_state_dict
+    ids, mask = _inputs(b=4, S=10)
+    for roberta in (False, True):
+        kw = dict(vocab_size=200, hidden_size=128, num_hidden_layers=2, num_attention_heads=2, intermediate_size=256,
+                  max_position_embeddings=32, hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+        torch.manual_seed(0)
+        if roberta:
+            hf = RobertaModel(RobertaConfig(pad_token_id=1, layer_norm_eps=1e-5, **kw), add_pooling_layer=False).eval()
+            toks = torch.where(mask.bool(), ids.long().clamp(min=2), torch.ones_like(ids.long()))
+        else:
+            hf = BertModel(BertConfig(layer_norm_eps=1e-12, **kw), add_pooling_layer=False).eval()
+            toks = ids.long()
+        with torch.no_grad():
+            want = hf(input_ids=toks, attention_mask=mask.long()).last_hidden_state
+        cfg = EncoderConfig(vocab_size=200, max_position_embeddings=30 if roberta else 32, dim=128, n_layers=2, n_heads=2,
+                            hidden_dim=256, dropout=0.0, attention_dropout=0.0, layer_norm_eps=1e-5 if roberta else 1e-12,
+                            pad_token_id=1 if roberta else 0)
+        mine = DistilEncoder(cfg).eval()
+        mine.load_state_dict(convert_bert_state_dict(hf.state_dict(), roberta=roberta))
+        with torch.no_grad():
+            got = mine(toks.int(), mask)["last_hidden_state"]
+        valid = mask.bool()
+        torch.testing.assert_close(got[valid], want[valid], rtol=1e-4, atol=1e-4)
