@@ -72,6 +72,7 @@ class TrainConfig:
     cuda_graph: bool = True
     fused_comm: bool = True
     stochastic_round: bool = False
+    overlap_dw: bool = False         # issue the last dW+SGD kernel on a side stream, under the encoder backward
     out_dir: str = ""
 
     @classmethod
@@ -189,7 +190,9 @@ class XCTrainer:
             loss=torch.zeros(1, dtype=torch.float32, device=dev),
         )
         self._ensure_pos_capacity(max(1024, self.B * 8))
-        if self.device.type == "cuda" and cfg.fp16xfc:
+        if self.device.type == "cuda" and cfg.fp16xfc and cfg.overlap_dw:
+            # measured on B200 (131k-s32): 4.27 ms/step with the overlap vs 4.23 ms without at one GPU,
+            # 2.86 vs 2.67 ms at two — the kernel competes with the backward GEMMs for HBM — so it is off by default
             self._side_stream = torch.cuda.Stream(device=self.device)
 
     def _ensure_pos_capacity(self, n: int) -> None:
