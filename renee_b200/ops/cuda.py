@@ -115,17 +115,40 @@ def embed_ln_bwd(dy, ids, word, pos, gamma, mean, rstd, S, p, rng, stream, pad_i
           _F(p), _p(rng.dev), _U(stream), _stream())
 
 
+def _attention_fits(qkv, S: int, H: int, nh: int) -> bool:
+    """fp32 activations use the CUDA-core kernels, whose backward tiles exceed shared memory for long
+    sequences; those shapes are composed from library ops instead (fp32 encoders are a debugging mode)."""
+    if qkv.dtype != torch.float32:
+        return S <= 128
+    hd = H // nh
+    return S <= 128 and 2 * S * (S + 1) * 4 + 4 * S * (hd + 2) * 4 <= 227 * 1024
+
+
 def attention_fwd(qkv, bqkv, mask, nh, p, rng, stream, ctx_out, ws):
     b, S = mask.shape
     H = ctx_out.shape[1]
-    _call("rb_attention_fwd" if qkv.dtype == torch.float32 else "rb_attention_fwd_tc", _I(DT[qkv.dtype]), _p(qkv), _p(bqkv), _p(mask), _p(ctx_out), _p(ws["probs"]), _I(b), _I(S),
+    if not _attention_fits(qkv, S, H, nh):
+        from . import reference as ref
+        ctx, probs = ref.attention_fwd(qkv, bqkv, mask, nh, p, int(rng.dev.item()) & 0xFFFFFFFF, stream)
+        ctx_out.copy_(ctx)
+        ws["probs"][:b].copy_(probs)
+        return
+    _call("rb_attention_fwd" if qkv.dtype == torch.float32 else "rb_attention_fwd_tc", _I(DT[qkv.dtype]),
+          _p(qkv), _p(bqkv), _p(mask), _p(ctx_out), _p(ws["probs"]), _I(b), _I(S),
           _I(H), _I(nh), _F(p), _p(rng.dev), _U(stream), _stream())
 
 
 def attention_bwd(dctx, qkv, bqkv, mask, nh, p, rng, stream, ws, dqkv_out, dbqkv_out):
     b, S = mask.shape
     H = dctx.shape[1]
-    _call("rb_attention_bwd" if qkv.dtype == torch.float32 else "rb_attention_bwd_tc", _I(DT[qkv.dtype]), _p(dctx), _p(qkv), _p(bqkv), _p(ws["probs"]), _p(dqkv_out), _I(b),
+    if not _attention_fits(qkv, S, H, nh):
+        from . import reference as ref
+        d = ref.attention_bwd(dctx, qkv, bqkv, mask, ws["probs"][:b], nh, p, int(rng.dev.item()) & 0xFFFFFFFF, stream)
+        dqkv_out.copy_(d)
+        colsum(dqkv_out, dbqkv_out)
+        return
+    _call("rb_attention_bwd" if qkv.dtype == torch.float32 else "rb_attention_bwd_tc", _I(DT[qkv.dtype]),
+          _p(dctx), _p(qkv), _p(bqkv), _p(ws["probs"]), _p(dqkv_out), _I(b),
           _I(S), _I(H), _I(nh), _F(p), _p(rng.dev), _U(stream), _stream())
     colsum(dqkv_out, dbqkv_out)
 

@@ -12,16 +12,19 @@ all-gather of embeddings    the pooling/dropout kernel of each rank stores its f
 reduce-scatter of ``dX``    the dX GEMM accumulates into this rank's partial buffer; its last CTA
                             raises a flag on every rank; a pull kernel sums this rank's rows over
                             all partials (and applies the dropout backward)
-encoder-gradient all-reduce signal → two-shot kernel (each rank sums its 1/G slice over all ranks
-                            and stores the result into every rank's gradient buffer, detecting
-                            non-finite values) → wait; the mean's 1/G goes into the fused AdamW
+encoder gradients +         sharded optimizer: each rank sums its 1/G slice of the flat gradient over
+AdamW                       all ranks (NVLS ``multimem.ld_reduce`` or peer loads), reports non-finite
+                            values to everyone, applies AdamW to its slice of the fp32 masters and
+                            stores the new 16-bit weights into every rank's compute copy
+                            (``multimem.st`` or peer stores); a non-sharded two-shot all-reduce
+                            kernel is kept as well
 ==========================  ==================================================================
 
 Buffers that peers write or read (``X``, the ``dX`` partials) are double-buffered by step parity;
 flags carry the step number read from a device-resident counter, so the launch sequence is identical
 every step and can be replayed from a CUDA graph (two graphs, one per parity).  The symmetric
 allocations and their peer mappings come from ``torch.distributed._symmetric_memory``; NCCL remains
-for bootstrap, evaluation merges and scalars.  No NVLS/multimem and no TMA multicast is used.
+for bootstrap, evaluation merges and scalars.  No TMA multicast is used anywhere.
 
 Safety of the buffer reuse (rank r at step n+2 may overwrite what rank q read at step n): r can only
 reach step n+2's overwrite after finishing its own pull of step n+1, which waited for q's step-(n+1)
