@@ -109,6 +109,7 @@ class FlatEncoder:
         self._init_params(seed)
         self._acts = None
         self._acts_key = None
+        self._plan = None
 
     # ------------------------------------------------------------------ parameter views
     def view(self, buf: torch.Tensor, name: str) -> torch.Tensor:
@@ -243,6 +244,19 @@ class FlatEncoder:
         (overwritten, not accumulated).  ``on_layer_done(lo, hi)`` is called with the flat range
         whose gradients have just become final, so a caller can start reducing it across ranks while
         the remaining layers are still being differentiated."""
+        if self.g.is_cuda:
+            # column sums (LN gammas/betas, all bias gradients) are accumulated by the kernels and converted
+            # by ONE launch at the end of the pass instead of a serial tail inside each kernel
+            from ..ops import cuda as cu
+            if self._plan is None:
+                self._plan = cu.DeferredColumns(self.device, self.act_dtype)
+            with cu.deferred_columns(self._plan):
+                self._backward(d_emb, on_layer_done)
+            self._plan.finalize()
+        else:
+            self._backward(d_emb, on_layer_done)
+
+    def _backward(self, d_emb: torch.Tensor, on_layer_done=None) -> None:
         cfg, A, fw = self.cfg, self._acts, self._fw
         b, S, pd, pa, rng = fw["b"], fw["S"], fw["pd"], fw["pa"], fw["rng"]
         T, H = b * S, cfg.dim

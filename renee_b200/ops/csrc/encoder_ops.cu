@@ -81,6 +81,28 @@ __device__ void finalize_columns(float* acc, unsigned* counter, int n_vec, int H
   if (threadIdx.x == 0) *counter = 0u;
 }
 
+// Deferred variant: kernels called with counter == nullptr only accumulate into their own replica block;
+// one launch of this kernel at the end of the backward pass then converts ALL pending column sums
+// (LayerNorm gammas/betas, every bias gradient) and clears the accumulators — one serial tail per step
+// instead of one per kernel.  Row r of the table: {acc base, out pointer, tot, v_off, len}.
+struct ColumnJob { const float* acc; void* out; int tot; int v_off; int len; int pad; };
+
+template <typename T>
+__global__ void __launch_bounds__(256) finalize_jobs_kernel(const ColumnJob* __restrict__ jobs) {
+  const ColumnJob j = jobs[blockIdx.x];
+  float* acc = const_cast<float*>(j.acc);
+  T* out = reinterpret_cast<T*>(j.out);
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < j.len; c += gridDim.y * blockDim.x) {
+    float v[kCopies];
+#pragma unroll
+    for (int k = 0; k < kCopies; ++k) v[k] = __ldcg(acc + (size_t)k * j.tot + j.v_off + c);
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < kCopies; ++k) { s += v[k]; acc[(size_t)k * j.tot + j.v_off + c] = 0.f; }
+    out[c] = from_f<T>(s);
+  }
+}
+
 // ------------------------------------------------------------------------------------ LN forward
 template <typename T, int NV>
 __global__ void __launch_bounds__(128) bias_dropout_add_ln_fwd_kernel(
@@ -363,7 +385,7 @@ __global__ void __launch_bounds__(128, 6) ln_bwd_kernel(
     }
     red_add_f32x4(my_acc + i, t.x, t.y, t.z, t.w);
   }
-  finalize_columns<T>(acc, counter, nvec, H, dgamma, dbeta, EMBED ? nullptr : dbias);
+  if (counter != nullptr) finalize_columns<T>(acc, counter, nvec, H, dgamma, dbeta, EMBED ? nullptr : dbias);
 }
 
 // ------------------------------------------------------------------------------------ GELU
@@ -433,7 +455,7 @@ __global__ void __launch_bounds__(128) bias_gelu_bwd_kernel(const T* __restrict_
     red_add_f32x4(my_acc + col, s[0], s[1], s[2], s[3]);
     red_add_f32x4(my_acc + col + 4, s[4], s[5], s[6], s[7]);
   }
-  finalize_columns<T>(acc, counter, 1, F, dbias, nullptr, nullptr);
+  if (counter != nullptr) finalize_columns<T>(acc, counter, 1, F, dbias, nullptr, nullptr);
 }
 
 template <typename T>
@@ -461,7 +483,7 @@ __global__ void __launch_bounds__(128) colsum_kernel(const T* __restrict__ x, fl
     red_add_f32x4(my_acc + col, s[0], s[1], s[2], s[3]);
     red_add_f32x4(my_acc + col + 4, s[4], s[5], s[6], s[7]);
   }
-  finalize_columns<T>(acc, counter, 1, N, out, nullptr, nullptr);
+  if (counter != nullptr) finalize_columns<T>(acc, counter, 1, N, out, nullptr, nullptr);
 }
 
 // ------------------------------------------------------------------------------------ pooling
@@ -731,6 +753,15 @@ RB_API int rb_colsum_noalloc(int dtype, const void* x, void* out, int rows, int 
   if (rc < 1) rc = 1;
   dim3 grid(cb, rc);
   DISPATCH_T(dtype, (colsum_kernel<T><<<grid, 128, 0, st>>>((const T*)x, slot.scratch, slot.counter, (T*)out, rows, N)));
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+
+RB_API int rb_finalize_columns(int dtype, const void* jobs, int n_jobs, int max_len, cudaStream_t st) {
+  if (n_jobs < 1) return 0;
+  dim3 grid(n_jobs, (max_len + 255) / 256);
+  DISPATCH_T(dtype, (finalize_jobs_kernel<T><<<grid, 256, 0, st>>>((const ColumnJob*)jobs)));
   RB_LAUNCH_CHECK();
   return 0;
 }

@@ -98,6 +98,76 @@ def check_status(device=None) -> None:
         raise KernelError(f"device-side wait timed out: code={st[0]} block={st[1]} site={st[2]} detail={st[3]}")
 
 
+# ----------------------------------------------------------------------------- deferred column sums
+class DeferredColumns:
+    """Per-engine plan for the column reductions of a backward pass (LayerNorm gamma/beta and all bias
+    gradients).  While a plan is active, the kernels only accumulate into their own fp32 replica block and
+    skip their last-block finalize; ``finalize()`` converts everything with one launch.  Slots are keyed by
+    the output addresses (views of the flat gradient buffer, stable across steps), so after the first
+    step no allocation happens and the launch sequence can be captured in a CUDA graph."""
+
+    REPLICAS = 8
+
+    def __init__(self, device, dtype):
+        self.device, self.dtype = device, dtype
+        self.slots: dict = {}
+        self.rows: list = []
+        self.table = None
+        self.max_len = 0
+
+    def slot(self, outs, width: int) -> torch.Tensor:
+        key = tuple(0 if o is None else o.data_ptr() for o in outs) + (width,)
+        acc = self.slots.get(key)
+        if acc is None:
+            n_vec = len(outs)
+            acc = torch.zeros(self.REPLICAS * n_vec * width, dtype=torch.float32, device=self.device)
+            self.slots[key] = acc
+            for v, o in enumerate(outs):
+                if o is not None:
+                    self.rows.append((acc.data_ptr(), o.data_ptr(), n_vec * width, v * width, width))
+            self.max_len = max(self.max_len, width)
+            self.table = None
+        return acc
+
+    def finalize(self) -> None:
+        if not self.rows:
+            return
+        if self.table is None:
+            import numpy as np
+            t = np.zeros((len(self.rows), 4), dtype=np.int64)
+            for i, (a, o, tot, voff, n) in enumerate(self.rows):
+                t[i] = (a, o, tot | (voff << 32), n)      # {acc*, out*, int tot, int v_off, int len, int pad}
+            self.table = torch.from_numpy(t).to(self.device)
+        _call("rb_finalize_columns", _I(DT[self.dtype]), _p(self.table), _I(len(self.rows)), _I(self.max_len), _stream())
+
+
+_DEFER: DeferredColumns | None = None
+
+
+class deferred_columns:
+    def __init__(self, plan: DeferredColumns | None):
+        self.plan = plan
+
+    def __enter__(self):
+        global _DEFER
+        self.prev, _DEFER = _DEFER, self.plan
+        return self.plan
+
+    def __exit__(self, *exc):
+        global _DEFER
+        _DEFER = self.prev
+        return False
+
+
+def _acc_for(outs, width, default_counter):
+    """(accumulator, counter) for a column-reducing kernel: the active plan's slot (no counter → no
+    in-kernel finalize) or the shared workspace with the kernel's own counter."""
+    if _DEFER is not None:
+        return _DEFER.slot(outs, width), None
+    ws = workspace(outs[0].device if outs[0] is not None else torch.cuda.current_device())
+    return ws.colacc, default_counter(ws)
+
+
 # ----------------------------------------------------------------------------- encoder ops
 def embed_ln_fwd(ids, word, pos, gamma, beta, eps, S, p, rng, stream, out, mean, rstd):
     T, H = out.shape
@@ -107,11 +177,11 @@ def embed_ln_fwd(ids, word, pos, gamma, beta, eps, S, p, rng, stream, out, mean,
 
 def embed_ln_bwd(dy, ids, word, pos, gamma, mean, rstd, S, p, rng, stream, pad_id, dword, dpos, dgamma, dbeta):
     T, H = dy.shape
-    ws = workspace(dy.device)
+    acc, counter = _acc_for([dgamma, dbeta], H, lambda ws: ws.counters)
     dword.zero_()
     dpos.zero_()
     _call("rb_embed_ln_bwd", _I(DT[dy.dtype]), _p(dy), _p(ids), _p(word), _p(pos), _p(gamma), _p(mean), _p(rstd),
-          _p(dword), _p(dpos), _p(ws.colacc), _p(ws.counters), _p(dgamma), _p(dbeta), _I(T), _I(H), _I(S), _I(pad_id),
+          _p(dword), _p(dpos), _p(acc), _p(counter), _p(dgamma), _p(dbeta), _I(T), _I(H), _I(S), _I(pad_id),
           _F(p), _p(rng.dev), _U(stream), _stream())
 
 
@@ -161,9 +231,9 @@ def bias_dropout_add_ln_fwd(x, bias, resid, gamma, beta, eps, p, rng, stream, y_
 
 def bias_dropout_add_ln_bwd(dy, pre, gamma, mean, rstd, p, rng, stream, dgamma, dbeta, dbias, dpre_out, dbranch_out):
     T, H = dy.shape
-    ws = workspace(dy.device)
+    acc, counter = _acc_for([dgamma, dbeta, dbias], H, lambda ws: ws.counters)
     _call("rb_bias_dropout_add_ln_bwd", _I(DT[dy.dtype]), _p(dy), _p(pre), _p(gamma), _p(mean), _p(rstd), _p(dpre_out),
-          _p(dbranch_out if p > 0 else None), _p(ws.colacc), _p(ws.counters), _p(dgamma), _p(dbeta), _p(dbias),
+          _p(dbranch_out if p > 0 else None), _p(acc), _p(counter), _p(dgamma), _p(dbeta), _p(dbias),
           _I(T), _I(H), _F(p), _p(rng.dev), _U(stream), _stream())
     return (dpre_out, dbranch_out) if p > 0 else (dpre_out, dpre_out)
 
@@ -175,15 +245,15 @@ def bias_gelu_fwd(x, bias, out):
 
 def bias_gelu_bwd(da, x, bias, dbias, dx_out):
     T, Fd = x.shape
-    ws = workspace(x.device)
-    _call("rb_bias_gelu_bwd", _I(DT[x.dtype]), _p(da), _p(x), _p(bias), _p(dx_out), _p(ws.colacc), _p(ws.counters[1:]),
+    acc, counter = _acc_for([dbias], Fd, lambda ws: ws.counters[1:])
+    _call("rb_bias_gelu_bwd", _I(DT[x.dtype]), _p(da), _p(x), _p(bias), _p(dx_out), _p(acc), _p(counter),
           _p(dbias), _I(T), _I(Fd), _stream())
 
 
 def colsum(x, out):
     T, N = x.shape
-    ws = workspace(x.device)
-    _call("rb_colsum", _I(DT[x.dtype]), _p(x), _p(ws.colacc), _p(ws.counters[2:]), _p(out), _I(T), _I(N), _stream())
+    acc, counter = _acc_for([out], N, lambda ws: ws.counters[2:])
+    _call("rb_colsum", _I(DT[x.dtype]), _p(x), _p(acc), _p(counter), _p(out), _I(T), _I(N), _stream())
     return out
 
 
