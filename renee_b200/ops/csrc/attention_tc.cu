@@ -139,7 +139,8 @@ __global__ void __launch_bounds__(128) attention_fwd_tc_kernel(
 template <typename T, int HD>
 __global__ void __launch_bounds__(128) attention_bwd_tc_kernel(
     const T* __restrict__ dctx, const T* __restrict__ qkv, const T* __restrict__ bqkv, const T* __restrict__ probs,
-    T* __restrict__ dqkv, int S, int Sp, int H, int nh, float p, const int* __restrict__ seed_ptr, uint32_t stream) {
+    T* __restrict__ dqkv, int S, int Sp, int H, int nh, float p, const int* __restrict__ seed_ptr, uint32_t stream,
+    float* __restrict__ bias_acc) {
   using W = typename WT<T>::type;
   extern __shared__ __align__(128) uint8_t sm_raw[];
   constexpr int RP = HD + 8;
@@ -152,6 +153,9 @@ __global__ void __launch_bounds__(128) attention_bwd_tc_kernel(
   T* sW = sDS + Sp * PP;
   float* sF = reinterpret_cast<float*>(sW + Sp * PP);
   float* sStage = sF + Sp * FP;
+  float* sBias = sStage + 4 * 16 * 20;   // [3][HD] column sums of dQ, dK, dV = this head's q/k/v bias gradients
+  if (bias_acc != nullptr)
+    for (int i = threadIdx.x; i < 3 * HD; i += blockDim.x) sBias[i] = 0.f;
   const int h = blockIdx.x, b = blockIdx.y;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t seed = p > 0.f ? (uint32_t)(*seed_ptr) : 0u;
@@ -246,9 +250,22 @@ __global__ void __launch_bounds__(128) attention_bwd_tc_kernel(
     }
     wmma::store_matrix_sync(stage, acc, 20, wmma::mem_row_major);
     __syncwarp();
-    flush_tile<T>(stage, dqkv + (size_t)(b * S + tr * 16) * 3 * H + which * H + h * HD + td * 16, 3 * H,
-                  min(16, S - tr * 16), lane);
+    const int rows_valid = min(16, S - tr * 16);
+    flush_tile<T>(stage, dqkv + (size_t)(b * S + tr * 16) * 3 * H + which * H + h * HD + td * 16, 3 * H, rows_valid, lane);
+    if (bias_acc != nullptr && lane < 16) {
+      float cs = 0.f;
+      for (int r = 0; r < rows_valid; ++r) cs += round_through<T>(stage[r * 20 + lane]);
+      atomicAdd(&sBias[which * HD + td * 16 + lane], cs);
+    }
     __syncwarp();
+  }
+  if (bias_acc != nullptr) {
+    // the bias gradient of the packed projection is the column sum of dqkv: add this (batch, head)'s part to
+    // one of the replicas of the step-wide accumulator (converted later by the deferred finalize kernel)
+    __syncthreads();
+    float* my_acc = bias_acc + (size_t)((blockIdx.y * gridDim.x + blockIdx.x) % 8) * 3 * H;
+    for (int i = threadIdx.x; i < 3 * HD; i += blockDim.x)
+      atomicAdd(my_acc + (i / HD) * H + h * HD + (i % HD), sBias[i]);
   }
 }
 
@@ -260,7 +277,8 @@ static size_t fwd_smem(int Sp, int hd, size_t esz) {
   return (size_t)3 * Sp * (hd + 8) * esz + (size_t)Sp * (Sp + 8) * esz + (size_t)Sp * (Sp + 4) * 4 + 4 * 16 * 20 * 4;
 }
 static size_t bwd_smem(int Sp, int hd, size_t esz) {
-  return (size_t)4 * Sp * (hd + 8) * esz + (size_t)2 * Sp * (Sp + 8) * esz + (size_t)Sp * (Sp + 4) * 4 + 4 * 16 * 20 * 4;
+  return (size_t)4 * Sp * (hd + 8) * esz + (size_t)2 * Sp * (Sp + 8) * esz + (size_t)Sp * (Sp + 4) * 4 + 4 * 16 * 20 * 4 +
+         3 * (size_t)hd * 4;
 }
 
 template <typename T, int HD>
@@ -276,18 +294,20 @@ static int launch_fwd_tc(const void* qkv, const void* bqkv, const int* mask, voi
 
 template <typename T, int HD>
 static int launch_bwd_tc(const void* dctx, const void* qkv, const void* bqkv, const void* probs, void* dqkv, int b, int S,
-                         int H, int nh, float p, const int* seed, unsigned stream_id, cudaStream_t st) {
+                         int H, int nh, float p, const int* seed, unsigned stream_id, float* bias_acc, cudaStream_t st) {
   const int Sp = (S + 15) / 16 * 16;
   const size_t smem = bwd_smem(Sp, HD, sizeof(T));
   if (smem > 227 * 1024) return -6;
   auto k = attention_bwd_tc_kernel<T, HD>;
   if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -5;
   k<<<dim3(nh, b), 128, smem, st>>>((const T*)dctx, (const T*)qkv, (const T*)bqkv, (const T*)probs, (T*)dqkv, S, Sp, H, nh,
-                                    p, seed, stream_id);
+                                    p, seed, stream_id, bias_acc);
   return 0;
 }
 
-// dtype: 1 = bf16, 2 = fp16 (fp32 activations use the CUDA-core kernels of attention.cu)
+// dtype: 1 = bf16, 2 = fp16 (fp32 activations use the CUDA-core kernels of attention.cu).
+// bias_acc (backward, nullable): 8 replicas x [3H] fp32; when given, the column sums of dqkv (the q/k/v bias
+// gradients) are accumulated there so that no separate pass over dqkv is needed.
 RB_API int rb_attention_fwd_tc(int dtype, const void* qkv, const void* bqkv, const int* mask, void* ctx, void* probs,
                                int b, int S, int H, int nh, float p, const int* seed, unsigned stream_id,
                                cudaStream_t st) {
@@ -305,14 +325,14 @@ RB_API int rb_attention_fwd_tc(int dtype, const void* qkv, const void* bqkv, con
 
 RB_API int rb_attention_bwd_tc(int dtype, const void* dctx, const void* qkv, const void* bqkv, const void* probs,
                                void* dqkv, int b, int S, int H, int nh, float p, const int* seed, unsigned stream_id,
-                               cudaStream_t st) {
+                               float* bias_acc, cudaStream_t st) {
   if (S > 128 || S < 1 || H % nh || H % 8) return -4;
   const int hd = H / nh;
   int rc = -4;
-  if (dtype == RB_BF16 && hd == 64) rc = launch_bwd_tc<__nv_bfloat16, 64>(dctx, qkv, bqkv, probs, dqkv, b, S, H, nh, p, seed, stream_id, st);
-  else if (dtype == RB_BF16 && hd == 32) rc = launch_bwd_tc<__nv_bfloat16, 32>(dctx, qkv, bqkv, probs, dqkv, b, S, H, nh, p, seed, stream_id, st);
-  else if (dtype == RB_F16 && hd == 64) rc = launch_bwd_tc<__half, 64>(dctx, qkv, bqkv, probs, dqkv, b, S, H, nh, p, seed, stream_id, st);
-  else if (dtype == RB_F16 && hd == 32) rc = launch_bwd_tc<__half, 32>(dctx, qkv, bqkv, probs, dqkv, b, S, H, nh, p, seed, stream_id, st);
+  if (dtype == RB_BF16 && hd == 64) rc = launch_bwd_tc<__nv_bfloat16, 64>(dctx, qkv, bqkv, probs, dqkv, b, S, H, nh, p, seed, stream_id, bias_acc, st);
+  else if (dtype == RB_BF16 && hd == 32) rc = launch_bwd_tc<__nv_bfloat16, 32>(dctx, qkv, bqkv, probs, dqkv, b, S, H, nh, p, seed, stream_id, bias_acc, st);
+  else if (dtype == RB_F16 && hd == 64) rc = launch_bwd_tc<__half, 64>(dctx, qkv, bqkv, probs, dqkv, b, S, H, nh, p, seed, stream_id, bias_acc, st);
+  else if (dtype == RB_F16 && hd == 32) rc = launch_bwd_tc<__half, 32>(dctx, qkv, bqkv, probs, dqkv, b, S, H, nh, p, seed, stream_id, bias_acc, st);
   if (rc) return rc;
   RB_LAUNCH_CHECK();
   return 0;

@@ -300,20 +300,29 @@ xfc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 // them in place from the TMEM accumulator (16-byte accesses on the 128-byte-swizzled panels, conflict
 // free), and one thread writes both tiles back with TMA stores.  Every global access is a full-line
 // bulk copy instead of 16-byte pieces at a 1.5 KB stride.
-constexpr int kDwStages = 2;
 constexpr int kPanelBytes = kBM * 64 * 2;                        // 128 rows x 64 fp16 = 16 KB
-constexpr int kDwTileBytes = 4 * kPanelBytes;                     // 64 KB per tensor
-constexpr int kDwSmemBytes = kDwStages * kStageBytes + 2 * kDwTileBytes + 1024 + 128;
+// BN_T = widest N tile the instantiation can hold (128: two CTAs per SM, so one CTA's loads/stores overlap
+// the other's epilogue; 256: one CTA per SM), STAGES = depth of the operand ring of the short K loop.
+template <int BN_T, int STAGES> struct DwCfg {
+  static constexpr int kStage = kABytes + BN_T * kBK * 2;
+  static constexpr int kTile = (BN_T / 64) * kPanelBytes;
+  static constexpr int kSmem = STAGES * kStage + 2 * kTile + 1024 + 128;
+  static constexpr int kTmem = BN_T;
+};
 
-__global__ void __launch_bounds__(kThreads, 1)
+template <int BN_T, int STAGES>
+__global__ void __launch_bounds__(kThreads, (BN_T <= 128 ? 2 : 1))
 xfc_dw_sgd_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmM,
                       const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sW = smem + kDwStages * kStageBytes;
-  uint8_t* sM = sW + kDwTileBytes;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sM + kDwTileBytes);
+  using C = DwCfg<BN_T, STAGES>;
+  constexpr int kDwStages = STAGES;
+  constexpr int kDwStage = C::kStage;
+  uint8_t* sW = smem + kDwStages * kDwStage;
+  uint8_t* sM = sW + C::kTile;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sM + C::kTile);
   uint64_t* empty_bar = full_bar + kDwStages;
   uint64_t* tmem_full_bar = empty_bar + kDwStages;
   uint64_t* wm_full_bar = tmem_full_bar + 1;
@@ -333,7 +342,7 @@ xfc_dw_sgd_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     tc::mbar_init(wm_full_bar, 1);
     tc::fence_barrier_init();
   }
-  if (warp == 1) tc::tmem_alloc(tmem_ptr_smem, kTmemCols);
+  if (warp == 1) tc::tmem_alloc(tmem_ptr_smem, C::kTmem);
   tc::tc_fence_before();
   __syncthreads();
   tc::tc_fence_after();
@@ -350,7 +359,7 @@ xfc_dw_sgd_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const int s = kb % kDwStages;
       const uint32_t ph = (kb / kDwStages) & 1;
       if (!tc::mbar_wait(empty_bar + s, ph ^ 1, aborted, p.status, tc::SITE_EMPTY, kb)) break;
-      uint8_t* sA = smem + s * kStageBytes;
+      uint8_t* sA = smem + s * kDwStage;
       uint8_t* sB = sA + kABytes;
       tc::mbar_expect_tx(full_bar + s, kABytes + b_bytes);
       tc::tma_load_2d(sA, &tmA, full_bar + s, kb * kBK, m0);
@@ -363,7 +372,7 @@ xfc_dw_sgd_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const uint32_t ph = (kb / kDwStages) & 1;
       if (!tc::mbar_wait(full_bar + s, ph, aborted, p.status, tc::SITE_FULL, kb)) break;
       tc::tc_fence_after();
-      const uint32_t sA = tc::smem_u32(smem + s * kStageBytes);
+      const uint32_t sA = tc::smem_u32(smem + s * kDwStage);
       const uint32_t sB = sA + kABytes;
 #pragma unroll
       for (int k = 0; k < kBK / 16; ++k) {
@@ -436,7 +445,7 @@ xfc_dw_sgd_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   __syncthreads();
   if (warp == 1) {
     tc::tc_fence_after();
-    tc::tmem_dealloc(tmem_base, kTmemCols);
+    tc::tmem_dealloc(tmem_base, C::kTmem);
   }
 }
 
@@ -609,12 +618,14 @@ RB_API int rb_xfc_dx(const void* Gt, int ldG, const void* W, int Lc, int D, int 
 }
 
 // W, Mom [Lc, D] updated in place from dW = Gt X (never stored); lr read from hp[LR_XFC]
-// use_tma_tiles != 0 selects the kernel that stages the W / M tiles through shared memory with TMA.
+// use_tma_tiles: 0 = epilogue reads/writes W and M directly; 1 = TMA-staged 128-column tiles, two CTAs per SM
+// (default); 2 = TMA-staged 256-column tiles, one CTA per SM.
 RB_API int rb_xfc_dw_sgd(const void* Gt, int ldG, const void* X, int B, void* W, void* Mom, int Lc, int D,
                          const float* hp, float mo, float wd, int use_tma_tiles, int stochastic_round, int* status,
                          cudaStream_t st) {
   if (D % 8 || ldG % 8 || Lc < 1) return -3;
-  const int BN = D >= 256 ? 256 : round_up(D, 64);
+  const int bn_max = (use_tma_tiles == 1) ? 128 : 256;
+  const int BN = D >= bn_max ? bn_max : round_up(D, 64);
   CUtensorMap ta, tb;
   int rc = tc::make_tmap_2d(&ta, Gt, Lc, ldG, ldG, 64, kBM, false);
   if (rc) return rc;
@@ -632,13 +643,25 @@ RB_API int rb_xfc_dw_sgd(const void* Gt, int ldG, const void* X, int B, void* W,
     if (rc) return rc;
     rc = tc::make_tmap_2d(&tm, Mom, Lc, D, D, 64, kBM, false);
     if (rc) return rc;
-    static bool attr_set = false;
-    if (!attr_set) {
-      if (cudaFuncSetAttribute(xfc_dw_sgd_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDwSmemBytes) != cudaSuccess)
-        return -5;
-      attr_set = true;
+    if (use_tma_tiles == 2) {
+      using C = DwCfg<256, 2>;
+      static bool attr_set = false;
+      if (!attr_set) {
+        if (cudaFuncSetAttribute(xfc_dw_sgd_tma_kernel<256, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem) != cudaSuccess)
+          return -5;
+        attr_set = true;
+      }
+      xfc_dw_sgd_tma_kernel<256, 2><<<grid, kThreads, C::kSmem, st>>>(ta, tb, tw, tm, p);
+    } else {
+      using C = DwCfg<128, 1>;
+      static bool attr_set = false;
+      if (!attr_set) {
+        if (cudaFuncSetAttribute(xfc_dw_sgd_tma_kernel<128, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem) != cudaSuccess)
+          return -5;
+        attr_set = true;
+      }
+      xfc_dw_sgd_tma_kernel<128, 1><<<grid, kThreads, C::kSmem, st>>>(ta, tb, tw, tm, p);
     }
-    xfc_dw_sgd_tma_kernel<<<grid, kThreads, kDwSmemBytes, st>>>(ta, tb, tw, tm, p);
   } else {
     rc = launch_gemm<MODE_DW>(ta, tb, p, grid, st);
     if (rc) return rc;

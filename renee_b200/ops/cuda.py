@@ -217,10 +217,17 @@ def attention_bwd(dctx, qkv, bqkv, mask, nh, p, rng, stream, ws, dqkv_out, dbqkv
         dqkv_out.copy_(d)
         colsum(dqkv_out, dbqkv_out)
         return
-    _call("rb_attention_bwd" if qkv.dtype == torch.float32 else "rb_attention_bwd_tc", _I(DT[qkv.dtype]),
-          _p(dctx), _p(qkv), _p(bqkv), _p(ws["probs"]), _p(dqkv_out), _I(b),
-          _I(S), _I(H), _I(nh), _F(p), _p(rng.dev), _U(stream), _stream())
-    colsum(dqkv_out, dbqkv_out)
+    if qkv.dtype == torch.float32:
+        _call("rb_attention_bwd", _I(DT[qkv.dtype]), _p(dctx), _p(qkv), _p(bqkv), _p(ws["probs"]), _p(dqkv_out), _I(b),
+              _I(S), _I(H), _I(nh), _F(p), _p(rng.dev), _U(stream), _stream())
+        colsum(dqkv_out, dbqkv_out)
+        return
+    # with a deferred-columns plan active the kernel also accumulates the q/k/v bias gradients
+    acc = _DEFER.slot([dbqkv_out], 3 * H) if _DEFER is not None else None
+    _call("rb_attention_bwd_tc", _I(DT[qkv.dtype]), _p(dctx), _p(qkv), _p(bqkv), _p(ws["probs"]), _p(dqkv_out), _I(b),
+          _I(S), _I(H), _I(nh), _F(p), _p(rng.dev), _U(stream), _p(acc), _stream())
+    if acc is None:
+        colsum(dqkv_out, dbqkv_out)
 
 
 def bias_dropout_add_ln_fwd(x, bias, resid, gamma, beta, eps, p, rng, stream, y_out, pre_out, mean, rstd):
@@ -327,7 +334,7 @@ def xfc_dw_sgd(Gt, ldG, X, W, M, hp_buf, mo, wd, tma_tiles=True, stochastic_roun
     B = X.shape[0]
     ws = workspace(W.device)
     _call("rb_xfc_dw_sgd", _p(Gt), _I(ldG), _p(X), _I(B), _p(W), _p(M), _I(Lc), _I(D), _p(hp_buf), _F(mo), _F(wd),
-          _I(1 if tma_tiles else 0), _I(1 if stochastic_round else 0), _p(ws.status), _stream())
+          _I(int(tma_tiles)), _I(1 if stochastic_round else 0), _p(ws.status), _stream())
 
 
 def dx_splits(B: int, D: int, Lc: int) -> int:

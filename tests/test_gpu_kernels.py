@@ -146,6 +146,15 @@ def test_attention(dt, S, nh, H, p):
     dr = ref.attention_bwd(dctx.float(), qkv.float(), bq.float(), mask, ws["probs"].float(), nh, p, rng.seed, 4)
     torch.testing.assert_close(dqkv.float(), dr, rtol=3e-2, atol=3e-2)
     torch.testing.assert_close(dbq.float(), dr.sum(0), rtol=5e-2, atol=2.5e-1)
+    # deferred mode: the kernel accumulates the bias gradient itself, one finalize launch converts it
+    plan = cu().DeferredColumns(dev(), dt)
+    dqkv2, dbq2 = torch.empty_like(qkv), torch.full((3 * H,), 9.0, device=dev(), dtype=dt)
+    for _ in range(2):          # twice: the accumulators must come back zeroed
+        with cu().deferred_columns(plan):
+            ops.attention_bwd(dctx, qkv, bq, mask, nh, p, rng, 4, ws, dqkv2, dbq2)
+        plan.finalize()
+        torch.testing.assert_close(dqkv2.float(), dqkv.float(), rtol=0, atol=0)
+        torch.testing.assert_close(dbq2.float(), dqkv.float().sum(0), rtol=3e-2, atol=1.5e-1)
 
 
 def test_adamw_gradcheck_scaler():
@@ -329,6 +338,10 @@ def test_xfc_dw_sgd_both_kernels_agree_and_stochastic_rounding_is_unbiased():
     cu().xfc_dw_sgd(Gt, B, X, W2, M2, hp.buf, 0.9, 1e-3, tma_tiles=False)
     cu().check_status()
     assert torch.equal(W1, W2) and torch.equal(M1, M2)
+    W3, M3 = W.clone(), M.clone()
+    cu().xfc_dw_sgd(Gt, B, X, W3, M3, hp.buf, 0.9, 1e-3, tma_tiles=2)      # 256-column tiles, one CTA per SM
+    cu().check_status()
+    assert torch.equal(W1, W3) and torch.equal(M1, M3)
     # updates of a tenth of an ulp: round-to-nearest loses them all, stochastic rounding keeps their mean
     Wc = torch.ones(Lc, D, dtype=torch.float16, device=dev())
     Mc = torch.full((Lc, D), 1.0, dtype=torch.float16, device=dev())
