@@ -27,7 +27,6 @@ from __future__ import annotations
 
 import torch
 
-from .. import ops
 from ..ops import reference as ref
 
 INIT_CHUNK = 1 << 16

@@ -21,7 +21,7 @@ import os
 import random
 import sys
 import time
-from dataclasses import dataclass, field, asdict
+from dataclasses import dataclass
 
 import numpy as np
 import torch
@@ -37,7 +37,7 @@ from .optim.schedule import CosineWarmupSchedule
 from .ops.rng import DropoutRNG
 from .parallel.collectives import TorchCollectives
 from .parallel.dist import DistContext
-from .utils.sharding import LabelSharding, batch_row_range
+from .utils.sharding import LabelSharding
 
 LOSS_SAMPLE_FREQ = 100   # dl_base.py:144
 _S_CLS_DROPOUT = 5
