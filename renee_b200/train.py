@@ -312,6 +312,37 @@ class XCTrainer:
             torch.cuda.current_stream().wait_stream(self._side_stream)   # the overlapped dW+SGD kernel joins here
         return loss
 
+    def profile_step(self, batch: XCBatch) -> dict:
+        """Runs one optimized step eagerly with device-side timers around its phases and returns
+        ``{phase: milliseconds}`` (it is a real training step: weights are updated)."""
+        from .utils.timing import PhaseTimer
+        cfg, bf, enc, comm = self.cfg, self.buf, self.encoder, self.comm
+        tm = PhaseTimer(self.device)
+        with tm.phase("h2d"):
+            self.stage_batch(batch)
+        b, B, nnz, _ = self._staged
+        comm.host_begin()
+        with tm.phase("encoder_forward"):
+            comm.device_begin()
+            emb = enc.forward(bf["ids"][:b], bf["mask"][:b], self.step_rng, train=True)
+        with tm.phase("allgather_classifier"):
+            X, wait = comm.embeddings_to_X(emb, B, cfg.dropout, self.step_rng, _S_CLS_DROPOUT, bf)
+            dX, signal = comm.dx_buffer(B, bf)
+            self.xfc.step(X, bf["pos_rows"], bf["pos_labels"], bf["nnz"] if X.is_cuda else nnz, dX, self.hp, cfg.mo,
+                          cfg.wd1, False, wait=wait, signal=signal)
+        with tm.phase("reduce_scatter"):
+            de = comm.dx_to_local(dX, B, cfg.dropout, self.step_rng, _S_CLS_DROPOUT, bf)
+        with tm.phase("encoder_backward"):
+            enc.backward(de)
+        with tm.phase("optimizer"):
+            comm.optimizer_step(enc, self.hp, 0.9, 0.999, cfg.adam_eps, cfg.wd2)
+            self.hp.update_scale()
+        self.count += 1
+        self.rng.advance()
+        self.xfc_sched.step()
+        self.tf_sched.step()
+        return tm.result_ms()
+
     def pop_loss(self) -> float | None:
         """Normalised sampled loss of the most recent sampling step (synchronises)."""
         pend = getattr(self, "_pending_loss", None)
@@ -377,7 +408,10 @@ class XCTrainer:
     # ------------------------------------------------------------------ epoch loop
     def fit(self, loader, evaluator=None, log=print) -> None:
         from .checkpoint import maybe_resume, save_checkpoint
+        from .utils.logging import JsonlLogger
         cfg = self.cfg
+        jl = JsonlLogger(os.path.join(self.out_dir, f"{self.name}_log.jsonl") if self.out_dir else None,
+                         enabled=self.ctx.is_main, echo=None)
         if cfg.checkpoint_resume:
             prev = maybe_resume(self, cfg.checkpoint_resume)
             if prev is not None:
@@ -405,6 +439,9 @@ class XCTrainer:
                 log(f"Scale:  {self.hp.get_scale()}")
                 log(f"epoch {epoch}: {n_rows / max(time.time() - t0, 1e-9):.1f} samples/s (wall)")
                 sys.stdout.flush()
+                jl.log("epoch", epoch=epoch, mean_loss=mean_loss, loss_scale=self.hp.get_scale(), steps=self.count,
+                       optimizer_steps=int(self.hp.buf[HP.ADAM_STEP]), rows=n_rows,
+                       samples_per_s=n_rows / max(time.time() - t0, 1e-9), world_size=self.G)
             last = epoch == cfg.epochs - 1
             if evaluator is not None and (((epoch + 1) % cfg.evaluation_epochs == 0) or last):
                 evaluator(self, epoch, mean_loss, self.out_dir, self.name)

@@ -1,0 +1,59 @@
+"""Run log, phase timer, checkpoint consolidation / re-sharding."""
+import os
+
+import numpy as np
+import torch
+
+from renee_b200.utils.logging import JsonlLogger, read_jsonl
+from renee_b200.utils.reshard import consolidate, reshard
+from renee_b200.utils.sharding import shard_labels
+from renee_b200.utils.timing import PhaseTimer
+
+
+def test_jsonl_logger_roundtrip(tmp_path):
+    p = str(tmp_path / "run" / "x_log.jsonl")
+    seen = []
+    jl = JsonlLogger(p, echo=seen.append)
+    jl("hello")
+    jl.log("epoch", epoch=1, mean_loss=np.float32(0.5))
+    recs = read_jsonl(p)
+    assert seen == ["hello"] and [r["kind"] for r in recs] == ["message", "epoch"] and recs[1]["mean_loss"] == 0.5
+    JsonlLogger(None).log("epoch", epoch=0)          # disabled logger is a no-op
+
+
+def test_phase_timer_cpu():
+    tm = PhaseTimer("cpu")
+    with tm.phase("a"):
+        torch.ones(1000).sum()
+    with tm.phase("a"):
+        pass
+    with tm.phase("b"):
+        pass
+    r = tm.result_ms()
+    assert set(r) == {"a", "b"} and r["a"] >= 0
+
+
+def test_consolidate_and_reshard_follow_the_padding_rule():
+    L, D = 1003, 8
+    full_W = torch.arange(L * D, dtype=torch.float32).view(L, D)
+    enc = {"embed.0.transformer.embeddings.LayerNorm.weight": torch.ones(D)}
+    src = reshard({"xfc_weight": full_W, **enc}, L, 8)
+    sh8 = shard_labels(L, 8)
+    assert all(s["xfc_weight"].shape == (sh8.labels_per_rank, D) for s in src)
+    assert float(src[-1]["xfc_weight"][-1].abs().sum()) == 0.0       # padded rows are zero
+    back = consolidate(src, L)
+    assert torch.equal(back["xfc_weight"], full_W) and "embed.0.transformer.embeddings.LayerNorm.weight" in back
+    two = reshard(back, L, 2)
+    assert two[0]["xfc_weight"].shape[0] == shard_labels(L, 2).labels_per_rank
+    assert torch.equal(torch.cat([t["xfc_weight"] for t in two])[:L], full_W)
+
+
+def test_profile_step_and_epoch_log(tmp_path):
+    from tests.test_train_equivalence import make
+    tr, loader = make(False, tmp_path, epochs=1)
+    batch = next(iter(loader.epoch(0)))
+    ph = tr.profile_step(batch)
+    assert {"encoder_forward", "allgather_classifier", "reduce_scatter", "encoder_backward", "optimizer"} <= set(ph)
+    tr.fit(loader, log=lambda *a: None)
+    recs = read_jsonl(os.path.join(str(tmp_path), "renee-exp_log.jsonl"))
+    assert recs[-1]["kind"] == "epoch" and recs[-1]["rows"] == 64
