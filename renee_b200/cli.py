@@ -144,8 +144,15 @@ def start(local_device: int, ngpus_per_node: int, args) -> None:
     cfg.out_dir = os.path.join(args.results_dir, dataset_name, args.expname)
     comm = None
     if G > 1 and ctx.device.type == "cuda" and args.fused_comm and not args.default_impl:
-        from .parallel.fused import PeerCollectives
-        comm = PeerCollectives(ctx)
+        import socket
+        import torch.distributed as dist
+        hosts = [None] * G
+        dist.all_gather_object(hosts, socket.gethostname())
+        if len(set(hosts)) == 1:
+            from .parallel.fused import PeerCollectives
+            comm = PeerCollectives(ctx)          # NVLink peer memory: all ranks on one node
+        elif ctx.is_main:
+            print("ranks span several nodes: using the NCCL collectives (peer-memory kernels are intra-node)")
     trainer = XCTrainer(cfg, enc_cfg, sharding, ctx, steps_per_epoch=len(trn_loader), comm=comm)
     if G > 1 and args.heartbeat_timeout > 0:
         import torch.distributed as dist

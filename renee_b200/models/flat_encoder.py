@@ -110,6 +110,7 @@ class FlatEncoder:
         self._acts = None
         self._acts_key = None
         self._plan = None
+        self.generation = 0
 
     # ------------------------------------------------------------------ parameter views
     def view(self, buf: torch.Tensor, name: str) -> torch.Tensor:
@@ -180,6 +181,7 @@ class FlatEncoder:
                           dh=e(T, H), dh_b=e(T, H), dqkv=e(T, 3 * H), dctx=e(T, H), df1=e(T, Fd), da1=e(T, Fd),
                           emb=e(b, self.out_dims, dtype=torch.float32))
         self._acts_key = key
+        self.generation += 1      # activation addresses changed: graphs captured over the old ones are stale
 
     # ------------------------------------------------------------------ forward
     def forward(self, input_ids: torch.Tensor, attention_mask: torch.Tensor, rng, train: bool = True) -> torch.Tensor:

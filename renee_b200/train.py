@@ -146,6 +146,7 @@ class XCTrainer:
         self.loss_steps = 0
         self._graphs: dict = {}
         self._graph_warm: dict = {}
+        self._graph_generation = -1
         self._pending_loss = None
         self._side_stream = None
         self.watchdog = None        # optional parallel.watchdog.Heartbeat, consulted before each step's launches
@@ -244,6 +245,9 @@ class XCTrainer:
         key = (b, B, self.comm.parity)
         use_graph = (self.cfg.cuda_graph and self.device.type == "cuda" and not want_loss
                      and getattr(self.comm, "graph_safe", self.G == 1))
+        if use_graph and self._graph_generation != self.encoder.generation:
+            self._graphs, self._graph_warm = {}, {}          # the encoder re-allocated its activations
+            self._graph_generation = self.encoder.generation
         if use_graph:
             g = self._graphs.get(key)
             if g is not None:
