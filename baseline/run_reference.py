@@ -85,7 +85,7 @@ def _wait_for(path, timeout=600.0):
 
 def run_reference(args, c) -> dict | None:
     if not (os.path.exists(os.path.join(REF, "main.py")) and os.path.exists(os.path.join(REF, "dl_base.py"))):
-        return {"impl": "reference", "unavailable": "baseline/_ref is not installed (see DESIGN.md: reference arm)"}
+        return {"impl": "reference", "unavailable": "the reference is not installed under baseline/_ref"}
     import torch
     if not torch.cuda.is_available():
         return {"impl": "reference", "unavailable": "no CUDA device"}

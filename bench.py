@@ -38,7 +38,7 @@ CONFIGS = {
 }
 
 
-# Reference samples/s measured on the same box type with `--impl reference` (BASELINE.md section 2)
+# Reference samples/s measured on the same box type with `--impl reference`
 REFERENCE_MEASURED = {("131k-s32", 1): 22446.22, ("131k-s32", 2): 20270.47}
 
 
