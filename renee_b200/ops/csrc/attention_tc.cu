@@ -30,7 +30,7 @@ __device__ __forceinline__ void flush_tile(const float* stage, T* dst, int ld, i
 }
 
 template <typename T, int HD>
-__global__ void __launch_bounds__(128) attention_fwd_tc_kernel(
+__global__ void __launch_bounds__(256) attention_fwd_tc_kernel(
     const T* __restrict__ qkv, const T* __restrict__ bqkv, const int* __restrict__ mask, T* __restrict__ ctx,
     T* __restrict__ probs, int S, int Sp, int H, int nh, float p, const int* __restrict__ seed_ptr, uint32_t stream) {
   using W = typename WT<T>::type;
@@ -42,9 +42,9 @@ __global__ void __launch_bounds__(128) attention_fwd_tc_kernel(
   T* sV = sK + Sp * RP;
   T* sP = sV + Sp * RP;
   float* sS = reinterpret_cast<float*>(sP + Sp * PP);
-  float* sStage = sS + Sp * FP;        // [4 warps][16][20]
+  float* sStage = sS + Sp * FP;        // [warps][16][20]
   const int h = blockIdx.x, b = blockIdx.y;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
   const uint32_t seed = p > 0.f ? (uint32_t)(*seed_ptr) : 0u;
   const float inv_keep = p > 0.f ? 1.f / (1.f - p) : 1.f;
   const float scale = rsqrtf((float)HD);
@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(128) attention_fwd_tc_kernel(
   }
   __syncthreads();
   const int nt = Sp / 16;
-  for (int t = warp; t < nt * nt; t += 4) {
+  for (int t = warp; t < nt * nt; t += nw) {
     const int ti = t / nt, tj = t % nt;
     wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
     wmma::fill_fragment(acc, 0.f);
@@ -81,7 +81,7 @@ __global__ void __launch_bounds__(128) attention_fwd_tc_kernel(
     wmma::store_matrix_sync(sS + ti * 16 * FP + tj * 16, acc, FP, wmma::mem_row_major);
   }
   __syncthreads();
-  for (int i = warp; i < Sp; i += 4) {
+  for (int i = warp; i < Sp; i += nw) {
     float sc[4];
     float mx = -1e30f;
 #pragma unroll
@@ -118,7 +118,7 @@ __global__ void __launch_bounds__(128) attention_fwd_tc_kernel(
   }
   __syncthreads();
   float* stage = sStage + warp * 16 * 20;
-  for (int t = warp; t < nt * (HD / 16); t += 4) {
+  for (int t = warp; t < nt * (HD / 16); t += nw) {
     const int ti = t / (HD / 16), td = t % (HD / 16);
     wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
     wmma::fill_fragment(acc, 0.f);
@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(128) attention_fwd_tc_kernel(
 }
 
 template <typename T, int HD>
-__global__ void __launch_bounds__(128) attention_bwd_tc_kernel(
+__global__ void __launch_bounds__(256) attention_bwd_tc_kernel(
     const T* __restrict__ dctx, const T* __restrict__ qkv, const T* __restrict__ bqkv, const T* __restrict__ probs,
     T* __restrict__ dqkv, int S, int Sp, int H, int nh, float p, const int* __restrict__ seed_ptr, uint32_t stream,
     float* __restrict__ bias_acc) {
@@ -153,11 +153,11 @@ __global__ void __launch_bounds__(128) attention_bwd_tc_kernel(
   T* sW = sDS + Sp * PP;
   float* sF = reinterpret_cast<float*>(sW + Sp * PP);
   float* sStage = sF + Sp * FP;
-  float* sBias = sStage + 4 * 16 * 20;   // [3][HD] column sums of dQ, dK, dV = this head's q/k/v bias gradients
+  float* sBias = sStage + 8 * 16 * 20;   // [3][HD] column sums of dQ, dK, dV = this head's q/k/v bias gradients
   if (bias_acc != nullptr)
     for (int i = threadIdx.x; i < 3 * HD; i += blockDim.x) sBias[i] = 0.f;
   const int h = blockIdx.x, b = blockIdx.y;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
   const uint32_t seed = p > 0.f ? (uint32_t)(*seed_ptr) : 0u;
   const float inv_keep = p > 0.f ? 1.f / (1.f - p) : 1.f;
   const float scale = rsqrtf((float)HD);
@@ -181,7 +181,7 @@ __global__ void __launch_bounds__(128) attention_bwd_tc_kernel(
   __syncthreads();
   const int nt = Sp / 16;
   // dP = dO V^T
-  for (int t = warp; t < nt * nt; t += 4) {
+  for (int t = warp; t < nt * nt; t += nw) {
     const int ti = t / nt, tj = t % nt;
     wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
     wmma::fill_fragment(acc, 0.f);
@@ -197,7 +197,7 @@ __global__ void __launch_bounds__(128) attention_bwd_tc_kernel(
   }
   __syncthreads();
   // rows of dS and of the dropped-out weights
-  for (int i = warp; i < Sp; i += 4) {
+  for (int i = warp; i < Sp; i += nw) {
     const size_t prow = ((size_t)(b * nh + h) * S + i) * S;
     float pr[4], dp[4], m[4];
     float dot = 0.f;
@@ -227,7 +227,7 @@ __global__ void __launch_bounds__(128) attention_bwd_tc_kernel(
   float* stage = sStage + warp * 16 * 20;
   const int ntd = HD / 16;
   // 3 * nt * ntd output tiles: which = 0 dQ = dS K, 1 dK = dS^T Q, 2 dV = P~^T dO
-  for (int t = warp; t < 3 * nt * ntd; t += 4) {
+  for (int t = warp; t < 3 * nt * ntd; t += nw) {
     const int which = t / (nt * ntd);
     const int tr = (t % (nt * ntd)) / ntd, td = t % ntd;
     wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
@@ -274,10 +274,10 @@ __global__ void __launch_bounds__(128) attention_bwd_tc_kernel(
 using namespace rb;
 
 static size_t fwd_smem(int Sp, int hd, size_t esz) {
-  return (size_t)3 * Sp * (hd + 8) * esz + (size_t)Sp * (Sp + 8) * esz + (size_t)Sp * (Sp + 4) * 4 + 4 * 16 * 20 * 4;
+  return (size_t)3 * Sp * (hd + 8) * esz + (size_t)Sp * (Sp + 8) * esz + (size_t)Sp * (Sp + 4) * 4 + 8 * 16 * 20 * 4;
 }
 static size_t bwd_smem(int Sp, int hd, size_t esz) {
-  return (size_t)4 * Sp * (hd + 8) * esz + (size_t)2 * Sp * (Sp + 8) * esz + (size_t)Sp * (Sp + 4) * 4 + 4 * 16 * 20 * 4 +
+  return (size_t)4 * Sp * (hd + 8) * esz + (size_t)2 * Sp * (Sp + 8) * esz + (size_t)Sp * (Sp + 4) * 4 + 8 * 16 * 20 * 4 +
          3 * (size_t)hd * 4;
 }
 
@@ -288,7 +288,8 @@ static int launch_fwd_tc(const void* qkv, const void* bqkv, const int* mask, voi
   const size_t smem = fwd_smem(Sp, HD, sizeof(T));
   auto k = attention_fwd_tc_kernel<T, HD>;
   if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -5;
-  k<<<dim3(nh, b), 128, smem, st>>>((const T*)qkv, (const T*)bqkv, mask, (T*)ctx, (T*)probs, S, Sp, H, nh, p, seed, stream_id);
+  // 8 warps per (batch, head) for long sequences (64+ tiles of work per product), 4 for short ones
+  k<<<dim3(nh, b), Sp >= 64 ? 256 : 128, smem, st>>>((const T*)qkv, (const T*)bqkv, mask, (T*)ctx, (T*)probs, S, Sp, H, nh, p, seed, stream_id);
   return 0;
 }
 
@@ -300,7 +301,7 @@ static int launch_bwd_tc(const void* dctx, const void* qkv, const void* bqkv, co
   if (smem > 227 * 1024) return -6;
   auto k = attention_bwd_tc_kernel<T, HD>;
   if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -5;
-  k<<<dim3(nh, b), 128, smem, st>>>((const T*)dctx, (const T*)qkv, (const T*)bqkv, (const T*)probs, (T*)dqkv, S, Sp, H, nh,
+  k<<<dim3(nh, b), Sp >= 64 ? 256 : 128, smem, st>>>((const T*)dctx, (const T*)qkv, (const T*)bqkv, (const T*)probs, (T*)dqkv, S, Sp, H, nh,
                                     p, seed, stream_id, bias_acc);
   return 0;
 }
