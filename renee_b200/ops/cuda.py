@@ -194,6 +194,14 @@ def _attention_fits(qkv, S: int, H: int, nh: int) -> bool:
     return S <= 128 and 2 * S * (S + 1) * 4 + 4 * S * (hd + 2) * 4 <= 227 * 1024
 
 
+def _attention_entry(direction: str, H: int, nh: int) -> str:
+    """16-bit activations: the register-resident kernels for head dim 64 (scores stay in MMA fragments), the
+    shared-memory tile kernels otherwise (head dim 32) or when ``RENEE_B200_ATTENTION=tiles`` asks for them."""
+    if H // nh == 64 and os.environ.get("RENEE_B200_ATTENTION", "") != "tiles":
+        return f"rb_attention_{direction}_mma"
+    return f"rb_attention_{direction}_tc"
+
+
 def attention_fwd(qkv, bqkv, mask, nh, p, rng, stream, ctx_out, ws):
     b, S = mask.shape
     H = ctx_out.shape[1]
@@ -203,7 +211,7 @@ def attention_fwd(qkv, bqkv, mask, nh, p, rng, stream, ctx_out, ws):
         ctx_out.copy_(ctx)
         ws["probs"][:b].copy_(probs)
         return
-    _call("rb_attention_fwd" if qkv.dtype == torch.float32 else "rb_attention_fwd_tc", _I(DT[qkv.dtype]),
+    _call("rb_attention_fwd" if qkv.dtype == torch.float32 else _attention_entry("fwd", H, nh), _I(DT[qkv.dtype]),
           _p(qkv), _p(bqkv), _p(mask), _p(ctx_out), _p(ws["probs"]), _I(b), _I(S),
           _I(H), _I(nh), _F(p), _p(rng.dev), _U(stream), _stream())
 
@@ -224,7 +232,7 @@ def attention_bwd(dctx, qkv, bqkv, mask, nh, p, rng, stream, ws, dqkv_out, dbqkv
         return
     # with a deferred-columns plan active the kernel also accumulates the q/k/v bias gradients
     acc = _DEFER.slot([dbqkv_out], 3 * H) if _DEFER is not None else None
-    _call("rb_attention_bwd_tc", _I(DT[qkv.dtype]), _p(dctx), _p(qkv), _p(bqkv), _p(ws["probs"]), _p(dqkv_out), _I(b),
+    _call(_attention_entry("bwd", H, nh), _I(DT[qkv.dtype]), _p(dctx), _p(qkv), _p(bqkv), _p(ws["probs"]), _p(dqkv_out), _I(b),
           _I(S), _I(H), _I(nh), _F(p), _p(rng.dev), _U(stream), _p(acc), _stream())
     if acc is None:
         colsum(dqkv_out, dbqkv_out)

@@ -122,10 +122,11 @@ def test_bias_gelu_colsum_pool_dropout(dt):
     torch.testing.assert_close(o2, ref.dropout_bwd(e, 0.85, rng.seed, 5))
 
 
-@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("S,nh,H,p", [(32, 12, 768, 0.1), (128, 2, 128, 0.0), (20, 12, 384, 0.2)])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32, torch.float16])
+@pytest.mark.parametrize("S,nh,H,p", [(32, 12, 768, 0.1), (128, 2, 128, 0.0), (20, 12, 384, 0.2), (45, 4, 256, 0.1),
+                                      (64, 2, 128, 0.3), (100, 3, 192, 0.1)])
 def test_attention(dt, S, nh, H, p):
-    if dt == torch.float32 and S == 128:
+    if dt == torch.float32 and S >= 100:
         pytest.skip("fp32 tiles of S=128 exceed shared memory; the engine composes library ops there")
     torch.manual_seed(0)
     b = 3
