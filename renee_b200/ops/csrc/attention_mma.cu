@@ -164,31 +164,45 @@ __device__ __forceinline__ void write_rows(const float (&out)[HD / 8][4], T* dst
 }
 
 // Stages (q + bq, k + bk, v + bv [, dO]) of one (batch, head) as [SP][RP] tiles; rows >= S are zero.
+// The CTA has SP * 2 threads and the tiles SP * 8 segments of 8 columns, so a thread owns the same 8 columns of
+// four rows: all of its global loads are issued before the first one is used.
 template <typename T, int SP, bool WITH_DO>
 __device__ __forceinline__ void stage_operands(const T* __restrict__ qkv, const T* __restrict__ bqkv, const T* __restrict__ dctx,
                                                T* sQ, T* sK, T* sV, T* sDO, int b, int h, int S, int H) {
-  for (int i = threadIdx.x; i < SP * (HD / 8); i += blockDim.x) {
-    const int s = i / (HD / 8), d = (i % (HD / 8)) * 8;
-    float q[8], k[8], v[8], g[8];
+  constexpr int ROWS_PER_PASS = SP * 2 / 8;
+  const int d = (threadIdx.x & 7) * 8, s0 = threadIdx.x >> 3;
+  Raw8<T> rq[4], rk[4], rv[4], rg[4];
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int s = s0 + it * ROWS_PER_PASS;
     if (s < S) {
       const size_t base = (size_t)(b * S + s) * 3 * H + h * HD + d;
-      float bq[8], bk[8], bv[8];
-      load8(qkv + base, q); load8(qkv + base + H, k); load8(qkv + base + 2 * H, v);
-      load8(bqkv + h * HD + d, bq); load8(bqkv + H + h * HD + d, bk); load8(bqkv + 2 * H + h * HD + d, bv);
-      if constexpr (WITH_DO) load8(dctx + (size_t)(b * S + s) * H + h * HD + d, g);
+      rq[it] = load_raw8(qkv + base); rk[it] = load_raw8(qkv + base + H); rv[it] = load_raw8(qkv + base + 2 * H);
+      if constexpr (WITH_DO) rg[it] = load_raw8(dctx + (size_t)(b * S + s) * H + h * HD + d);
+    }
+  }
+  float bq[8], bk[8], bv[8];
+  load8(bqkv + h * HD + d, bq); load8(bqkv + H + h * HD + d, bk); load8(bqkv + 2 * H + h * HD + d, bv);
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int s = s0 + it * ROWS_PER_PASS;
+    float q[8], k[8], v[8];
+    if (s < S) {
+      unpack8(rq[it], q); unpack8(rk[it], k); unpack8(rv[it], v);
 #pragma unroll
       for (int j = 0; j < 8; ++j) { q[j] += bq[j]; k[j] += bk[j]; v[j] += bv[j]; }
+      if constexpr (WITH_DO) *reinterpret_cast<uint4*>(sDO + s * RP + d) = rg[it].v;
     } else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { q[j] = 0.f; k[j] = 0.f; v[j] = 0.f; g[j] = 0.f; }
+      for (int j = 0; j < 8; ++j) { q[j] = 0.f; k[j] = 0.f; v[j] = 0.f; }
+      if constexpr (WITH_DO) *reinterpret_cast<uint4*>(sDO + s * RP + d) = make_uint4(0u, 0u, 0u, 0u);
     }
     store8(sQ + s * RP + d, q); store8(sK + s * RP + d, k); store8(sV + s * RP + d, v);
-    if constexpr (WITH_DO) store8(sDO + s * RP + d, g);
   }
 }
 
 template <typename T, int SP>
-__global__ void __launch_bounds__(SP * 2) attention_fwd_mma_kernel(
+__global__ void __launch_bounds__(SP * 2, SP == 128 ? 2 : 1) attention_fwd_mma_kernel(
     const T* __restrict__ qkv, const T* __restrict__ bqkv, const int* __restrict__ mask, T* __restrict__ ctx,
     T* __restrict__ probs, int S, int H, int nh, float p, const int* __restrict__ seed_ptr, uint32_t stream) {
   extern __shared__ __align__(128) uint8_t sm_raw[];

@@ -1,6 +1,6 @@
 """Small-case launcher for profiling: ``python renee_b200/ops/profile_case.py [repeats]`` launches each
 hand-written kernel once per repeat at the headline benchmark's shapes (encoder: T=8192 tokens, H=768,
-F=3072, 256 sequences of 32 tokens, 12 heads; classifier: B=256, D=768, a 16384-label shard = the per-GPU
+F=3072, 256 sequences of 32 tokens and 64 sequences of 128 tokens, 12 heads; classifier: B=256, D=768, a 16384-label shard = the per-GPU
 shard at 8 GPUs; AdamW over 66.4M parameters).  About 1.5 GB on the device, a few milliseconds of work:
 sized so that ``ncu --set full`` on it ends by itself within a minute or two."""
 import os, sys, torch
@@ -27,6 +27,8 @@ n0 = torch.zeros(1, dtype=torch.int32, device=dev); e = torch.zeros(1, dtype=tor
 b_, S_, nh_ = 256, 32, 12
 mask = torch.ones(b_, S_, dtype=torch.int32, device=dev)
 aws = ops.attention_workspace(b_, S_, nh_, dev, dt)
+mask_long = torch.ones(64, 128, dtype=torch.int32, device=dev)
+aws_long = ops.attention_workspace(64, 128, nh_, dev, dt)
 bq = torch.zeros(3 * H, device=dev, dtype=dt); ctx = torch.empty(T, H, device=dev, dtype=dt); dqkv = torch.empty_like(q)
 Zt = torch.empty(B, L, device=dev); ov = torch.empty(B, 100, device=dev); oi = torch.empty(B, 100, dtype=torch.int32, device=dev)
 n_ad = 66_400_000 // 1024 * 1024
@@ -42,6 +44,8 @@ for it in range(int(sys.argv[1]) if len(sys.argv) > 1 else 1):
     cu.xfc_dw_sgd(Gt, B, X, W, M, hp.buf, 0.9, 1e-4)
     ops.attention_fwd(q, bq, mask, nh_, 0.1, rng, 4, ctx, aws)
     ops.attention_bwd(ctx, q, bq, mask, nh_, 0.1, rng, 4, aws, dqkv, dq)
+    ops.attention_fwd(q, bq, mask_long, nh_, 0.1, rng, 4, ctx, aws_long)
+    ops.attention_bwd(ctx, q, bq, mask_long, nh_, 0.1, rng, 4, aws_long, dqkv, dq)
     cu.xfc_logits_grad(W, X, None, L, None, None, None, 0, raw_out=Zt)
     cu.topk_rows(Zt, L, 100, 0, ov, oi)
     ops.adamw_step(p32, am, av, ag, p16, hp, 0.9, 0.999, 1e-6, 0.01, n_ad // 2)
