@@ -108,26 +108,24 @@ __device__ __forceinline__ void red_add_f32x4(float* p, float a, float b, float 
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
-// erf by a rational minimax approximation on [-4, 4] (|error| < 4e-7, i.e. fp32 round-off): one
-// reciprocal and 13 FMAs, about half the instructions of erff, which matters because the GELU kernels
-// are otherwise bound by the math pipes rather than by HBM.
-__device__ __forceinline__ float fast_erf(float x) {
-  x = fminf(fmaxf(x, -4.f), 4.f);
-  const float x2 = x * x;
-  float p = -2.72614225801306e-10f;
-  p = fmaf(p, x2, 2.77068142495902e-08f);
-  p = fmaf(p, x2, -2.10102402082508e-06f);
-  p = fmaf(p, x2, -5.69250639462346e-05f);
-  p = fmaf(p, x2, -7.34990630326855e-04f);
-  p = fmaf(p, x2, -2.95459980854025e-03f);
-  p = fmaf(p, x2, -1.60960333262415e-02f);
-  p *= x;
-  float q = -1.45660718464996e-05f;
-  q = fmaf(q, x2, -2.13374055278905e-04f);
-  q = fmaf(q, x2, -1.68282697438203e-03f);
-  q = fmaf(q, x2, -7.37332916720468e-03f);
-  q = fmaf(q, x2, -1.42647390514189e-02f);
-  return __fdividef(p, q);
+// Standard normal CDF Phi(z) = 0.5 erfc(-z / sqrt 2), and e = exp(-z^2 / 2) as a by-product (the GELU
+// gradient needs it for the density).  erfc(|x|) = t (a1 + t (a2 + t (a3 + t (a4 + t a5)))) exp(-x^2) with
+// t = 1 / (1 + p |x|) (Abramowitz & Stegun 7.1.26, |error| <= 1.5e-7): the negative tail comes out of the
+// product directly, without the cancellation of 1 + erf, and the whole thing is 2 special-function
+// instructions and about 12 FMA-pipe ones -- which matters because the GELU kernels are bound by
+// instruction issue rather than by HBM.
+__device__ __forceinline__ float normal_cdf(float z, float& e) {
+  const float ax = fabsf(z) * 0.70710678118654752f;
+  float t;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, ax, 1.f)));
+  float p = 1.061405429f;
+  p = fmaf(p, t, -1.453152027f);
+  p = fmaf(p, t, 1.421413741f);
+  p = fmaf(p, t, -0.284496736f);
+  p = fmaf(p, t, 0.254829592f);
+  e = __expf(-ax * ax);
+  const float half = 0.5f * p * t * e;
+  return z < 0.f ? half : 1.f - half;
 }
 
 // Counter-based dropout RNG; must stay bit-identical to renee_b200/ops/rng.py::mix32
