@@ -24,6 +24,7 @@ from dataclasses import dataclass
 import torch
 
 from .. import ops
+from ..utils import guard
 from .encoder import EncoderConfig
 
 ALIGN = 128  # elements; keeps every parameter 256-byte aligned in bf16
@@ -92,20 +93,20 @@ class FlatEncoder:
         if H % ALIGN != 0:
             raise ValueError(f"hidden size must be a multiple of {ALIGN}")
         dev = self.device
-        self.p32 = torch.zeros(off, dtype=torch.float32, device=dev)
+        self.p32 = guard.zeros(off, dtype=torch.float32, device=dev, name="encoder.p32")
         if act_dtype == torch.float32:
             self.p16 = self.p32
         elif p16_alloc is not None:
             self.p16 = p16_alloc(off, act_dtype)[:off]
         else:
-            self.p16 = torch.zeros(off, dtype=act_dtype, device=dev)
+            self.p16 = guard.zeros(off, dtype=act_dtype, device=dev, name="encoder.p16")
         if grad_alloc is not None and act_dtype != torch.float32:
             # the gradient buffer lives where the collective backend wants it (symmetric peer memory)
             self.g = grad_alloc(off, act_dtype)[:off]
         else:
-            self.g = torch.zeros(off, dtype=act_dtype, device=dev)
-        self.m = torch.zeros(off, dtype=torch.float32, device=dev)
-        self.v = torch.zeros(off, dtype=torch.float32, device=dev)
+            self.g = guard.zeros(off, dtype=act_dtype, device=dev, name="encoder.grad")
+        self.m = guard.zeros(off, dtype=torch.float32, device=dev, name="encoder.adam_m")
+        self.v = guard.zeros(off, dtype=torch.float32, device=dev, name="encoder.adam_v")
         self._init_params(seed)
         self._acts = None
         self._acts_key = None
@@ -168,7 +169,7 @@ class FlatEncoder:
             return
         cfg, dev, dt = self.cfg, self.device, self.act_dtype
         T, H, Fd, nh = b * S, cfg.dim, cfg.hidden_dim, cfg.n_heads
-        e = lambda *shape, dtype=dt: torch.empty(*shape, dtype=dtype, device=dev)
+        e = lambda *shape, dtype=dt: guard.empty(*shape, dtype=dtype, device=dev, name=f"encoder.act{guard.registered()}")
         layers = []
         for _ in range(cfg.n_layers):
             layers.append(dict(qkv=e(T, 3 * H), ctx=e(T, H), ao=e(T, H), pre1=e(T, H), h1=e(T, H),

@@ -28,6 +28,7 @@ from __future__ import annotations
 import torch
 
 from ..ops import reference as ref
+from ..utils import guard
 
 INIT_CHUNK = 1 << 16
 GT_L2_BUDGET_BYTES = 48 << 20   # keep the Gt chunk well inside the 126 MB L2
@@ -45,8 +46,8 @@ class XFCClassifier:
         self.accum = max(1, int(accum))
         self.max_batch = int(max_batch)
         self.stochastic_round = bool(stochastic_round)
-        self.W = torch.empty(self.Ls, self.D, dtype=self.dtype, device=self.device)
-        self.M = torch.zeros(self.Ls, self.D, dtype=self.dtype, device=self.device)
+        self.W = guard.empty(self.Ls, self.D, dtype=self.dtype, device=self.device, name="xfc.W")
+        self.M = guard.zeros(self.Ls, self.D, dtype=self.dtype, device=self.device, name="xfc.M")
         self._init_weight(seed, init_std)
         self.chunk = self._pick_chunk()
         self._scratch = None
@@ -91,8 +92,8 @@ class XFCClassifier:
         if self._scratch is None or self._scratch["B"] < B:
             chunk = min(self.chunk, (self.Ls + 127) // 128 * 128)
             ldg = (B + 7) // 8 * 8
-            self._scratch = {"B": B, "Gt": torch.empty(chunk * ldg, dtype=torch.float16 if self.dtype == torch.float16 else torch.float32,
-                                                      device=self.device)}
+            self._scratch = {"B": B, "Gt": guard.empty(chunk * ldg, dtype=torch.float16 if self.dtype == torch.float16 else torch.float32,
+                                                      device=self.device, name="xfc.Gt")}
         return self._scratch
 
     def step(self, X: torch.Tensor, pos_rows: torch.Tensor, pos_labels: torch.Tensor, nnz,

@@ -14,6 +14,7 @@ from __future__ import annotations
 import torch
 
 from . import reference as ref
+from ..utils import guard
 from .rng import DropoutRNG, keep_mask  # noqa: F401
 
 
@@ -55,7 +56,7 @@ def embed_ln_bwd(dy, ids, word, pos, gamma, mean, rstd, S, p, rng, stream, pad_i
 
 def attention_workspace(b, S, nh, device, dtype):
     """Buffers the attention forward leaves for its backward: the softmax probabilities."""
-    return {"probs": torch.empty(b, nh, S, S, dtype=dtype, device=device)}
+    return {"probs": guard.empty(b, nh, S, S, dtype=dtype, device=device, name="attention.probs")}
 
 
 def attention_fwd(qkv, bqkv, mask, nh, p, rng, stream, ctx_out, ws):

@@ -35,6 +35,7 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
+from ..utils import guard
 from ..utils.sharding import batch_row_range
 from .collectives import TorchCollectives
 from .dist import DistContext
@@ -71,13 +72,23 @@ class PeerCollectives(TorchCollectives):
         self.host_step = 0
 
     # ------------------------------------------------------------------ allocation
-    def _symm(self, numel: int, dtype):
+    def _symm(self, numel: int, dtype, name: str = "symmetric"):
         import torch.distributed._symmetric_memory as symm_mem
-        t = symm_mem.empty(numel, dtype=dtype, device=self.ctx.device)
-        hdl = symm_mem.rendezvous(t, self.group)
+        whole = []
+
+        def alloc(n, dt):
+            whole.append(symm_mem.empty(n, dtype=dt, device=self.ctx.device))
+            return whole[0]
+
+        # in guard mode the payload sits one band into the allocation on every rank: shift the peer and
+        # multicast addresses by the same amount
+        t = guard.from_allocator(alloc, numel, dtype, name=f"{name}{len(self._handles)}")
+        off = guard.payload_offset_bytes()
+        hdl = symm_mem.rendezvous(whole[0], self.group)
         self._handles.append(hdl)
-        self._last_multicast = int(getattr(hdl, "multicast_ptr", 0) or 0) if self.use_nvls else 0
-        return t, [int(p) for p in hdl.buffer_ptrs]
+        mc = int(getattr(hdl, "multicast_ptr", 0) or 0) if self.use_nvls else 0
+        self._last_multicast = mc + off if mc else 0
+        return t, [int(p) + off for p in hdl.buffer_ptrs]
 
     def setup(self, B_max: int, D: int) -> None:
         from ..ops import cuda as cu
@@ -124,7 +135,7 @@ class PeerCollectives(TorchCollectives):
         self.p16.zero_()
         self._p16_ptrs = cu.ptr_array(pp)
         per = ((numel // 8) + self.G - 1) // self.G * 8
-        self.gsum = torch.zeros(per + 8, dtype=torch.float32, device=self.ctx.device)
+        self.gsum = guard.zeros(per + 8, dtype=torch.float32, device=self.ctx.device, name="optimizer.gsum")
         torch.cuda.synchronize()
         dist.barrier(group=self.group)
         return self.p16

@@ -37,6 +37,7 @@ from .optim.schedule import CosineWarmupSchedule
 from .ops.rng import DropoutRNG
 from .parallel.collectives import TorchCollectives
 from .parallel.dist import DistContext
+from .utils import guard
 from .utils.sharding import LabelSharding
 
 LOSS_SAMPLE_FREQ = 100   # dl_base.py:144
@@ -180,15 +181,15 @@ class XCTrainer:
         b, S = cfg.batch_size + 1, cfg.maxlen
         self.max_nnz = 0
         self.buf = dict(
-            ids=torch.zeros(b, S, dtype=torch.int32, device=dev),
-            mask=torch.zeros(b, S, dtype=torch.int32, device=dev),
-            x_local=torch.zeros(b, D, dtype=self.xfc.dtype, device=dev),
-            X=torch.zeros(self.B + self.G, D, dtype=self.xfc.dtype, device=dev),
-            dX=torch.zeros(self.B + self.G, D, dtype=torch.float32, device=dev),
-            dx_local=torch.zeros(b, D, dtype=torch.float32, device=dev),
-            de=torch.zeros(b, D, dtype=torch.float32, device=dev),
-            nnz=torch.zeros(1, dtype=torch.int32, device=dev),
-            loss=torch.zeros(1, dtype=torch.float32, device=dev),
+            ids=guard.zeros(b, S, dtype=torch.int32, device=dev, name="step.ids"),
+            mask=guard.zeros(b, S, dtype=torch.int32, device=dev, name="step.mask"),
+            x_local=guard.zeros(b, D, dtype=self.xfc.dtype, device=dev, name="step.x_local"),
+            X=guard.zeros(self.B + self.G, D, dtype=self.xfc.dtype, device=dev, name="step.X"),
+            dX=guard.zeros(self.B + self.G, D, dtype=torch.float32, device=dev, name="step.dX"),
+            dx_local=guard.zeros(b, D, dtype=torch.float32, device=dev, name="step.dx_local"),
+            de=guard.zeros(b, D, dtype=torch.float32, device=dev, name="step.de"),
+            nnz=guard.zeros(1, dtype=torch.int32, device=dev, name="step.nnz"),
+            loss=guard.zeros(1, dtype=torch.float32, device=dev, name="step.loss"),
         )
         self._ensure_pos_capacity(max(1024, self.B * 8))
         if self.device.type == "cuda" and cfg.fp16xfc and cfg.overlap_dw:
@@ -203,8 +204,8 @@ class XCTrainer:
         while cap < n:
             cap *= 2
         self.max_nnz = cap
-        self.buf["pos_rows"] = torch.zeros(cap, dtype=torch.int32, device=self.device)
-        self.buf["pos_labels"] = torch.zeros(cap, dtype=torch.int32, device=self.device)
+        self.buf["pos_rows"] = guard.zeros(cap, dtype=torch.int32, device=self.device, name="step.pos_rows")
+        self.buf["pos_labels"] = guard.zeros(cap, dtype=torch.int32, device=self.device, name="step.pos_labels")
         self._graphs, self._graph_warm = {}, {}   # static addresses changed: captured graphs are stale
 
     # ------------------------------------------------------------------ one step (optimized)
@@ -454,7 +455,15 @@ class XCTrainer:
         self.epoch = cfg.epochs
 
     def check_device_status(self) -> None:
-        """Raise (and tell the other ranks) if a bounded device-side wait has expired since the last check."""
+        """Raise (and tell the other ranks) if a bounded device-side wait has expired since the last check, or
+        (guard mode) if something wrote outside a framework buffer."""
+        if guard.enabled():
+            try:
+                guard.assert_clean()
+            except guard.GuardError as exc:
+                if self.watchdog is not None:
+                    self.watchdog.post_failure(str(exc))
+                raise
         if self.device.type != "cuda":
             return
         from .ops import cuda as cu
