@@ -38,6 +38,7 @@ from .ops.rng import DropoutRNG
 from .parallel.collectives import TorchCollectives
 from .parallel.dist import DistContext
 from .utils import guard
+from .utils.timing import nvtx_range
 from .utils.sharding import LabelSharding
 
 LOSS_SAMPLE_FREQ = 100   # dl_base.py:144
@@ -300,19 +301,24 @@ class XCTrainer:
         cfg, bf, enc, comm = self.cfg, self.buf, self.encoder, self.comm
         ids, mask = bf["ids"][:b], bf["mask"][:b]
         comm.device_begin()
-        emb = enc.forward(ids, mask, self.step_rng, train=True)
-        # classifier-input dropout + cast + all-gather (fused into one kernel on the peer-memory backend)
-        X, wait = comm.embeddings_to_X(emb, B, cfg.dropout, self.step_rng, _S_CLS_DROPOUT, bf)
-        dX, signal = comm.dx_buffer(B, bf)
-        loss = self.xfc.step(X, bf["pos_rows"], bf["pos_labels"], bf["nnz"] if X.is_cuda else nnz, dX,
-                             self.hp, cfg.mo, cfg.wd1, want_loss, wait=wait, signal=signal,
-                             side_stream=self._side_stream)
-        if want_loss:
-            loss = comm.allreduce_scalar(loss.reshape(1))
-        de = comm.dx_to_local(dX, B, cfg.dropout, self.step_rng, _S_CLS_DROPOUT, bf)
-        enc.backward(de)
-        comm.optimizer_step(enc, self.hp, 0.9, 0.999, cfg.adam_eps, cfg.wd2)
-        self.hp.update_scale()
+        with nvtx_range("encoder_forward"):
+            emb = enc.forward(ids, mask, self.step_rng, train=True)
+        with nvtx_range("allgather_classifier"):
+            # classifier-input dropout + cast + all-gather (fused into one kernel on the peer-memory backend)
+            X, wait = comm.embeddings_to_X(emb, B, cfg.dropout, self.step_rng, _S_CLS_DROPOUT, bf)
+            dX, signal = comm.dx_buffer(B, bf)
+            loss = self.xfc.step(X, bf["pos_rows"], bf["pos_labels"], bf["nnz"] if X.is_cuda else nnz, dX,
+                                 self.hp, cfg.mo, cfg.wd1, want_loss, wait=wait, signal=signal,
+                                 side_stream=self._side_stream)
+            if want_loss:
+                loss = comm.allreduce_scalar(loss.reshape(1))
+        with nvtx_range("reduce_scatter"):
+            de = comm.dx_to_local(dX, B, cfg.dropout, self.step_rng, _S_CLS_DROPOUT, bf)
+        with nvtx_range("encoder_backward"):
+            enc.backward(de)
+        with nvtx_range("optimizer"):
+            comm.optimizer_step(enc, self.hp, 0.9, 0.999, cfg.adam_eps, cfg.wd2)
+            self.hp.update_scale()
         if self._side_stream is not None:
             torch.cuda.current_stream().wait_stream(self._side_stream)   # the overlapped dW+SGD kernel joins here
         return loss

@@ -7,10 +7,32 @@ times.  The reference has no timing beyond tqdm's iteration rate.
 """
 from __future__ import annotations
 
+import os
 import time
 from contextlib import contextmanager
 
 import torch
+
+_NVTX = os.environ.get("RENEE_B200_NVTX", "") == "1"
+
+
+def nvtx_enabled() -> bool:
+    return _NVTX and torch.cuda.is_available()
+
+
+@contextmanager
+def nvtx_range(name: str):
+    """NVTX range around a phase of the step when ``RENEE_B200_NVTX=1`` (for timeline profilers; a no-op
+    otherwise).  Ranges are host-side annotations: they label the launches of an eager step, and the capture —
+    not the replays — of a CUDA-graph step, so profile with ``cuda_graph=False``."""
+    if not nvtx_enabled():
+        yield
+        return
+    torch.cuda.nvtx.range_push(name)
+    try:
+        yield
+    finally:
+        torch.cuda.nvtx.range_pop()
 
 
 class PhaseTimer:
@@ -20,6 +42,10 @@ class PhaseTimer:
 
     @contextmanager
     def phase(self, name: str):
+        with nvtx_range(name):
+            yield from self._phase(name)
+
+    def _phase(self, name: str):
         if self.cuda:
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
