@@ -171,12 +171,14 @@ class FlatEncoder:
         T, H, Fd, nh = b * S, cfg.dim, cfg.hidden_dim, cfg.n_heads
         e = lambda *shape, dtype=dt: guard.empty(*shape, dtype=dtype, device=dev, name=f"encoder.act{guard.registered()}")
         layers = []
+        # long sequences: one softmax-gradient scratch serves every layer (it lives within one attention backward)
+        att_ds = (e(b, nh, S, S) if S > 128 and dev.type == "cuda" and dt != torch.float32 else None)
         for _ in range(cfg.n_layers):
             layers.append(dict(qkv=e(T, 3 * H), ctx=e(T, H), ao=e(T, H), pre1=e(T, H), h1=e(T, H),
                                mean1=e(T, dtype=torch.float32), rstd1=e(T, dtype=torch.float32),
                                f1=e(T, Fd), a1=e(T, Fd), f2=e(T, H), pre2=e(T, H), h2=e(T, H),
                                mean2=e(T, dtype=torch.float32), rstd2=e(T, dtype=torch.float32),
-                               att=ops.attention_workspace(b, S, nh, dev, dt)))
+                               att=ops.attention_workspace(b, S, nh, dev, dt, ds=att_ds)))
         self._acts = dict(h0=e(T, H), mean0=e(T, dtype=torch.float32), rstd0=e(T, dtype=torch.float32),
                           layers=layers, pooled=e(b, H, dtype=torch.float32),
                           dh=e(T, H), dh_b=e(T, H), dqkv=e(T, 3 * H), dctx=e(T, H), df1=e(T, Fd), da1=e(T, Fd),

@@ -54,9 +54,14 @@ def embed_ln_bwd(dy, ids, word, pos, gamma, mean, rstd, S, p, rng, stream, pad_i
     ref.embed_ln_bwd(dy, ids, word, pos, gamma, mean, rstd, S, p, rng.seed, stream, pad_id, dword, dpos, dgamma, dbeta)
 
 
-def attention_workspace(b, S, nh, device, dtype):
-    """Buffers the attention forward leaves for its backward: the softmax probabilities."""
-    return {"probs": guard.empty(b, nh, S, S, dtype=dtype, device=device, name="attention.probs")}
+def attention_workspace(b, S, nh, device, dtype, ds=None):
+    """Buffers the attention forward leaves for its backward: the softmax probabilities.  On CUDA, 16-bit
+    sequences longer than 128 tokens also need a same-shaped scratch for the softmax gradient (``ds``; pass one
+    tensor to share it between layers, it only lives within one backward call)."""
+    ws = {"probs": guard.empty(b, nh, S, S, dtype=dtype, device=device, name="attention.probs")}
+    if S > 128 and torch.device(device).type == "cuda" and dtype != torch.float32:
+        ws["ds"] = ds if ds is not None else guard.empty(b, nh, S, S, dtype=dtype, device=device, name="attention.ds")
+    return ws
 
 
 def attention_fwd(qkv, bqkv, mask, nh, p, rng, stream, ctx_out, ws):

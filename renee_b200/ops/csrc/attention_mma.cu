@@ -1,4 +1,5 @@
-// Register-resident self-attention forward/backward for 16-bit activations, head dim 64, S <= 128.
+// Register-resident self-attention forward/backward for 16-bit activations, head dim 64, S <= 512
+// (one CTA per (batch, head) up to 128 tokens; blocked kernels, further down, for 129..512).
 // Same fusion and interface as attention_tc.cu (bias add, scale, key-padding mask, softmax, counter-based
 // attention dropout, head split/merge addressing, q/k/v bias gradients), organised so that the score
 // matrix never touches shared memory:
@@ -435,6 +436,357 @@ static int launch_bwd(const void* dctx, const void* qkv, const void* bqkv, const
   return 0;
 }
 
+
+// ------------------------------------------------------------------------------------ sequences of 129..512 tokens
+// Same math and the same fragment routines, blocked: a CTA of 4 warps owns 64 query rows (forward, dQ) or 64 key
+// rows (dK, dV) of one (batch, head) and walks the other dimension in blocks of 128 through shared memory.
+//   forward   two passes over the key blocks: running row maximum / sum first, then probabilities (stored for the
+//             backward, as for short sequences), dropout and O += P~ V.
+//   dQ        two passes as well (the softmax gradient needs the whole row's sum of dP * P before any dS):
+//             dP = dO V^T per key block, then dS, written to a [b, nh, S, S] workspace, and dQ += dS K.
+//   dK, dV    per block of 64 keys, over query blocks: dS and P~ tiles staged in shared memory (P~ rebuilt from
+//             the stored probabilities and the counter-based dropout mask), dK += dS^T Q, dV += P~^T dO.
+constexpr int QB = 64;     // rows owned by a CTA
+constexpr int KBLK = 128;  // rows of the other dimension per step
+constexpr int PPK = QB + 8;
+
+// rows first.. of a [*, ld] matrix (pointer already at this (batch, head)'s first column) -> [n_tile][RP] tile
+template <typename T>
+__device__ __forceinline__ void stage_block(T* dst, const T* __restrict__ src, size_t ld, const T* __restrict__ bias,
+                                            int first, int n_tile, int S) {
+  for (int i = threadIdx.x; i < n_tile * (HD / 8); i += blockDim.x) {
+    const int s = i >> 3, d = (i & 7) * 8;
+    float v[8];
+    if (first + s < S) {
+      load8(src + (size_t)(first + s) * ld + d, v);
+      if (bias != nullptr) {
+        float bb[8];
+        load8(bias + d, bb);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] += bb[j];
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = 0.f;
+    }
+    store8(dst + s * RP + d, v);
+  }
+}
+
+// two consecutive elements idx, idx + 1 of a [.., S] row; ok0 / ok1 say which exist; `pair` = 4-byte access allowed
+template <typename T>
+__device__ __forceinline__ float2 load_pair(const T* __restrict__ base, size_t idx, bool ok0, bool ok1, bool pair) {
+  float2 r = make_float2(0.f, 0.f);
+  if (ok0) {
+    if (pair) r = Pack<T>::unpack(*reinterpret_cast<const uint32_t*>(base + idx));
+    else { r.x = to_f(base[idx]); if (ok1) r.y = to_f(base[idx + 1]); }
+  }
+  return r;
+}
+template <typename T>
+__device__ __forceinline__ void store_pair(T* __restrict__ base, size_t idx, uint32_t u, bool ok0, bool ok1, bool pair) {
+  if (ok0) {
+    if (pair) *reinterpret_cast<uint32_t*>(base + idx) = u;
+    else {
+      const T* e = reinterpret_cast<const T*>(&u);
+      base[idx] = e[0];
+      if (ok1) base[idx + 1] = e[1];
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) attention_fwd_long_kernel(
+    const T* __restrict__ qkv, const T* __restrict__ bqkv, const int* __restrict__ mask, T* __restrict__ ctx,
+    T* __restrict__ probs, int S, int H, int nh, float p, const int* __restrict__ seed_ptr, uint32_t stream) {
+  extern __shared__ __align__(128) uint8_t sm_raw[];
+  T* sQ = reinterpret_cast<T*>(sm_raw);
+  T* sK = sQ + QB * RP;
+  T* sV = sK + KBLK * RP;
+  uint8_t* sCode = reinterpret_cast<uint8_t*>(sV + KBLK * RP);   // per key of the block: 0 beyond S, 1 attend, 2 masked
+  const int h = blockIdx.x, b = blockIdx.y, q0 = blockIdx.z * QB;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const uint32_t seed = p > 0.f ? (uint32_t)(*seed_ptr) : 0u;
+  const float inv_keep = p > 0.f ? 1.f / (1.f - p) : 1.f;
+  const float scale = rsqrtf((float)HD);
+  const T* base = qkv + (size_t)b * S * 3 * H + h * HD;
+  stage_block<T>(sQ, base, (size_t)3 * H, bqkv + h * HD, q0, QB, S);
+  const int r0 = warp * 16;
+  const int i0 = q0 + r0 + g, i1 = i0 + 8;
+  const int nkb = (S + KBLK - 1) / KBLK;
+  float m0 = -1e30f, m1 = -1e30f, l0 = 0.f, l1 = 0.f;
+  for (int kb = 0; kb < nkb; ++kb) {
+    __syncthreads();
+    stage_block<T>(sK, base + H, (size_t)3 * H, bqkv + H + h * HD, kb * KBLK, KBLK, S);
+    for (int j = threadIdx.x; j < KBLK; j += blockDim.x) {
+      const int key = kb * KBLK + j;
+      sCode[j] = key < S ? (mask[b * S + key] != 0 ? 1 : 2) : 0;
+    }
+    __syncthreads();
+    float acc[KBLK / 8][4];
+#pragma unroll
+    for (int j = 0; j < KBLK / 8; ++j) { acc[j][0] = 0.f; acc[j][1] = 0.f; acc[j][2] = 0.f; acc[j][3] = 0.f; }
+    rows_times_transposed<T, KBLK>(acc, sQ, sK, r0, lane);
+    float bm0 = -1e30f, bm1 = -1e30f;
+#pragma unroll
+    for (int j = 0; j < KBLK / 8; ++j) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int code = sCode[8 * j + 2 * t + e];
+        acc[j][e] = code == 1 ? acc[j][e] * scale : -1e30f;
+        acc[j][2 + e] = code == 1 ? acc[j][2 + e] * scale : -1e30f;
+        if (code != 0) { bm0 = fmaxf(bm0, acc[j][e]); bm1 = fmaxf(bm1, acc[j][2 + e]); }
+      }
+    }
+    const float n0 = fmaxf(m0, quad_max(bm0)), n1 = fmaxf(m1, quad_max(bm1));
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < KBLK / 8; ++j) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        if (sCode[8 * j + 2 * t + e] != 0) { s0 += __expf(acc[j][e] - n0); s1 += __expf(acc[j][2 + e] - n1); }
+      }
+    }
+    l0 = l0 * __expf(m0 - n0) + s0;
+    l1 = l1 * __expf(m1 - n1) + s1;
+    m0 = n0; m1 = n1;
+  }
+  l0 = quad_sum(l0); l1 = quad_sum(l1);
+  const float inv0 = i0 < S ? 1.f / l0 : 0.f, inv1 = i1 < S ? 1.f / l1 : 0.f;
+  const size_t prow0 = ((size_t)(b * nh + h) * S + i0) * S, prow1 = ((size_t)(b * nh + h) * S + i1) * S;
+  const bool pair = (S & 1) == 0;
+  float out[HD / 8][4];
+#pragma unroll
+  for (int jd = 0; jd < HD / 8; ++jd) { out[jd][0] = 0.f; out[jd][1] = 0.f; out[jd][2] = 0.f; out[jd][3] = 0.f; }
+  for (int kb = 0; kb < nkb; ++kb) {
+    __syncthreads();
+    stage_block<T>(sK, base + H, (size_t)3 * H, bqkv + H + h * HD, kb * KBLK, KBLK, S);
+    stage_block<T>(sV, base + 2 * H, (size_t)3 * H, bqkv + 2 * H + h * HD, kb * KBLK, KBLK, S);
+    for (int j = threadIdx.x; j < KBLK; j += blockDim.x) {
+      const int key = kb * KBLK + j;
+      sCode[j] = key < S ? (mask[b * S + key] != 0 ? 1 : 2) : 0;
+    }
+    __syncthreads();
+    float acc[KBLK / 8][4];
+#pragma unroll
+    for (int j = 0; j < KBLK / 8; ++j) { acc[j][0] = 0.f; acc[j][1] = 0.f; acc[j][2] = 0.f; acc[j][3] = 0.f; }
+    rows_times_transposed<T, KBLK>(acc, sQ, sK, r0, lane);
+    uint32_t pf[KBLK / 16][4];
+#pragma unroll
+    for (int j = 0; j < KBLK / 8; ++j) {
+      const int c = 8 * j + 2 * t, key = kb * KBLK + c;
+      float e00, e01, e10, e11;
+      {
+        const int c0 = sCode[c], c1 = sCode[c + 1];
+        e00 = c0 != 0 ? __expf((c0 == 1 ? acc[j][0] * scale : -1e30f) - m0) * inv0 : 0.f;
+        e01 = c1 != 0 ? __expf((c1 == 1 ? acc[j][1] * scale : -1e30f) - m0) * inv0 : 0.f;
+        e10 = c0 != 0 ? __expf((c0 == 1 ? acc[j][2] * scale : -1e30f) - m1) * inv1 : 0.f;
+        e11 = c1 != 0 ? __expf((c1 == 1 ? acc[j][3] * scale : -1e30f) - m1) * inv1 : 0.f;
+      }
+      const uint32_t u0 = Pack<T>::pack(e00, e01), u1 = Pack<T>::pack(e10, e11);
+      store_pair<T>(probs, prow0 + key, u0, i0 < S && key < S, key + 1 < S, pair);
+      store_pair<T>(probs, prow1 + key, u1, i1 < S && key < S, key + 1 < S, pair);
+      float2 q0v = Pack<T>::unpack(u0), q1v = Pack<T>::unpack(u1);
+      if (p > 0.f) {
+        q0v.x = keep(seed, stream, (uint32_t)(prow0 + key), p) ? q0v.x * inv_keep : 0.f;
+        q0v.y = keep(seed, stream, (uint32_t)(prow0 + key + 1), p) ? q0v.y * inv_keep : 0.f;
+        q1v.x = keep(seed, stream, (uint32_t)(prow1 + key), p) ? q1v.x * inv_keep : 0.f;
+        q1v.y = keep(seed, stream, (uint32_t)(prow1 + key + 1), p) ? q1v.y * inv_keep : 0.f;
+      }
+      pf[j >> 1][(j & 1) * 2 + 0] = Pack<T>::pack(q0v.x, q0v.y);
+      pf[j >> 1][(j & 1) * 2 + 1] = Pack<T>::pack(q1v.x, q1v.y);
+    }
+    frag_times_rows<T, KBLK>(out, pf, sV, lane);
+  }
+  write_rows<T>(out, ctx + (size_t)(b * S + q0 + r0) * H + h * HD, H, q0 + r0, S, lane, nullptr);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) attention_bwd_long_dq_kernel(
+    const T* __restrict__ dctx, const T* __restrict__ qkv, const T* __restrict__ bqkv, const T* __restrict__ probs,
+    T* __restrict__ ds_ws, T* __restrict__ dqkv, int S, int H, int nh, float p, const int* __restrict__ seed_ptr,
+    uint32_t stream, float* __restrict__ bias_acc) {
+  extern __shared__ __align__(128) uint8_t sm_raw[];
+  T* sDO = reinterpret_cast<T*>(sm_raw);
+  T* sK = sDO + QB * RP;
+  T* sV = sK + KBLK * RP;
+  float* sBias = reinterpret_cast<float*>(sV + KBLK * RP);   // [HD] column sums of this CTA's dQ rows
+  const int h = blockIdx.x, b = blockIdx.y, q0 = blockIdx.z * QB;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const uint32_t seed = p > 0.f ? (uint32_t)(*seed_ptr) : 0u;
+  const float inv_keep = p > 0.f ? 1.f / (1.f - p) : 1.f;
+  const float scale = rsqrtf((float)HD);
+  const T* base = qkv + (size_t)b * S * 3 * H + h * HD;
+  if (bias_acc != nullptr)
+    for (int i = threadIdx.x; i < HD; i += blockDim.x) sBias[i] = 0.f;
+  stage_block<T>(sDO, dctx + (size_t)b * S * H + h * HD, (size_t)H, nullptr, q0, QB, S);
+  const int r0 = warp * 16;
+  const int i0 = q0 + r0 + g, i1 = i0 + 8;
+  const int nkb = (S + KBLK - 1) / KBLK;
+  const size_t prow0 = ((size_t)(b * nh + h) * S + i0) * S, prow1 = ((size_t)(b * nh + h) * S + i1) * S;
+  const bool pair = (S & 1) == 0;
+  float dot0 = 0.f, dot1 = 0.f;
+  float out[HD / 8][4];
+#pragma unroll
+  for (int jd = 0; jd < HD / 8; ++jd) { out[jd][0] = 0.f; out[jd][1] = 0.f; out[jd][2] = 0.f; out[jd][3] = 0.f; }
+  for (int pass = 0; pass < 2; ++pass) {
+    for (int kb = 0; kb < nkb; ++kb) {
+      __syncthreads();
+      stage_block<T>(sV, base + 2 * H, (size_t)3 * H, bqkv + 2 * H + h * HD, kb * KBLK, KBLK, S);
+      if (pass == 1) stage_block<T>(sK, base + H, (size_t)3 * H, bqkv + H + h * HD, kb * KBLK, KBLK, S);
+      __syncthreads();
+      float acc[KBLK / 8][4];
+#pragma unroll
+      for (int j = 0; j < KBLK / 8; ++j) { acc[j][0] = 0.f; acc[j][1] = 0.f; acc[j][2] = 0.f; acc[j][3] = 0.f; }
+      rows_times_transposed<T, KBLK>(acc, sDO, sV, r0, lane);
+      uint32_t dsf[KBLK / 16][4];
+#pragma unroll
+      for (int j = 0; j < KBLK / 8; ++j) {
+        const int key = kb * KBLK + 8 * j + 2 * t;
+        const bool k0 = key < S, k1 = key + 1 < S;
+        const float2 pr0 = load_pair<T>(probs, prow0 + key, i0 < S && k0, k1, pair);
+        const float2 pr1 = load_pair<T>(probs, prow1 + key, i1 < S && k0, k1, pair);
+        float m00 = 1.f, m01 = 1.f, m10 = 1.f, m11 = 1.f;
+        if (p > 0.f) {
+          m00 = keep(seed, stream, (uint32_t)(prow0 + key), p) ? inv_keep : 0.f;
+          m01 = keep(seed, stream, (uint32_t)(prow0 + key + 1), p) ? inv_keep : 0.f;
+          m10 = keep(seed, stream, (uint32_t)(prow1 + key), p) ? inv_keep : 0.f;
+          m11 = keep(seed, stream, (uint32_t)(prow1 + key + 1), p) ? inv_keep : 0.f;
+        }
+        const float a00 = acc[j][0] * m00, a01 = acc[j][1] * m01, a10 = acc[j][2] * m10, a11 = acc[j][3] * m11;
+        if (pass == 0) {
+          dot0 += a00 * pr0.x + a01 * pr0.y;
+          dot1 += a10 * pr1.x + a11 * pr1.y;
+        } else {
+          const uint32_t d0 = Pack<T>::pack(pr0.x * (a00 - dot0) * scale, pr0.y * (a01 - dot0) * scale);
+          const uint32_t d1 = Pack<T>::pack(pr1.x * (a10 - dot1) * scale, pr1.y * (a11 - dot1) * scale);
+          store_pair<T>(ds_ws, prow0 + key, d0, i0 < S && k0, k1, pair);
+          store_pair<T>(ds_ws, prow1 + key, d1, i1 < S && k0, k1, pair);
+          dsf[j >> 1][(j & 1) * 2 + 0] = d0;
+          dsf[j >> 1][(j & 1) * 2 + 1] = d1;
+        }
+      }
+      if (pass == 1) frag_times_rows<T, KBLK>(out, dsf, sK, lane);
+    }
+    if (pass == 0) { dot0 = quad_sum(dot0); dot1 = quad_sum(dot1); }
+  }
+  write_rows<T>(out, dqkv + (size_t)(b * S + q0 + r0) * 3 * H + h * HD, 3 * H, q0 + r0, S, lane,
+                bias_acc != nullptr ? sBias : nullptr);
+  if (bias_acc != nullptr) {
+    __syncthreads();
+    const int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    float* my_acc = bias_acc + (size_t)(cta % 8) * 3 * H;
+    for (int i = threadIdx.x; i < HD; i += blockDim.x) atomicAdd(my_acc + h * HD + i, sBias[i]);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) attention_bwd_long_dkv_kernel(
+    const T* __restrict__ dctx, const T* __restrict__ qkv, const T* __restrict__ bqkv, const T* __restrict__ probs,
+    const T* __restrict__ ds_ws, T* __restrict__ dqkv, int S, int H, int nh, float p, const int* __restrict__ seed_ptr,
+    uint32_t stream, float* __restrict__ bias_acc) {
+  extern __shared__ __align__(128) uint8_t sm_raw[];
+  T* sDS = reinterpret_cast<T*>(sm_raw);      // [query of the block][key of this CTA]
+  T* sW = sDS + KBLK * PPK;
+  T* sQ = sW + KBLK * PPK;
+  T* sDO = sQ + KBLK * RP;
+  float* sBias = reinterpret_cast<float*>(sDO + KBLK * RP);   // [2][HD] column sums of this CTA's dK, dV rows
+  const int h = blockIdx.x, b = blockIdx.y, key0 = blockIdx.z * QB;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t seed = p > 0.f ? (uint32_t)(*seed_ptr) : 0u;
+  const float inv_keep = p > 0.f ? 1.f / (1.f - p) : 1.f;
+  const T* base = qkv + (size_t)b * S * 3 * H + h * HD;
+  if (bias_acc != nullptr)
+    for (int i = threadIdx.x; i < 2 * HD; i += blockDim.x) sBias[i] = 0.f;
+  const bool vec = (S & 7) == 0;     // then every 8-key segment starts 16-byte aligned and lies inside the row
+  const int nqb = (S + KBLK - 1) / KBLK;
+  float outK[HD / 8][4], outV[HD / 8][4];
+#pragma unroll
+  for (int jd = 0; jd < HD / 8; ++jd) {
+    outK[jd][0] = 0.f; outK[jd][1] = 0.f; outK[jd][2] = 0.f; outK[jd][3] = 0.f;
+    outV[jd][0] = 0.f; outV[jd][1] = 0.f; outV[jd][2] = 0.f; outV[jd][3] = 0.f;
+  }
+  for (int qb = 0; qb < nqb; ++qb) {
+    __syncthreads();
+    stage_block<T>(sQ, base, (size_t)3 * H, bqkv + h * HD, qb * KBLK, KBLK, S);
+    stage_block<T>(sDO, dctx + (size_t)b * S * H + h * HD, (size_t)H, nullptr, qb * KBLK, KBLK, S);
+    for (int i = threadIdx.x; i < KBLK * (QB / 8); i += blockDim.x) {
+      const int qr = i >> 3, kc = (i & 7) * 8;
+      const int q = qb * KBLK + qr, key = key0 + kc;
+      float dsv[8], wv[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { dsv[j] = 0.f; wv[j] = 0.f; }
+      if (q < S && key < S) {
+        const size_t idx = ((size_t)(b * nh + h) * S + q) * S + key;
+        if (vec) {
+          load8(ds_ws + idx, dsv);
+          load8(probs + idx, wv);
+        } else {
+          for (int j = 0; j < 8; ++j)
+            if (key + j < S) { dsv[j] = to_f(ds_ws[idx + j]); wv[j] = to_f(probs[idx + j]); }
+        }
+        if (p > 0.f) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) wv[j] = keep(seed, stream, (uint32_t)(idx + j), p) ? wv[j] * inv_keep : 0.f;
+        }
+      }
+      store8(sDS + qr * PPK + kc, dsv);
+      store8(sW + qr * PPK + kc, wv);
+    }
+    __syncthreads();
+    transposed_times_rows<T, KBLK>(outK, sDS, PPK, warp * 16, sQ, lane);
+    transposed_times_rows<T, KBLK>(outV, sW, PPK, warp * 16, sDO, lane);
+  }
+  const int k0 = key0 + warp * 16;
+  write_rows<T>(outK, dqkv + (size_t)(b * S + k0) * 3 * H + H + h * HD, 3 * H, k0, S, lane,
+                bias_acc != nullptr ? sBias : nullptr);
+  write_rows<T>(outV, dqkv + (size_t)(b * S + k0) * 3 * H + 2 * H + h * HD, 3 * H, k0, S, lane,
+                bias_acc != nullptr ? sBias + HD : nullptr);
+  if (bias_acc != nullptr) {
+    __syncthreads();
+    const int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    float* my_acc = bias_acc + (size_t)(cta % 8) * 3 * H;
+    for (int i = threadIdx.x; i < 2 * HD; i += blockDim.x)
+      atomicAdd(my_acc + (1 + i / HD) * H + h * HD + (i % HD), sBias[i]);
+  }
+}
+
+constexpr size_t fwd_long_smem(size_t esz) { return (size_t)(QB + 2 * KBLK) * RP * esz + KBLK; }
+constexpr size_t dq_long_smem(size_t esz) { return (size_t)(QB + 2 * KBLK) * RP * esz + HD * sizeof(float); }
+constexpr size_t dkv_long_smem(size_t esz) {
+  return (size_t)2 * KBLK * PPK * esz + (size_t)2 * KBLK * RP * esz + 2 * HD * sizeof(float);
+}
+
+template <typename T>
+static int launch_fwd_long(const void* qkv, const void* bqkv, const int* mask, void* ctx, void* probs, int b, int S, int H,
+                           int nh, float p, const int* seed, unsigned stream_id, cudaStream_t st) {
+  auto k = attention_fwd_long_kernel<T>;
+  constexpr size_t smem = fwd_long_smem(sizeof(T));
+  if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -5;
+  k<<<dim3(nh, b, (S + QB - 1) / QB), 128, smem, st>>>((const T*)qkv, (const T*)bqkv, mask, (T*)ctx, (T*)probs, S, H, nh, p,
+                                                        seed, stream_id);
+  return 0;
+}
+
+template <typename T>
+static int launch_bwd_long(const void* dctx, const void* qkv, const void* bqkv, const void* probs, void* ds_ws, void* dqkv,
+                           int b, int S, int H, int nh, float p, const int* seed, unsigned stream_id, float* bias_acc,
+                           cudaStream_t st) {
+  auto kq = attention_bwd_long_dq_kernel<T>;
+  auto kkv = attention_bwd_long_dkv_kernel<T>;
+  constexpr size_t sq = dq_long_smem(sizeof(T)), skv = dkv_long_smem(sizeof(T));
+  if (cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sq) != cudaSuccess) return -5;
+  if (cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)skv) != cudaSuccess) return -5;
+  const dim3 grid(nh, b, (S + QB - 1) / QB);
+  kq<<<grid, 128, sq, st>>>((const T*)dctx, (const T*)qkv, (const T*)bqkv, (const T*)probs, (T*)ds_ws, (T*)dqkv, S, H, nh, p,
+                            seed, stream_id, bias_acc);
+  kkv<<<grid, 128, skv, st>>>((const T*)dctx, (const T*)qkv, (const T*)bqkv, (const T*)probs, (const T*)ds_ws, (T*)dqkv, S,
+                              H, nh, p, seed, stream_id, bias_acc);
+  return 0;
+}
+
 }  // namespace amma
 }  // namespace rb
 
@@ -467,6 +819,39 @@ RB_API int rb_attention_bwd_mma(int dtype, const void* dctx, const void* qkv, co
   if (dtype == RB_BF16) rc = S <= 32 ? RB_BWD(__nv_bfloat16, 32) : S <= 64 ? RB_BWD(__nv_bfloat16, 64) : RB_BWD(__nv_bfloat16, 128);
   else rc = S <= 32 ? RB_BWD(__half, 32) : S <= 64 ? RB_BWD(__half, 64) : RB_BWD(__half, 128);
 #undef RB_BWD
+  if (rc) return rc;
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+// Sequences of 129..512 tokens (same requirements otherwise).  The backward needs ds_ws, a [b, nh, S, S] scratch of
+// the activation dtype (the softmax gradient, written by its first kernel and read by its second); two launches.
+static bool long_args_ok(int dtype, int b, int S, int H, int nh) {
+  if (S <= 128 || S > 512 || H % nh || H % 8 || H / nh != amma::HD || (dtype != RB_BF16 && dtype != RB_F16)) return false;
+  return (long long)b * nh * S * S < (1LL << 32);   // dropout counters are 32-bit element indices
+}
+
+RB_API int rb_attention_fwd_long(int dtype, const void* qkv, const void* bqkv, const int* mask, void* ctx, void* probs,
+                                 int b, int S, int H, int nh, float p, const int* seed, unsigned stream_id,
+                                 cudaStream_t st) {
+  if (!long_args_ok(dtype, b, S, H, nh)) return -4;
+  const int rc = dtype == RB_BF16
+                     ? amma::launch_fwd_long<__nv_bfloat16>(qkv, bqkv, mask, ctx, probs, b, S, H, nh, p, seed, stream_id, st)
+                     : amma::launch_fwd_long<__half>(qkv, bqkv, mask, ctx, probs, b, S, H, nh, p, seed, stream_id, st);
+  if (rc) return rc;
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+RB_API int rb_attention_bwd_long(int dtype, const void* dctx, const void* qkv, const void* bqkv, const void* probs,
+                                 void* ds_ws, void* dqkv, int b, int S, int H, int nh, float p, const int* seed,
+                                 unsigned stream_id, float* bias_acc, cudaStream_t st) {
+  if (!long_args_ok(dtype, b, S, H, nh) || ds_ws == nullptr) return -4;
+  const int rc = dtype == RB_BF16
+                     ? amma::launch_bwd_long<__nv_bfloat16>(dctx, qkv, bqkv, probs, ds_ws, dqkv, b, S, H, nh, p, seed,
+                                                            stream_id, bias_acc, st)
+                     : amma::launch_bwd_long<__half>(dctx, qkv, bqkv, probs, ds_ws, dqkv, b, S, H, nh, p, seed, stream_id,
+                                                     bias_acc, st);
   if (rc) return rc;
   RB_LAUNCH_CHECK();
   return 0;

@@ -202,12 +202,28 @@ def _attention_entry(direction: str, H: int, nh: int) -> str:
     return f"rb_attention_{direction}_tc"
 
 
+def _attention_long(qkv, S: int, H: int, nh: int, ws) -> bool:
+    """Sequences of 129..512 tokens, 16-bit activations, head dim 64: the blocked kernels of attention_mma.cu
+    (``RENEE_B200_ATTENTION_LONG=0`` sends these shapes to the composed library ops instead)."""
+    return (qkv.dtype != torch.float32 and 128 < S <= 512 and H // nh == 64 and "ds" in ws
+            and os.environ.get("RENEE_B200_ATTENTION_LONG", "") != "0")
+
+
+def _seed_tensor(rng):
+    # the device-resident seed as a non-negative int64 scalar: no host read, so the composed path can be captured
+    return rng.dev.to(torch.int64).reshape(-1)[0] & 0xFFFFFFFF
+
+
 def attention_fwd(qkv, bqkv, mask, nh, p, rng, stream, ctx_out, ws):
     b, S = mask.shape
     H = ctx_out.shape[1]
+    if _attention_long(qkv, S, H, nh, ws):
+        _call("rb_attention_fwd_long", _I(DT[qkv.dtype]), _p(qkv), _p(bqkv), _p(mask), _p(ctx_out), _p(ws["probs"]),
+              _I(b), _I(S), _I(H), _I(nh), _F(p), _p(rng.dev), _U(stream), _stream())
+        return
     if not _attention_fits(qkv, S, H, nh):
         from . import reference as ref
-        ctx, probs = ref.attention_fwd(qkv, bqkv, mask, nh, p, int(rng.dev.item()) & 0xFFFFFFFF, stream)
+        ctx, probs = ref.attention_fwd(qkv, bqkv, mask, nh, p, _seed_tensor(rng), stream)
         ctx_out.copy_(ctx)
         ws["probs"][:b].copy_(probs)
         return
@@ -219,9 +235,16 @@ def attention_fwd(qkv, bqkv, mask, nh, p, rng, stream, ctx_out, ws):
 def attention_bwd(dctx, qkv, bqkv, mask, nh, p, rng, stream, ws, dqkv_out, dbqkv_out):
     b, S = mask.shape
     H = dctx.shape[1]
+    if _attention_long(qkv, S, H, nh, ws):
+        acc = _DEFER.slot([dbqkv_out], 3 * H) if _DEFER is not None else None
+        _call("rb_attention_bwd_long", _I(DT[qkv.dtype]), _p(dctx), _p(qkv), _p(bqkv), _p(ws["probs"]), _p(ws["ds"]),
+              _p(dqkv_out), _I(b), _I(S), _I(H), _I(nh), _F(p), _p(rng.dev), _U(stream), _p(acc), _stream(), launches=2)
+        if acc is None:
+            colsum(dqkv_out, dbqkv_out)
+        return
     if not _attention_fits(qkv, S, H, nh):
         from . import reference as ref
-        d = ref.attention_bwd(dctx, qkv, bqkv, mask, ws["probs"][:b], nh, p, int(rng.dev.item()) & 0xFFFFFFFF, stream)
+        d = ref.attention_bwd(dctx, qkv, bqkv, mask, ws["probs"][:b], nh, p, _seed_tensor(rng), stream)
         dqkv_out.copy_(d)
         colsum(dqkv_out, dbqkv_out)
         return

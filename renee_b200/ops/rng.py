@@ -22,8 +22,10 @@ def _mul32(x: torch.Tensor, c: int) -> torch.Tensor:
     return (lo + hi) & _M32
 
 
-def mix32(seed: int, stream: int, idx: torch.Tensor) -> torch.Tensor:
-    """idx: int64 tensor of non-negative element indices (< 2^32)."""
+def mix32(seed, stream: int, idx: torch.Tensor) -> torch.Tensor:
+    """idx: int64 tensor of non-negative element indices (< 2^32).  ``seed`` is a Python int or an int64 tensor
+    (one element, on ``idx``'s device): the tensor form keeps the whole computation on the device, so it can be
+    recorded into a CUDA graph and follow the device-resident seed from step to step."""
     x = (_mul32(idx & _M32, 0x9E3779B1) + (seed & _M32)) & _M32
     x = x ^ (x >> 16)
     x = _mul32(x, 0x85EBCA6B)
@@ -39,15 +41,17 @@ def mix32(seed: int, stream: int, idx: torch.Tensor) -> torch.Tensor:
     return x
 
 
-def keep_mask(seed: int, stream: int, shape, p: float, device="cpu") -> torch.Tensor:
-    """Boolean keep-mask of ``shape`` (row-major element index), True = element survives."""
+def keep_mask(seed, stream: int, shape, p: float, device="cpu") -> torch.Tensor:
+    """Boolean keep-mask of ``shape`` (row-major element index), True = element survives.  ``seed``: int or
+    one-element integer tensor (see :func:`mix32`)."""
     n = 1
     for s in shape:
         n *= int(s)
     if p <= 0.0:
         return torch.ones(shape, dtype=torch.bool, device=device)
     idx = torch.arange(n, dtype=torch.int64, device=device)
-    u = (mix32(int(seed), int(stream), idx) >> 8).to(torch.float32) * (1.0 / 16777216.0)
+    seed = seed.to(torch.int64).reshape(()) if torch.is_tensor(seed) else int(seed)
+    u = (mix32(seed, int(stream), idx) >> 8).to(torch.float32) * (1.0 / 16777216.0)
     return (u >= p).view(*shape)
 
 

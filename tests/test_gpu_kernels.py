@@ -124,7 +124,9 @@ def test_bias_gelu_colsum_pool_dropout(dt):
 
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32, torch.float16])
 @pytest.mark.parametrize("S,nh,H,p", [(32, 12, 768, 0.1), (128, 2, 128, 0.0), (20, 12, 384, 0.2), (45, 4, 256, 0.1),
-                                      (64, 2, 128, 0.3), (100, 3, 192, 0.1)])
+                                      (64, 2, 128, 0.3), (100, 3, 192, 0.1),
+                                      # 129..512 tokens: blocked kernels (vector and scalar probability paths)
+                                      (200, 3, 192, 0.1), (129, 2, 128, 0.2), (512, 2, 128, 0.1), (256, 12, 768, 0.0)])
 def test_attention(dt, S, nh, H, p):
     if dt == torch.float32 and S >= 100:
         pytest.skip("fp32 tiles of S=128 exceed shared memory; the engine composes library ops there")

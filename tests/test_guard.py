@@ -37,7 +37,7 @@ def test_detects_writes_on_either_side_and_names_the_buffer():
     assert not guard.enabled() and guard.registered() == 0
 
 
-def _tiny_trainer(device, fp16xfc):
+def _tiny_trainer(device, fp16xfc, B=24, S=20):
     from renee_b200.data import xcrepo
     from renee_b200.data.collate import XCCollator
     from renee_b200.data.synthetic import SyntheticSpec, SyntheticXC
@@ -45,13 +45,14 @@ def _tiny_trainer(device, fp16xfc):
     from renee_b200.parallel.dist import DistContext
     from renee_b200.train import TrainConfig, XCTrainer
     from renee_b200.utils.sharding import shard_labels
-    B, S, L = 24, 20, 1000          # ragged on purpose: B not a multiple of 8, L not of 16, S not of 16
+    L = 1000                        # ragged on purpose: B not a multiple of 8, L not of 16, S not of 16
     spec = SyntheticSpec(num_labels=L, seq_len=S, len_lo=3, len_hi=S, poisson_lam=2.0, zipf_s=1.1, seed=1)
     ids, mask, lab = SyntheticXC(spec).rows(np.arange(4 * B))
     ds = xcrepo.InMemoryDataset(ids, mask, lab)
     sh = shard_labels(L, 1)
     ctx = DistContext(rank=0, world_size=1, local_rank=0, device=torch.device(device), backend=None)
-    enc = EncoderConfig(vocab_size=30522, dim=128, n_layers=2, n_heads=2, hidden_dim=256, max_position_embeddings=64)
+    enc = EncoderConfig(vocab_size=30522, dim=128, n_layers=2, n_heads=2, hidden_dim=256,
+                        max_position_embeddings=max(64, S))
     cfg = TrainConfig(batch_size=B, epochs=1, seed=0, dropout=0.5, lr1=0.05, lr2=1e-4, warmup=10, wd1=1e-4,
                       noloss=False, fp16xfc=fp16xfc, maxlen=S, pooling="mean")
     tr = XCTrainer(cfg, enc, sh, ctx, steps_per_epoch=100)
@@ -87,3 +88,21 @@ def test_kernels_leave_guard_bands_intact():
         tr.check_device_status()
         cu.check_status()
         assert torch.isfinite(tr.xfc.W.float()).all()
+
+
+@pytest.mark.gpu
+def test_long_sequence_step_from_graph_leaves_guard_bands_intact():
+    """Sequences of 129..512 tokens take the blocked attention kernels (two-pass forward, dQ and dK/dV backward
+    kernels with a softmax-gradient scratch): a few steps, eager and replayed from the CUDA graph."""
+    from renee_b200.ops import cuda as cu
+    with guard.enabled_for_test():
+        tr, batches = _tiny_trainer("cuda:0", fp16xfc=True, B=6, S=164)
+        w0 = tr.encoder.p32.clone()
+        for i in range(6):
+            tr.train_step(batches[i % len(batches)])
+        torch.cuda.synchronize()
+        tr.check_device_status()
+        cu.check_status()
+        assert tr.graph_active()
+        assert "ds" in tr.encoder._acts["layers"][0]["att"]
+        assert torch.isfinite(tr.encoder.p32).all() and not torch.equal(w0, tr.encoder.p32)
