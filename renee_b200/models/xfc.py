@@ -57,6 +57,8 @@ class XFCClassifier:
         """Rows are generated in fixed chunks keyed by their GLOBAL label index, so the assembled
         ``[Lp, D]`` matrix does not depend on the number of ranks (the reference seeds every rank
         identically, which makes all shards start equal — main.py:22, dl_base.py:187)."""
+        if self.device.type == "meta":      # size-accounting dry runs (utils/memory_plan.py): nothing to fill
+            return
         lo = self.rank * self.Ls
         hi = lo + self.Ls
         g = torch.Generator(device=self.device)

@@ -135,7 +135,7 @@ class XCTrainer:
             os.makedirs(self.out_dir, exist_ok=True)
         self.B = cfg.batch_size * self.G
         self.Ls = sharding.labels_per_rank
-        on_gpu = self.device.type == "cuda"
+        on_gpu = self.device.type in ("cuda", "meta")     # meta: size-accounting dry runs plan for a GPU
         self.act_dtype = torch.float32 if (cfg.fp32encoder or not on_gpu) else \
             (torch.bfloat16 if cfg.encoder_dtype == "bf16" else torch.float16)
         self.xfc_sched = CosineWarmupSchedule(cfg.lr1, cfg.warmup, self.total_steps)
