@@ -106,3 +106,47 @@ def test_long_sequence_step_from_graph_leaves_guard_bands_intact():
         assert tr.graph_active()
         assert "ds" in tr.encoder._acts["layers"][0]["att"]
         assert torch.isfinite(tr.encoder.p32).all() and not torch.equal(w0, tr.encoder.p32)
+
+
+def test_symmetric_allocation_addresses_follow_the_payload(monkeypatch):
+    """``PeerCollectives._symm`` with a stand-in for the symmetric-memory module: without guard mode the peer and
+    multicast addresses are the allocation's own; in guard mode they are shifted by one band, like the payload."""
+    import sys
+    import types
+    from renee_b200.parallel import fused
+
+    class Handle:
+        def __init__(self, t):
+            self.buffer_ptrs = [t.data_ptr(), t.data_ptr() + (1 << 30)]
+            self.multicast_ptr = 1 << 40
+
+    fake = types.ModuleType("torch.distributed._symmetric_memory")
+    fake.empty = lambda n, dtype, device: torch.empty(n, dtype=dtype, device=device)
+    fake.rendezvous = lambda t, group: Handle(t)
+    monkeypatch.setitem(sys.modules, "torch.distributed._symmetric_memory", fake)
+    import torch.distributed as dist
+    monkeypatch.setattr(dist, "_symmetric_memory", fake, raising=False)
+
+    class Ctx:
+        device = torch.device("cpu")
+
+    def make():
+        pc = fused.PeerCollectives.__new__(fused.PeerCollectives)
+        pc.ctx, pc.group, pc._handles, pc.use_nvls = Ctx(), None, [], True
+        return pc
+
+    guard.enable(False)
+    pc = make()
+    t, ptrs = pc._symm(1000, torch.float16)
+    assert t.numel() == 1000 and ptrs[0] == t.data_ptr() and ptrs[1] == t.data_ptr() + (1 << 30)
+    assert pc._last_multicast == 1 << 40
+    with guard.enabled_for_test():
+        pc = make()
+        t, ptrs = pc._symm(1000, torch.float16)
+        assert t.numel() == 1000 and ptrs[0] == t.data_ptr() and ptrs[1] == t.data_ptr() + (1 << 30)
+        assert pc._last_multicast == (1 << 40) + guard.BAND_BYTES
+        t.fill_(1.0)
+        guard.assert_clean()
+        pc.use_nvls = False
+        pc._symm(10, torch.int32)
+        assert pc._last_multicast == 0
