@@ -293,6 +293,186 @@ xfc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   }
 }
 
+// ------------------------------------------------------------------------------------ persistent logits GEMM
+// Same math as xfc_gemm_kernel<MODE_LOGITS / MODE_RAW> for label chunks of many tiles: one CTA per SM walks the
+// tiles tile = blockIdx.x, blockIdx.x + gridDim.x, ...; the shared-memory ring keeps streaming across tile
+// boundaries, and TMEM holds TWO accumulators (2 x 256 columns) so that the epilogue of tile i (sigmoid, fp16
+// stores, positives) runs under the loads and MMAs of tile i + 1 instead of after them.  Barriers: full / empty per
+// ring stage as before, tmem_full[2] (MMA warp -> epilogue, one commit) and tmem_empty[2] (epilogue -> MMA warp,
+// one arrival per epilogue warp).  Opt-in (rb_xfc_set_persistent), off by default.
+constexpr int kAccBufs = 2;
+constexpr int kTmemColsPersistent = kAccBufs * 256;
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+xfc_logits_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                             const GemmParams p, const int n_m_tiles, const int n_n_tiles) {
+  static_assert(MODE == MODE_LOGITS || MODE == MODE_RAW, "logits modes only");
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tmem_full_bar = empty_bar + kStages;       // [kAccBufs]
+  uint64_t* tmem_empty_bar = tmem_full_bar + kAccBufs; // [kAccBufs]
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(tmem_empty_bar + kAccBufs);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n_tiles = n_m_tiles * n_n_tiles;
+  const uint32_t b_bytes = (uint32_t)p.BN * kBK * 2;
+
+  if (threadIdx.x == 0) {
+    tc::prefetch_tmap(&tmA);
+    tc::prefetch_tmap(&tmB);
+    for (int s = 0; s < kStages; ++s) { tc::mbar_init(full_bar + s, 1); tc::mbar_init(empty_bar + s, 1); }
+    for (int a = 0; a < kAccBufs; ++a) { tc::mbar_init(tmem_full_bar + a, 1); tc::mbar_init(tmem_empty_bar + a, 4); }
+    *s_abort = 0;
+    tc::fence_barrier_init();
+  }
+  if (warp == 1) tc::tmem_alloc(tmem_ptr_smem, kTmemColsPersistent);
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+  bool aborted = false;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------- TMA producer: one continuous stream of (tile, k block) stages
+    if (MODE == MODE_LOGITS && p.wait_flags != nullptr) {
+      const uint32_t want = p.tag.value();
+      for (int q = 0; q < p.wait_n; ++q)
+        if (!wait_flag(p.wait_flags + q, want, p.status, 100 + q)) aborted = true;
+      asm volatile("fence.proxy.async;" ::: "memory");
+    }
+    int it = 0;
+    for (int tile = blockIdx.x; tile < n_tiles && !aborted; tile += gridDim.x) {
+      const int m0 = (tile / n_n_tiles) * kBM, n0 = (tile % n_n_tiles) * p.BN;
+      for (int kb = 0; kb < p.kb_total; ++kb, ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1;
+        if (!tc::mbar_wait(empty_bar + s, ph ^ 1, aborted, p.status, tc::SITE_EMPTY, kb)) break;
+        uint8_t* sA = smem + s * kStageBytes;
+        uint8_t* sB = sA + kABytes;
+        tc::mbar_expect_tx(full_bar + s, kABytes + b_bytes);
+        tc::tma_load_2d(sA, &tmA, full_bar + s, kb * kBK, m0);
+        tc::tma_load_2d(sB, &tmB, full_bar + s, kb * kBK, n0);
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------- MMA issuer: accumulator t_local & 1, reused every second tile once the epilogue has drained it
+    const uint32_t idesc = tc::make_idesc(0, 0, 0, kBM, p.BN);
+    int it = 0, t_local = 0;
+    for (int tile = blockIdx.x; tile < n_tiles && !aborted; tile += gridDim.x, ++t_local) {
+      const int buf = t_local & 1;
+      const uint32_t use = (uint32_t)(t_local >> 1);
+      if (!tc::mbar_wait(tmem_empty_bar + buf, (use & 1) ^ 1, aborted, p.status, tc::SITE_TMEM_EMPTY, tile)) break;
+      tc::tc_fence_after();
+      const uint32_t d_tmem = tmem_base + (uint32_t)buf * 256u;
+      for (int kb = 0; kb < p.kb_total; ++kb, ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1;
+        if (!tc::mbar_wait(full_bar + s, ph, aborted, p.status, tc::SITE_FULL, kb)) break;
+        tc::tc_fence_after();
+        const uint32_t sA = tc::smem_u32(smem + s * kStageBytes);
+        const uint32_t sB = sA + kABytes;
+#pragma unroll
+        for (int k = 0; k < kBK / 16; ++k) {
+          const uint64_t ad = tc::make_smem_desc(sA + k * 32, 16, 1024);
+          const uint64_t bd = tc::make_smem_desc(sB + k * 32, 16, 1024);
+          tc::umma_f16(d_tmem, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        }
+        tc::umma_commit(empty_bar + s);
+      }
+      if (aborted) break;
+      tc::umma_commit(tmem_full_bar + buf);
+    }
+  } else if (warp >= 2) {
+    // ---------------- epilogue warps: TMEM lane quarter each; all four take the same decisions (named barrier 1)
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    float loss = 0.f;
+    int t_local = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t_local) {
+      const int m0 = (tile / n_n_tiles) * kBM, n0 = (tile % n_n_tiles) * p.BN;
+      const int row = m0 + r;
+      const int buf = t_local & 1;
+      const uint32_t use = (uint32_t)(t_local >> 1);
+      if (!tc::mbar_wait(tmem_full_bar + buf, use & 1, aborted, p.status, tc::SITE_TMEM_FULL, tile)) *s_abort = 1;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*s_abort) break;                                  // the same answer in all four warps
+      tc::tc_fence_after();
+      const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * 256u;
+      for (int c0 = 0; c0 < p.BN; c0 += 32) {
+        float v[32];
+        tc::tmem_ld32(tbase + c0, v);
+        const int col0 = n0 + c0;
+        if (MODE == MODE_LOGITS) {
+          if (row < p.M) {
+            if (p.loss_acc != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) loss += fmaxf(v[j], 0.f) + log1pf(__expf(-fabsf(v[j])));
+            }
+#pragma unroll
+            for (int j8 = 0; j8 < 4; ++j8) {
+              const int c = col0 + 8 * j8;
+              if (c < p.ldG) {
+                uint4 pk;
+                __half2* h2 = reinterpret_cast<__half2*>(&pk);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float a = (c + 2 * j < p.N) ? 1.f / (1.f + __expf(-v[8 * j8 + 2 * j])) : 0.f;
+                  const float b = (c + 2 * j + 1 < p.N) ? 1.f / (1.f + __expf(-v[8 * j8 + 2 * j + 1])) : 0.f;
+                  h2[j] = __floats2half2_rn(a, b);
+                }
+                *reinterpret_cast<uint4*>(p.Gt + (size_t)row * p.ldG + c) = pk;
+              }
+            }
+          }
+        } else {
+          if (row < p.M) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) p.Zout[(size_t)(col0 + j) * p.ldG + row] = v[j];
+          }
+        }
+      }
+      // every tcgen05.ld of this tile has completed (tmem_ld32 waits): hand the accumulator back to the MMA warp
+      tc::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(tmem_empty_bar + buf);
+      if (MODE == MODE_LOGITS) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");      // all four warps have stored their rows of this tile
+        if (p.pos_labels != nullptr) {
+          const int nnz = *p.nnz_ptr;
+          const int lab_lo = p.label0 + m0;
+          const int lab_hi = p.label0 + min(m0 + kBM, p.M);
+          const int e0 = lower_bound_i32(p.pos_labels, nnz, lab_lo);
+          const int e1 = lower_bound_i32(p.pos_labels, nnz, lab_hi);
+          for (int e = e0 + (int)threadIdx.x - 64; e < e1; e += 128) {
+            const int b = p.pos_rows[e];
+            if (b >= n0 && b < min(n0 + p.BN, p.N)) {
+              __half* g = p.Gt + (size_t)(p.pos_labels[e] - p.label0) * p.ldG + b;
+              *g = __float2half_rn(__half2float(*g) - 1.f);
+            }
+          }
+        }
+      }
+    }
+    if (MODE == MODE_LOGITS && p.loss_acc != nullptr) {
+      loss = warp_sum(loss);
+      if (lane == 0) atomicAdd(p.loss_acc, loss);
+    }
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc::tc_fence_after();
+    tc::tmem_dealloc(tmem_base, kTmemColsPersistent);
+  }
+}
+
 // ------------------------------------------------------------------------------------ dW + SGD, W/M tiles staged by TMA
 // Same math as xfc_gemm_kernel<MODE_DW>, restructured because the kernel is bound by the W / momentum
 // traffic, not by the MMA: the producer warp first issues TMA loads of this CTA's [128 x <=256] tiles of W
@@ -549,6 +729,36 @@ static int launch_gemm(const CUtensorMap& a, const CUtensorMap& b, const GemmPar
 
 static int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
+static int g_xfc_persistent = 0;
+// Chooses the persistent logits kernel for chunks with more tiles than SMs (0 = off, the default).
+RB_API void rb_xfc_set_persistent(int on) { g_xfc_persistent = on ? 1 : 0; }
+RB_API int rb_xfc_get_persistent(void) { return g_xfc_persistent; }
+
+static int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1)
+      n = 148;
+  }
+  return n;
+}
+
+template <int MODE>
+static int launch_persistent(const CUtensorMap& a, const CUtensorMap& b, const GemmParams& p, int n_m_tiles, int n_n_tiles,
+                             cudaStream_t st) {
+  static bool attr_set = false;
+  auto k = xfc_logits_persistent_kernel<MODE>;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) return -5;
+    attr_set = true;
+  }
+  const int n_tiles = n_m_tiles * n_n_tiles;
+  const int ctas = n_tiles < sm_count() ? n_tiles : sm_count();
+  k<<<ctas, kThreads, kSmemBytes, st>>>(a, b, p, n_m_tiles, n_n_tiles);
+  return 0;
+}
+
 // Gt[Lc, ldG] = sigmoid(W X^T) - Y for the label chunk W[Lc, D]; labels of the chunk are
 // label0 .. label0+Lc-1 in the numbering of pos_labels.  raw_out != null writes fp32 logits instead
 // (no sigmoid, no positives), batch-major, into raw_out[B, ldG] with ldG >= Lc.
@@ -570,7 +780,13 @@ RB_API int rb_xfc_logits_grad(const void* W, int Lc, int D, const void* X, int B
   p.label0 = label0; p.loss_acc = loss_acc; p.Zout = raw_out;
   p.wait_flags = wait_flags; p.wait_n = wait_n; p.tag = StepTag{step_ptr, 1u, 0u};
   dim3 grid((Lc + kBM - 1) / kBM, (B + BN - 1) / BN, 1);
-  rc = raw_out ? launch_gemm<MODE_RAW>(ta, tb, p, grid, st) : launch_gemm<MODE_LOGITS>(ta, tb, p, grid, st);
+  if (g_xfc_persistent && (int)(grid.x * grid.y) > sm_count()) {
+    // more tiles than SMs: one persistent CTA per SM, epilogues overlapped with the next tile's main loop
+    rc = raw_out ? launch_persistent<MODE_RAW>(ta, tb, p, (int)grid.x, (int)grid.y, st)
+                 : launch_persistent<MODE_LOGITS>(ta, tb, p, (int)grid.x, (int)grid.y, st);
+  } else {
+    rc = raw_out ? launch_gemm<MODE_RAW>(ta, tb, p, grid, st) : launch_gemm<MODE_LOGITS>(ta, tb, p, grid, st);
+  }
   if (rc) return rc;
   RB_LAUNCH_CHECK();
   return 0;

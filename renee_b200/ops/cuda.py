@@ -347,6 +347,12 @@ def xfc_logits_grad(W, X, Gt, ldG, pos_rows, pos_labels, nnz, label0, loss_acc=N
           _p(nnz), _I(label0), _p(loss_acc), _p(raw_out), _p(wf), _I(wn), _p(wstep), _p(ws.status), _stream())
 
 
+def set_xfc_persistent(on: bool) -> None:
+    """Chooses the persistent logits kernel (one CTA per SM walking the tiles, epilogue of tile i under the main
+    loop of tile i + 1) for label chunks with more 128-label tiles than SMs.  Off by default."""
+    lib().rb_xfc_set_persistent(_I(1 if on else 0))
+
+
 def xfc_dx(Gt, ldG, W, B, dX, hp_buf, splits, signal=None):
     """``signal = (counter_tensor, peer_flag_ptr_array, n_peers, flag_index, step_tensor)``: the last CTA
     stores ``*step`` into word ``flag_index`` of every peer's flag array (reduce-scatter signal)."""

@@ -235,6 +235,34 @@ def test_xfc_logits_grad(B, D, Lc, nnz):
         torch.testing.assert_close(torch.gather(raw[:, :Lc], 1, (oi - 7).long()), ov, rtol=0, atol=0)
 
 
+@pytest.mark.parametrize("B,D,Lc,nnz", [(256, 768, 24676, 3000), (100, 128, 40000, 500), (512, 64, 21000, 100)])
+def test_xfc_logits_persistent_kernel_is_bit_identical(B, D, Lc, nnz):
+    """More tiles than SMs: the persistent kernel (several tiles per CTA, double-buffered accumulators) must give
+    exactly what the one-tile-per-CTA kernel gives -- same MMAs in the same order, same epilogue."""
+    X, W, rows, labels = _xfc_problem(B, D, Lc, nnz)
+    ldG = (B + 7) // 8 * 8
+    ldZ = (Lc + 7) // 8 * 8
+    n = torch.tensor([rows.numel()], dtype=torch.int32, device=dev())
+    out = []
+    try:
+        for persistent in (False, True):
+            cu().set_xfc_persistent(persistent)
+            Gt = torch.full((Lc, ldG), 7.0, dtype=torch.float16, device=dev())
+            loss = torch.zeros(1, device=dev())
+            cu().xfc_logits_grad(W, X, Gt, ldG, rows, labels, n, 0, loss_acc=loss)
+            raw = torch.zeros(B, ldZ, device=dev())
+            cu().xfc_logits_grad(W, X, None, ldZ, None, None, None, 0, raw_out=raw)
+            cu().check_status()
+            out.append((Gt, loss, raw))
+    finally:
+        cu().set_xfc_persistent(False)
+    torch.testing.assert_close(out[1][0], out[0][0], rtol=0, atol=0)
+    torch.testing.assert_close(out[1][2], out[0][2], rtol=0, atol=0)
+    torch.testing.assert_close(out[1][1], out[0][1], rtol=1e-4, atol=1e-2)      # loss: atomics in another order
+    Zr = X.float() @ W.float().t()
+    torch.testing.assert_close(out[1][2][:, :Lc], Zr, rtol=1e-3, atol=1e-3)
+
+
 @pytest.mark.parametrize("B,D,Lc,nnz", XFC_SHAPES)
 def test_xfc_dx(B, D, Lc, nnz):
     X, W, rows, labels = _xfc_problem(B, D, Lc, nnz)
