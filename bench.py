@@ -118,6 +118,8 @@ def run_ours(args) -> dict:
     cfg = TrainConfig(batch_size=B // G, epochs=1, seed=0, dropout=c["dropout"], lr1=0.05, lr2=1e-5, warmup=5000,
                       wd1=1e-4, noloss=True, fp16xfc=True, maxlen=c["seq"], pooling="cls",
                       cuda_graph=not args.no_graph, fused_comm=not args.no_fused_comm)
+    if args.persistent_logits:
+        cu.set_xfc_persistent(True)
     comm = None
     if G > 1 and cfg.fused_comm:
         from renee_b200.parallel.fused import PeerCollectives
@@ -185,7 +187,8 @@ def run_ours(args) -> dict:
                       "parallelism": f"dp{G} encoder + label-sharded classifier x{G}",
                       "flags": "--fp16xfc --noloss --dropout 0.85 --lr1 0.05 --lr2 1e-5 --wd1 1e-4, CLS pooling",
                       "l2": "per-step working set (W, momentum, encoder params/moments/activations) exceeds the 126 MB L2",
-                      "cuda_graph": tr.graph_active(), "fused_comm": comm is not None},
+                      "cuda_graph": tr.graph_active(), "fused_comm": comm is not None,
+                      "persistent_logits": bool(args.persistent_logits)},
            "clocks": clocks,
            "e2e": {"value": round(B * K / (e2e_ms / 1e3), 2), "unit": "samples/s", "ms_per_step": round(e2e_ms / K, 4),
                    "h2d_bytes_per_step": h2d // K, "d2h_bytes_per_step": 64},
@@ -205,6 +208,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-fused-comm", action="store_true")
+    ap.add_argument("--persistent-logits", action="store_true",
+                    help="classifier logits GEMM: persistent CTAs with double-buffered TMEM accumulators")
     ap.add_argument("--custom-cuda", action="store_true", help="reference arm: route its GEMMs to its CUTLASS extension")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
