@@ -57,3 +57,30 @@ def test_profile_step_and_epoch_log(tmp_path):
     tr.fit(loader, log=lambda *a: None)
     recs = read_jsonl(os.path.join(str(tmp_path), "renee-exp_log.jsonl"))
     assert recs[-1]["kind"] == "epoch" and recs[-1]["rows"] == 64
+
+
+def test_dropout_mask_from_a_tensor_seed_equals_the_integer_seed_mask():
+    """The composed attention path takes the seed as a device tensor (no host read, so it can be captured into a
+    CUDA graph); the mask must be the one the kernels derive from the same seed."""
+    import torch
+    from renee_b200.ops import reference as ref
+    from renee_b200.ops.rng import keep_mask
+    seed = 0x9E3779B1            # above 2^31: the device word is a negative int32
+    as_i32 = torch.tensor([seed - (1 << 32)], dtype=torch.int32)
+    a = keep_mask(seed, 11, (3, 4, 9, 9), 0.25)
+    b = keep_mask(as_i32.to(torch.int64).reshape(-1)[0] & 0xFFFFFFFF, 11, (3, 4, 9, 9), 0.25)
+    assert torch.equal(a, b) and 0.6 < a.float().mean() < 0.9
+    torch.manual_seed(0)
+    qkv, bq = torch.randn(2 * 9, 3 * 16), torch.randn(3 * 16) * 0.1
+    mask = torch.ones(2, 9, dtype=torch.int32)
+    c1, p1 = ref.attention_fwd(qkv, bq, mask, 2, 0.25, seed, 4)
+    c2, p2 = ref.attention_fwd(qkv, bq, mask, 2, 0.25, torch.tensor(seed, dtype=torch.int64), 4)
+    assert torch.equal(c1, c2) and torch.equal(p1, p2)
+
+
+def test_nvtx_ranges_are_noops_when_disabled():
+    from renee_b200.utils.timing import nvtx_enabled, nvtx_range
+    assert not nvtx_enabled()
+    with nvtx_range("phase"):
+        x = 1
+    assert x == 1
