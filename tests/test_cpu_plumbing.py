@@ -3,7 +3,6 @@ encoder, seq 32 with lengths 8-32, batch 32, fp32, SGD momentum 0.9 lr 0.05 for 
 lr 1e-5 for the encoder, seed 0, 1+Poisson(2) positives from Zipf(1.1)) trained with plain PyTorch BCE,
 and the same task through the loss-skipping path: both must learn, and end at the same weights."""
 import numpy as np
-import torch
 
 from renee_b200.data import xcrepo
 from renee_b200.data.collate import GlobalBatchSampler, PrefetchLoader, XCCollator
