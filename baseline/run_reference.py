@@ -28,10 +28,14 @@ REF = os.path.join(HERE, "_ref")
 SHIMS = os.path.join(HERE, "shims")
 
 
+_ZIPF_CUM: dict = {}
+
+
 def _zipf_sample(rng, L, s, n):
     head = min(L, 1 << 20)
-    w = np.power(np.arange(1, head + 1, dtype=np.float64), -s)
-    cum = np.cumsum(w)
+    cum = _ZIPF_CUM.get((head, s))
+    if cum is None:
+        cum = _ZIPF_CUM[(head, s)] = np.cumsum(np.power(np.arange(1, head + 1, dtype=np.float64), -s))
     tail = 0.0
     if L > head:
         tail = ((L + 0.5) ** (1 - s) - (head + 0.5) ** (1 - s)) / (1 - s)
@@ -75,6 +79,36 @@ def _write_dataset(root, c, n_trn, n_tst, seed=0):
         pass  # another rank won the race
 
 
+def _preflight(c, G, B, accum, custom_cuda, local):
+    """Sizes the reference's classifier state from its source before anything is allocated, so that a
+    configuration it cannot hold is reported instead of driving the box out of memory.  Per rank, with
+    ``n = Ls * 768`` elements: fp32 parameter built on the HOST first (dl_base.py:185-187, then ``model.cuda()``,
+    main.py:157); on the device fp32 W + fp32 .grad + fp32 momentum + the per-step fp16 copy (dl_base.py:562) =
+    14 n bytes, the fp16 ``[B/accum, Ls]`` logits buffer (dl_base.py:176), and on the cuBLAS path an fp16
+    ``[Ls, 768]`` product before its fp32 cast (dl_base.py:625-631); about 3 GB for the encoder, its
+    optimizer state, activations and the CUDA context."""
+    import torch
+    per_rank = (c["labels"] + G - 1) // G
+    Ls = (per_rank + 15) // 16 * 16                      # main.py:76-87
+    n = Ls * 768
+    dev = 14 * n + 2 * (B // accum) * Ls + (0 if custom_cuda else 2 * n) + 3e9
+    total = torch.cuda.get_device_properties(local).total_memory
+    if dev > total:
+        return (f"reference classifier state needs about {dev / 1e9:.0f} GB per GPU at {Ls} labels per rank "
+                f"(fp32 W+grad+momentum, fp16 copy, [B/accum, Ls] logits, cuBLAS temporaries; accum={accum}) "
+                f"but the device has {total / 1e9:.0f} GB")
+    host = 4 * n * G * 1.25
+    try:
+        import psutil
+        avail = psutil.virtual_memory().available
+    except Exception:
+        avail = None
+    if avail is not None and host > avail:
+        return (f"reference builds its fp32 classifier on the host first: {host / 1e9:.0f} GB for {G} ranks, "
+                f"{avail / 1e9:.0f} GB of host memory available")
+    return None
+
+
 def _wait_for(path, timeout=600.0):
     t0 = time.time()
     while not os.path.exists(path):
@@ -93,6 +127,10 @@ def run_reference(args, c) -> dict | None:
     G = int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
     K, W, B = args.steps, args.warmup, c["batch"]
+    accum = max(1, int(getattr(args, "accum", 1)))
+    why = _preflight(c, G, B, accum, bool(getattr(args, "custom_cuda", False)), local)
+    if why is not None:
+        return {"impl": "reference", "unavailable": why} if rank == 0 else None
     work = os.environ.get("RENEE_REF_WORKDIR", "/tmp/renee_ref")
     data = os.path.join(work, f"LF-Synthetic-{c['labels']}-s{c['seq']}-n{(W + K) * B}")
     model_dir = os.path.join(work, "distilbert-random-init")
@@ -155,9 +193,16 @@ def run_reference(args, c) -> dict | None:
         data_dir=data, custom_cuda=bool(getattr(args, "custom_cuda", False)), default_impl=False, batch_size=B // G,
         epochs=1, expname="bench", device=None, dist_url=f"tcp://127.0.0.1:{port}", rank=0, world_size=G, seed=42,
         bottleneck_dims=0, dropout=c["dropout"], lr1=0.05, lr2=1e-5, mo=0.9, wd1=1e-4, wd2=0.01, fp32encoder=False,
-        fp16xfc=True, noloss=True, checkpoint_resume="", infer=False, warmup=5000, accum=1, pre_tok=True,
+        fp16xfc=True, noloss=True, checkpoint_resume="", infer=False, warmup=5000, accum=accum, pre_tok=True,
         maxlen=c["seq"], tf=model_dir, use_ngame_encoder="", compile=False)
-    refmain.start(local, max(G, 1), ns)
+    try:
+        refmain.start(local, max(G, 1), ns)
+    except torch.cuda.OutOfMemoryError as exc:
+        msg = str(exc).splitlines()[0][:300]
+        print(f"reference arm, rank {rank}: {msg}", file=sys.stderr, flush=True)
+        if G > 1:
+            os._exit(0 if rank else 3)     # the other ranks sit in a collective: leave without joining it
+        return {"impl": "reference", "unavailable": f"reference ran out of device memory: {msg}"}
     if state["ev0"] is None or state["ev1"] is None:
         return {"impl": "reference", "unavailable": "reference loop ended before the timed region"} if rank == 0 else None
     ms = state["ev0"].elapsed_time(state["ev1"])
@@ -177,10 +222,14 @@ def run_reference(args, c) -> dict | None:
             "n_gpus": G, "steps": K, "warmup": W, "ms_per_step": round(ms / K, 4), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "fp16 autocast encoder, fp16 classifier compute (fp32 master)",
             "data": "synthetic seeded, random-init weights", "impl": "reference",
-            "config": {"model": f"HF DistilBERT 6x768 + label-sharded XFC, L={c['labels']}", "global_batch": B,
-                       "seq_len": c["seq"], "labels": c["labels"], "parallelism": f"DDP x{G} + label-sharded classifier",
+            "config": {"model": f"DistilBERT-style 6x768 encoder + label-sharded XFC, L={c['labels']}",
+                       "name": getattr(args, "config", ""), "global_batch": B,
+                       "seq_len": c["seq"], "labels": c["labels"],
+                       "parallelism": f"dp{G} encoder + label-sharded classifier x{G}",
                        "flags": "--fp16xfc --noloss --dropout 0.85 --lr1 0.05 --lr2 1e-5 --wd1 1e-4"
-                                + (" --custom-cuda" if ns.custom_cuda else ""),
+                                + (f" --accum {accum}" if accum > 1 else ""),
+                       "arm": "HF DistilBertModel under DDP, mean pooling, fp16 autocast"
+                              + (", --custom-cuda" if ns.custom_cuda else ""),
                        "note": "the reference's loop is end to end by construction: DataLoader, pageable H2D, step"},
             "clocks": state["clocks"],
             "e2e": {"value": round(value, 2), "unit": "samples/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 0},

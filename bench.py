@@ -5,9 +5,13 @@
 For N > 1 launch with ``python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr
 127.0.0.1 --master-port P bench.py --gpus N ...`` (one rank per GPU, NCCL).  Rank 0 prints ONE JSON
 line.  ``value`` is the whole-job samples/s of K device-timed steps (CUDA events, max over ranks)
-with inputs already resident; ``e2e`` times the same K steps through the public
-``XCTrainer.train_step`` call, including the pinned host→device copy of every step's inputs and a
-device→host read of the step's result.  The global batch is fixed, so scaling is strong.
+with inputs already resident (``ms_per_step_min/median/max`` come from one event per step); ``e2e``
+times K steps the way ``XCTrainer.fit`` runs them: batches drawn from the prefetching loader (sampling,
+collation and pinning inside the timed region), the public ``XCTrainer.train_step`` call with its
+pinned host→device copy of every step's inputs, and a device→host read of the step's result;
+``e2e_precollated`` is the same without the loader.  Warm-up continues past ``--warmup`` until every
+CUDA graph the run replays exists, and the run asserts that no capture happened while timing.  The
+global batch is fixed, so scaling is strong.
 Synthetic seeded data of the configuration's shape, random-init weights.
 
 ``--impl reference`` runs the unmodified reference (``baseline/_ref``) through its own ``start()``
@@ -36,10 +40,6 @@ CONFIGS = {
     "131k-s32-shard8": dict(labels=16384, seq=32, len_lo=6, batch=32, lam=1.3, zipf=1.1, dropout=0.85),
     "tiny": dict(labels=8192, seq=32, len_lo=6, batch=64, lam=1.3, zipf=1.1, dropout=0.85),
 }
-
-
-# Reference samples/s measured on the same box type with `--impl reference`
-REFERENCE_MEASURED = {("131k-s32", 1): 22446.22, ("131k-s32", 2): 20270.47}
 
 
 class ClockSampler:
@@ -93,7 +93,7 @@ def run_ours(args) -> dict:
     import torch.distributed as dist
 
     from renee_b200.data import xcrepo
-    from renee_b200.data.collate import XCCollator
+    from renee_b200.data.collate import GlobalBatchSampler, PrefetchLoader, XCCollator
     from renee_b200.data.synthetic import SyntheticSpec, SyntheticXC
     from renee_b200.models.encoder import EncoderConfig
     from renee_b200.ops import cuda as cu
@@ -110,88 +110,138 @@ def run_ours(args) -> dict:
     K, W = args.steps, args.warmup
     spec = SyntheticSpec(num_labels=c["labels"], seq_len=c["seq"], len_lo=c["len_lo"], len_hi=c["seq"],
                          poisson_lam=c["lam"], zipf_s=c["zipf"], seed=0)
-    n_batches = min(W + K, 24)
+    n_batches = min(max(W + K, 8), 48)
     ids, mask, lab = SyntheticXC(spec).rows(np.arange(n_batches * B))
     ds = xcrepo.InMemoryDataset(ids, mask, lab)
     sh = shard_labels(c["labels"], G)
     enc_cfg = EncoderConfig()
     cfg = TrainConfig(batch_size=B // G, epochs=1, seed=0, dropout=c["dropout"], lr1=0.05, lr2=1e-5, warmup=5000,
-                      wd1=1e-4, noloss=True, fp16xfc=True, maxlen=c["seq"], pooling="cls",
+                      wd1=1e-4, noloss=True, fp16xfc=True, maxlen=c["seq"], pooling="cls", accum=args.accum,
                       cuda_graph=not args.no_graph, fused_comm=not args.no_fused_comm)
     if args.persistent_logits:
         cu.set_xfc_persistent(True)
     comm = None
     if G > 1 and cfg.fused_comm:
         from renee_b200.parallel.fused import PeerCollectives
-        comm = PeerCollectives(ctx)
+        comm = PeerCollectives(ctx, use_nvls=True if args.nvls else None)
     tr = XCTrainer(cfg, enc_cfg, sh, ctx, steps_per_epoch=100000, comm=comm)
-    coll = XCCollator(sh, ds, rank, 1, B, True)
+    if G > 1 and not args.no_watchdog:
+        # the CLI's training path runs with the heartbeat watchdog; so does the benchmark
+        from renee_b200.parallel.watchdog import Heartbeat
+        store = dist.distributed_c10d._get_default_store()
+        tr.watchdog = Heartbeat(store, rank, G, interval=1.0, timeout=60.0).start()
+    coll = XCCollator(sh, ds, rank, args.accum, max(1, B // args.accum), True)
     batches = [coll(np.arange(i * B, (i + 1) * B)).pin() for i in range(n_batches)]
+    b_local = batches[0].input_ids.shape[0]
 
     def barrier():
         if G > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(W):
-        tr.train_step(batches[i % n_batches])
+    # ---- warm-up: at least W steps, and until every CUDA graph the run will replay has been captured
+    warm = 0
+    while warm < W or (not tr.graphs_ready(b_local, B) and warm < W + 12):
+        tr.train_step(batches[warm % n_batches])
+        warm += 1
     barrier()
     cu.check_status()
+    if cfg.cuda_graph:
+        assert tr.graphs_ready(b_local, B) and tr.graph_active(), "CUDA graphs not captured during warm-up"
+    captures0 = tr.n_captures
 
-    # ---- device-timed region: inputs resident, K full steps
+    # ---- device-timed region: inputs resident, K full steps, one event per step
     sampler = ClockSampler(ctx.device.index or 0)
     if rank == 0:
         sampler.start()
-    tr.stage_batch(batches[W % n_batches])
+    tr.stage_batch(batches[warm % n_batches])
     barrier()
     l0 = cu.launch_count()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(K + 1)]
+    evs[0].record()
     for i in range(K):
         tr.device_step()
-    ev1.record()
+        evs[i + 1].record()
     barrier()
     launches = tr.launches_per_step() * K if tr.graph_active() else cu.launch_count() - l0
-    ms = ev0.elapsed_time(ev1)
-    # ---- end-to-end region through the public API: pinned H2D of each step's inputs + D2H of its result
+    ms = evs[0].elapsed_time(evs[K])
+    per_step = sorted(evs[i].elapsed_time(evs[i + 1]) for i in range(K))
+
+    # ---- end to end, pre-collated: public train_step (pinned H2D of each step's inputs) + D2H of its result
     result_host = torch.zeros(K, 16, dtype=torch.float32).pin_memory()
     h2d = 0
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(K):
-        b = batches[(W + i) % n_batches]
+        b = batches[(warm + i) % n_batches]
         tr.train_step(b)
         result_host[i].copy_(tr.hp.buf, non_blocking=True)
         h2d += tr.h2d_bytes(b)
     e1.record()
     barrier()
-    e2e_ms = e0.elapsed_time(e1)
+    pre_ms = e0.elapsed_time(e1)
+
+    # ---- end to end through the loader, as `fit` runs: sampling, collation and pinning of every batch happen
+    # (on the loader's thread) inside the timed region, then the same train_step + D2H
+    loader = PrefetchLoader(GlobalBatchSampler(n_batches * B, B, True, 0), coll, pin=True)
+    h2d_l = 0
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    done, epoch = 0, 0
+    while done < K:
+        for b in loader.epoch(epoch):
+            if b.batch_size != B:
+                continue
+            tr.train_step(b)
+            result_host[done].copy_(tr.hp.buf, non_blocking=True)
+            h2d_l += tr.h2d_bytes(b)
+            done += 1
+            if done == K:
+                break
+        epoch += 1
+    f1.record()
+    barrier()
+    e2e_ms = f0.elapsed_time(f1)
     clocks = sampler.stop() if rank == 0 else None
     cu.check_status()
-    t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=ctx.device)
+    assert tr.n_captures == captures0, "a CUDA-graph capture landed inside a timed region"
+    t = torch.tensor([ms, pre_ms, e2e_ms, per_step[0], per_step[K // 2], per_step[-1]], dtype=torch.float64,
+                     device=ctx.device)
     if G > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = float(t[0]), float(t[1])
+    ms, pre_ms, e2e_ms, s_min, s_med, s_max = (float(x) for x in t)
     assert torch.isfinite(result_host).all()
+    if tr.watchdog is not None:
+        tr.watchdog.stop()
     value = B * K / (ms / 1e3)
     out = {"metric": "train samples/sec (device-timed, max over ranks)", "value": round(value, 2), "unit": "samples/s",
-           "n_gpus": G, "steps": K, "warmup": W, "ms_per_step": round(ms / K, 4), "higher_is_better": True,
-           "scaling": "strong",
-           "vs_baseline": (round(value / REFERENCE_MEASURED[(args.config, G)], 3)
-                           if (args.config, G) in REFERENCE_MEASURED else None),
+           "n_gpus": G, "steps": K, "warmup": W, "warmup_run": warm, "ms_per_step": round(ms / K, 4),
+           "ms_per_step_min": round(s_min, 4), "ms_per_step_median": round(s_med, 4), "ms_per_step_max": round(s_max, 4),
+           "higher_is_better": True, "scaling": "strong",
+           "vs_baseline": None,      # the reference publishes epoch times on V100s, no samples/s for this config
            "dtype": "bf16 encoder, fp16 classifier W+momentum",
            "data": "synthetic seeded (Zipf labels, Poisson positives), random-init weights", "impl": "ours",
            "config": {"model": f"DistilBERT-style 6x768 encoder + label-sharded XFC, L={c['labels']}",
-                      "global_batch": B, "seq_len": c["seq"], "labels": c["labels"],
+                      "name": args.config, "global_batch": B, "seq_len": c["seq"], "labels": c["labels"],
                       "parallelism": f"dp{G} encoder + label-sharded classifier x{G}",
-                      "flags": "--fp16xfc --noloss --dropout 0.85 --lr1 0.05 --lr2 1e-5 --wd1 1e-4, CLS pooling",
+                      "flags": "--fp16xfc --noloss --dropout 0.85 --lr1 0.05 --lr2 1e-5 --wd1 1e-4"
+                               + (f" --accum {args.accum}" if args.accum > 1 else ""),
+                      "arm": "own flat encoder engine, CLS pooling, bf16",
                       "l2": "per-step working set (W, momentum, encoder params/moments/activations) exceeds the 126 MB L2",
                       "cuda_graph": tr.graph_active(), "fused_comm": comm is not None,
+                      "nvls": bool(comm is not None and comm.use_nvls), "watchdog": tr.watchdog is not None,
+                      "own_gemm": bool(getattr(tr.encoder, "own_gemm", False)),
                       "persistent_logits": bool(args.persistent_logits)},
            "clocks": clocks,
            "e2e": {"value": round(B * K / (e2e_ms / 1e3), 2), "unit": "samples/s", "ms_per_step": round(e2e_ms / K, 4),
-                   "h2d_bytes_per_step": h2d // K, "d2h_bytes_per_step": 64},
+                   "h2d_bytes_per_step": h2d_l // K, "d2h_bytes_per_step": 64,
+                   "path": "GlobalBatchSampler -> XCCollator -> pin (loader thread) -> XCTrainer.train_step -> D2H"},
+           "e2e_precollated": {"value": round(B * K / (pre_ms / 1e3), 2), "unit": "samples/s",
+                               "ms_per_step": round(pre_ms / K, 4), "h2d_bytes_per_step": h2d // K,
+                               "d2h_bytes_per_step": 64},
+           "memory_gb": round(torch.cuda.max_memory_allocated() / 1e9, 2),
            "gpu_launches": int(launches)}
     if G > 1:
         dist.barrier()
@@ -211,6 +261,9 @@ def main() -> None:
     ap.add_argument("--persistent-logits", action="store_true",
                     help="classifier logits GEMM: persistent CTAs with double-buffered TMEM accumulators")
     ap.add_argument("--custom-cuda", action="store_true", help="reference arm: route its GEMMs to its CUTLASS extension")
+    ap.add_argument("--accum", type=int, default=1, help="split accumulation factor (both arms)")
+    ap.add_argument("--nvls", action="store_true", help="gradient reduction and parameter push through NVLS multimem")
+    ap.add_argument("--no-watchdog", action="store_true", help="run multi-GPU steps without the heartbeat watchdog")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":

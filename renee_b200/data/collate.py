@@ -6,9 +6,13 @@ dl_base.py:900-978 and the seed-coordinated DataLoaders of main.py:101-122).
 
 Differences from the reference, made for the fused kernels:
 
-* positives are emitted as int32 ``(row, local_label)`` pairs **sorted by micro-batch, then by
-  local label id**, so a CTA that owns a 128-label tile finds its positives with two binary
-  searches instead of a dense target or an ``index_put_`` pass;
+* positives are emitted as int32 ``(row in the GLOBAL batch, local_label)`` pairs **sorted by local
+  label id** (ties by row), so a CTA that owns a 128-label tile finds its positives with two binary
+  searches instead of a dense target or an ``index_put_`` pass.  The layout does not depend on
+  ``--accum``: the classifier splits the step over the LABEL axis (``models/xfc.py``), every label
+  chunk sees all rows of the batch, and a chunk's positives are a contiguous range of the sorted
+  list.  (The reference splits the rows instead and rebases them per micro-batch,
+  dl_base.py:939-959; that convention does not exist here.);
 * duplicates are removed on the host (the reference's ``out[pos_x,pos_y] -= 1`` is a
   non-accumulating indexed write, dl_base.py:594);
 * the sampler is a pure function of ``(seed, epoch)``, so ranks agree by construction rather than
@@ -16,7 +20,7 @@ Differences from the reference, made for the fused kernels:
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 import numpy as np
 import scipy.sparse as sp
@@ -31,10 +35,8 @@ class XCBatch:
     numy: int                           # padded label count (Lp)
     input_ids: torch.Tensor             # [b_local, S] int32
     attention_mask: torch.Tensor        # [b_local, S] int32
-    pos_rows: torch.Tensor | None = None      # [nnz] int32, row inside its micro-batch
-    pos_labels: torch.Tensor | None = None    # [nnz] int32, label id inside this rank's shard
-    micro_offsets: torch.Tensor | None = None  # [n_micro+1] int32 prefix offsets into pos_*
-    micro_rows: list = field(default_factory=list)  # [(row_start, row_end)] per micro-batch
+    pos_rows: torch.Tensor | None = None      # [nnz] int32, row inside the global batch
+    pos_labels: torch.Tensor | None = None    # [nnz] int32, label id inside this rank's shard (ascending)
     row_ids: np.ndarray | None = None   # global dataset rows (for evaluation bookkeeping)
     dense_targets: torch.Tensor | None = None  # [B, Ls] float (default/autograd path only)
 
@@ -44,27 +46,18 @@ class XCBatch:
         return torch.stack([self.pos_rows.long(), self.pos_labels.long()])
 
     def pin(self) -> "XCBatch":
-        for name in ("input_ids", "attention_mask", "pos_rows", "pos_labels", "micro_offsets"):
+        for name in ("input_ids", "attention_mask", "pos_rows", "pos_labels"):
             t = getattr(self, name)
             if isinstance(t, torch.Tensor) and not t.is_pinned() and torch.cuda.is_available():
                 setattr(self, name, t.pin_memory())
         return self
 
 
-def micro_batch_rows(batch_size: int, xfc_batch: int) -> list[tuple[int, int]]:
-    """Row ranges of the classifier micro-batches: chunks of ``xfc_batch`` rows, the last one
-    shorter for a partial final batch (reference dl_base.py:318-340)."""
-    out = []
-    s = 0
-    while s < batch_size:
-        e = min(s + xfc_batch, batch_size)
-        out.append((s, e))
-        s = e
-    return out
-
-
 class XCCollator:
-    def __init__(self, sharding: LabelSharding, dataset, rank: int, accum: int, xfc_batch: int,
+    """``accum`` and ``xfc_batch`` keep the reference collator's argument list (dl_base.py:900-912); they
+    do not change what is emitted (see the module docstring)."""
+
+    def __init__(self, sharding: LabelSharding, dataset, rank: int, accum: int = 1, xfc_batch: int = 0,
                  train: bool = True, dense_targets: bool = False):
         self.sharding = sharding
         self.dataset = dataset
@@ -102,16 +95,10 @@ class XCCollator:
         cols = coo.col.astype(np.int64)
         keep = coo.data != 0
         rows, cols = rows[keep], cols[keep]
-        micro = micro_batch_rows(bsz, self.xfc_batch if self.accum > 1 else max(bsz, 1))
-        mb = np.searchsorted(np.array([m[0] for m in micro] + [bsz]), rows, side="right") - 1
-        order = np.lexsort((rows, cols, mb))
-        rows, cols, mb = rows[order], cols[order], mb[order]
-        offsets = np.searchsorted(mb, np.arange(len(micro) + 1), side="left")
-        starts = np.array([m[0] for m in micro], dtype=np.int64)
-        batch.pos_rows = torch.from_numpy((rows - starts[mb] if len(rows) else rows).astype(np.int32))
+        order = np.lexsort((rows, cols))
+        rows, cols = rows[order], cols[order]
+        batch.pos_rows = torch.from_numpy(rows.astype(np.int32))
         batch.pos_labels = torch.from_numpy(cols.astype(np.int32))
-        batch.micro_offsets = torch.from_numpy(offsets.astype(np.int32))
-        batch.micro_rows = micro
         if self.dense_targets:
             y = torch.zeros(bsz, self.sharding.labels_per_rank)
             y[torch.from_numpy(coo.row[keep].astype(np.int64)), torch.from_numpy(coo.col[keep].astype(np.int64))] = 1.0

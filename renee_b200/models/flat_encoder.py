@@ -8,10 +8,14 @@ so this engine is built for CUDA-graph capture instead:
   no-decay group), with a low-precision compute copy, a flat gradient buffer and flat Adam moments —
   the gradient all-reduce and the fused AdamW each touch one contiguous range;
 * the q/k/v projections are adjacent in the buffer, so one GEMM computes all three;
-* forward and backward are explicit sequences of GEMMs (library calls — framework layer) and fused
-  kernels from :mod:`renee_b200.ops` (bias+dropout+residual+LayerNorm, bias+GELU, attention,
-  embedding gather+LayerNorm, pooling), writing into pre-allocated activations; no autograd graph,
-  no allocator calls inside the step;
+* forward and backward are explicit sequences of GEMMs and fused kernels from :mod:`renee_b200.ops`
+  (attention, LayerNorm, embedding gather+LayerNorm, pooling), writing into pre-allocated activations;
+  no autograd graph, no allocator calls inside the step.  With 16-bit activations on a GPU every
+  linear layer is an own tcgen05 GEMM (``ops/csrc/gemm.cu``) whose epilogue carries its element-wise
+  neighbours: bias + GELU (storing the pre-activation), bias + dropout + residual (producing the
+  LayerNorm input), GELU backward + bias-gradient column sums, the residual-gradient add of the
+  data-gradient GEMMs, and a split-K weight-gradient GEMM.  fp32 activations (CPU, debugging mode) use
+  library GEMMs and stand-alone element-wise ops;
 * dropout masks are recomputed from a counter-based RNG in the backward pass.
 
 State-dict keys are those of HF DistilBERT (see :mod:`renee_b200.models.encoder`).
@@ -112,6 +116,10 @@ class FlatEncoder:
         self._acts_key = None
         self._plan = None
         self.generation = 0
+        self.own_gemm = False
+        if self.device.type == "cuda" and act_dtype != torch.float32:
+            from ..ops import cuda as cu
+            self.own_gemm = cu.enc_gemm_supported(self.p16, H, Fd)
 
     # ------------------------------------------------------------------ parameter views
     def view(self, buf: torch.Tensor, name: str) -> torch.Tensor:
@@ -205,7 +213,9 @@ class FlatEncoder:
                          self.view(P, "embeddings.position_embeddings.weight"),
                          self.view(P, "embeddings.LayerNorm.weight"), self.view(P, "embeddings.LayerNorm.bias"),
                          cfg.layer_norm_eps, S, pd, rng, _S_EMB, h, A["mean0"][:T], A["rstd0"][:T])
-        for l, L in enumerate(A["layers"]):
+        if self.own_gemm:
+            h = self._forward_layers_fused(h, attention_mask, T, pd, pa, po, rng)
+        for l, L in enumerate(A["layers"] if not self.own_gemm else ()):
             pre = f"transformer.layer.{l}."
             sb = 8 * (l + 1)
             qkv = L["qkv"][:T]
@@ -242,6 +252,37 @@ class FlatEncoder:
             torch.mm(pooled, self.bottleneck_weight().t(), out=emb)   # fp32, master weights
             return emb
         return pooled
+
+    def _forward_layers_fused(self, h, attention_mask, T, pd, pa, po, rng):
+        """The transformer blocks on the own GEMMs: 4 GEMMs, 1 attention and 2 LayerNorm launches per layer."""
+        from ..ops import cuda as cu
+        cfg, A, P = self.cfg, self._acts, self.p16
+        for l, L in enumerate(A["layers"]):
+            pre = f"transformer.layer.{l}."
+            sb = 8 * (l + 1)
+            qkv = L["qkv"][:T]
+            cu.linear_fwd(h, self._qkv(P, l, "weight"), qkv)
+            ctx = L["ctx"][:T]
+            ops.attention_fwd(qkv, self._qkv(P, l, "bias"), attention_mask, cfg.n_heads, pa, rng, sb + _S_PROBS,
+                              ctx, L["att"])
+            pre1 = L["pre1"][:T]
+            cu.linear_fwd(ctx, self.view(P, pre + "attention.out_lin.weight"), pre1, "bias_dropout_resid",
+                          bias=self.view(P, pre + "attention.out_lin.bias"), resid=h, p=po, rng=rng, stream=sb + _S_ATTN)
+            h1 = L["h1"][:T]
+            cu.ln_fwd(pre1, self.view(P, pre + "sa_layer_norm.weight"), self.view(P, pre + "sa_layer_norm.bias"),
+                      cfg.layer_norm_eps, h1, L["mean1"][:T], L["rstd1"][:T])
+            a1 = L["a1"][:T]
+            cu.linear_fwd(h1, self.view(P, pre + "ffn.lin1.weight"), a1, "bias_gelu",
+                          bias=self.view(P, pre + "ffn.lin1.bias"), pre_out=L["f1"][:T])     # f1 holds x W^T + bias here
+            pre2 = L["pre2"][:T]
+            cu.linear_fwd(a1, self.view(P, pre + "ffn.lin2.weight"), pre2, "bias_dropout_resid",
+                          bias=self.view(P, pre + "ffn.lin2.bias"), resid=h1, p=pd, rng=rng, stream=sb + _S_FFN)
+            h2 = L["h2"][:T]
+            cu.ln_fwd(pre2, self.view(P, pre + "output_layer_norm.weight"), self.view(P, pre + "output_layer_norm.bias"),
+                      cfg.layer_norm_eps, h2, L["mean2"][:T], L["rstd2"][:T])
+            L["h_in"] = h
+            h = h2
+        return h
 
     # ------------------------------------------------------------------ backward
     def backward(self, d_emb: torch.Tensor, on_layer_done=None) -> None:
@@ -290,6 +331,30 @@ class FlatEncoder:
                 pd, rng, sb + _S_FFN,
                 self.view(G, pre + "output_layer_norm.weight"), self.view(G, pre + "output_layer_norm.bias"),
                 self.view(G, pre + "ffn.lin2.bias"), A["dh_b"][:T], L["f2"][:T])
+            if self.own_gemm:
+                from ..ops import cuda as cu
+                cu.linear_wgrad(d_f2, L["a1"][:T], self.view(G, pre + "ffn.lin2.weight"))
+                df1 = A["df1"][:T]
+                cu.linear_dgrad(d_f2, self.view(P, pre + "ffn.lin2.weight"), df1, "gelu_bwd", pre=L["f1"][:T],
+                                dbias=self.view(G, pre + "ffn.lin1.bias"))
+                cu.linear_wgrad(df1, L["h1"][:T], self.view(G, pre + "ffn.lin1.weight"))
+                dh1 = cu.linear_dgrad(df1, self.view(P, pre + "ffn.lin1.weight"), dh, "add", resid=d_pre2)
+                d_pre1, d_ao = ops.bias_dropout_add_ln_bwd(
+                    dh1, L["pre1"][:T], self.view(P, pre + "sa_layer_norm.weight"), L["mean1"][:T], L["rstd1"][:T],
+                    fw["po"], rng, sb + _S_ATTN,
+                    self.view(G, pre + "sa_layer_norm.weight"), self.view(G, pre + "sa_layer_norm.bias"),
+                    self.view(G, pre + "attention.out_lin.bias"), A["dh_b"][:T], L["ao"][:T])
+                cu.linear_wgrad(d_ao, L["ctx"][:T], self.view(G, pre + "attention.out_lin.weight"))
+                dctx = A["dctx"][:T]
+                cu.linear_dgrad(d_ao, self.view(P, pre + "attention.out_lin.weight"), dctx)
+                dqkv = A["dqkv"][:T]
+                ops.attention_bwd(dctx, L["qkv"][:T], self._qkv(P, l, "bias"), mask, cfg.n_heads, pa, rng,
+                                  sb + _S_PROBS, L["att"], dqkv, self._qkv(G, l, "bias"))
+                cu.linear_wgrad(dqkv, h_in, self._qkv(G, l, "weight"))
+                cu.linear_dgrad(dqkv, self._qkv(P, l, "weight"), dh, "add", resid=d_pre1)
+                if on_layer_done is not None:
+                    on_layer_done(l)
+                continue
             torch.mm(d_f2.t(), L["a1"][:T], out=self.view(G, pre + "ffn.lin2.weight"))
             da1 = A["da1"][:T]
             torch.mm(d_f2, self.view(P, pre + "ffn.lin2.weight"), out=da1)

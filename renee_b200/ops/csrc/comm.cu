@@ -20,6 +20,7 @@
 // never both, so emulated ranks can be run one after another on a single GPU in tests.  Every wait is
 // bounded: on expiry it records a status word and the kernel finishes normally.  Buffers written by
 // peers are double-buffered by step parity on the host side.
+#include <cstring>
 #include "peer.cuh"
 
 namespace rb {
@@ -403,3 +404,38 @@ RB_API int rb_adamw_shard_push(int dtype, float* p32, float* m, float* v, const 
   RB_LAUNCH_CHECK();
   return 0;
 }
+
+// ------------------------------------------------------------------------------------ peer-mapped allocations
+// Plain CUDA IPC: a cudaMalloc'd buffer is exported with cudaIpcGetMemHandle and mapped by the other ranks'
+// processes with cudaIpcOpenMemHandle.  Such a mapping is peer-to-peer only -- it never binds an NVLink
+// multicast object -- which is what the default (NVLS off) configuration wants: a rank that dies while
+// its memory is bound to a multicast object can fault the surviving ranks' GPUs.
+RB_API int rb_ipc_alloc(long long bytes, void** out) {
+  if (bytes < 1 || out == nullptr) return -3;
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, (size_t)bytes);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaMemset(p, 0, (size_t)bytes);
+  if (e != cudaSuccess) { cudaFree(p); return (int)e; }
+  *out = p;
+  return 0;
+}
+RB_API int rb_ipc_free(void* p) { return (int)cudaFree(p); }
+RB_API int rb_ipc_handle_bytes(void) { return (int)sizeof(cudaIpcMemHandle_t); }
+RB_API int rb_ipc_export(void* p, void* handle_out) {
+  cudaIpcMemHandle_t h;
+  const cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) return (int)e;
+  memcpy(handle_out, &h, sizeof(h));
+  return 0;
+}
+RB_API int rb_ipc_open(const void* handle, void** out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  void* p = nullptr;
+  const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return (int)e;
+  *out = p;
+  return 0;
+}
+RB_API int rb_ipc_close(void* p) { return (int)cudaIpcCloseMemHandle(p); }

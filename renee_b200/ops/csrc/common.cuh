@@ -128,6 +128,29 @@ __device__ __forceinline__ float normal_cdf(float z, float& e) {
   return z < 0.f ? half : 1.f - half;
 }
 
+// Exact (erf) GELU and its derivative: gelu(z) = z Phi(z), gelu'(z) = Phi(z) + z phi(z)
+__device__ __forceinline__ float gelu_f(float z) {
+  float e;
+  return z * normal_cdf(z, e);
+}
+__device__ __forceinline__ float gelu_grad_f(float z) {
+  float e;
+  const float cdf = normal_cdf(z, e);
+  return fmaf(z * 0.39894228040143268f, e, cdf);
+}
+
+// Number of SMs of the current device (queried once per process; all GPUs of a job are alike)
+inline int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1)
+      n = 1;
+  }
+  return n;
+}
+
 // Counter-based dropout RNG; must stay bit-identical to renee_b200/ops/rng.py::mix32
 __device__ __forceinline__ uint32_t mix32(uint32_t seed, uint32_t stream, uint32_t idx) {
   uint32_t x = idx * 0x9E3779B1u + seed;

@@ -389,15 +389,6 @@ __global__ void __launch_bounds__(128, 6) ln_bwd_kernel(
 }
 
 // ------------------------------------------------------------------------------------ GELU
-__device__ __forceinline__ float gelu_f(float z) {
-  float e;
-  return z * normal_cdf(z, e);
-}
-__device__ __forceinline__ float gelu_grad_f(float z) {
-  float e;
-  const float cdf = normal_cdf(z, e);
-  return fmaf(z * 0.39894228040143268f, e, cdf);
-}
 
 // grid = (ceil(F/8/128), row_chunks): a thread owns 8 columns (its bias stays in registers) and walks rows
 template <typename T>
@@ -605,7 +596,7 @@ RB_API int rb_embed_ln_fwd(int dtype, const int* ids, const void* word, const vo
 
 static int ln_bwd_blocks(int rows, int S, bool embed) {
   int blocks = (rows + 3) / 4;
-  if (blocks > 148 * 5) blocks = 148 * 5;
+  if (blocks > sm_count() * 5) blocks = sm_count() * 5;
   if (embed) {  // total warps (4 per block) must be a multiple of S: round blocks to a multiple of S
     blocks = (blocks / S) * S;
     if (blocks == 0) blocks = S;
@@ -646,7 +637,7 @@ RB_API int rb_embed_ln_bwd(int dtype, const void* dy, const int* ids, const void
 RB_API int rb_bias_gelu_fwd(int dtype, const void* x, const void* bias, void* out, int rows, int F, cudaStream_t st) {
   if (F % 8) return -3;
   const int cb = (F / 8 + 127) / 128;
-  int rc = 148 * 8 / cb;   // 8 CTAs per SM measured best (5, 10: 15 % slower)
+  int rc = sm_count() * 8 / cb;   // 8 CTAs per SM measured best (5, 10: 15 % slower)
   if (rc > (rows + 3) / 4) rc = (rows + 3) / 4;
   if (rc < 1) rc = 1;
   dim3 grid(cb, rc);
@@ -659,7 +650,7 @@ RB_API int rb_bias_gelu_bwd(int dtype, const void* da, const void* x, const void
                             unsigned* counter, void* dbias, int rows, int F, cudaStream_t st) {
   if (F % 8) return -3;
   const int cb = (F / 8 + 127) / 128;
-  int rc = 148 * 8 / cb;
+  int rc = sm_count() * 8 / cb;
   if (rc > (rows + 3) / 4) rc = (rows + 3) / 4;
   if (rc < 1) rc = 1;
   dim3 grid(cb, rc);
@@ -673,7 +664,7 @@ RB_API int rb_colsum(int dtype, const void* x, float* acc, unsigned* counter, vo
                      cudaStream_t st) {
   if (N % 8) return -3;
   const int cb = (N / 8 + 127) / 128;
-  int rc = 148 * 5 / cb;
+  int rc = sm_count() * 5 / cb;
   if (rc > (rows + 3) / 4) rc = (rows + 3) / 4;
   if (rc < 1) rc = 1;
   dim3 grid(cb, rc);
@@ -702,7 +693,7 @@ RB_API int rb_pool_bwd(int dtype, const float* de, const int* mask, void* dh, in
 RB_API int rb_dropout_cast_fwd(int out_dtype, const float* x, void* out, long long n, float p, const int* seed,
                                unsigned stream_id, cudaStream_t st) {
   int blocks = (int)((n + 255) / 256);
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > sm_count() * 8) blocks = sm_count() * 8;
   DISPATCH_T(out_dtype, (dropout_kernel<float, T><<<blocks, 256, 0, st>>>(x, (T*)out, (size_t)n, p, seed, stream_id)));
   RB_LAUNCH_CHECK();
   return 0;
@@ -726,6 +717,10 @@ NoAllocSlot g_noalloc_slots[64];
 RB_API int rb_colsum_noalloc_max_cols(void) { return kNoAllocMaxCols; }
 
 RB_API int rb_colsum_noalloc(int dtype, const void* x, void* out, int rows, int N, cudaStream_t st) {
+  if (dtype != RB_F32 && dtype != RB_BF16 && dtype != RB_F16) {
+    fprintf(stderr, "rb_colsum_noalloc: unknown dtype code %d (0 = fp32, 1 = bf16, 2 = fp16)\n", dtype);
+    return -1;     // checked before anything is queued on the stream
+  }
   if (rows < 1 || N < 8 || N % 8) {
     fprintf(stderr, "rb_colsum_noalloc: rows must be >= 1 and N a positive multiple of 8 (got rows=%d, N=%d)\n", rows, N);
     return -3;
@@ -751,7 +746,7 @@ RB_API int rb_colsum_noalloc(int dtype, const void* x, void* out, int rows, int 
   if (cudaMemsetAsync(slot.scratch, 0, sizeof(float) * rb::kCopies * (size_t)N, st) != cudaSuccess) return -13;
   if (cudaMemsetAsync(slot.counter, 0, sizeof(unsigned), st) != cudaSuccess) return -13;
   const int cb = (N / 8 + 127) / 128;
-  int rc = 148 * 5 / cb;
+  int rc = sm_count() * 5 / cb;
   if (rc > (rows + 3) / 4) rc = (rows + 3) / 4;
   if (rc < 1) rc = 1;
   dim3 grid(cb, rc);

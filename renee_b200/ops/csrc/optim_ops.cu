@@ -80,7 +80,7 @@ using namespace rb;
 
 static int flat_blocks(size_t n_vec) {
   size_t b = (n_vec + 255) / 256;
-  return (int)(b > 148 * 8 ? 148 * 8 : (b == 0 ? 1 : b));
+  return (int)(b > rb::sm_count() * 8 ? rb::sm_count() * 8 : (b == 0 ? 1 : b));
 }
 
 RB_API int rb_grad_check(int dtype, const void* g, long long n, float* hp, cudaStream_t st) {

@@ -13,8 +13,9 @@
  *   out[c] = sum over r of x[r, c]   for a row-major [rows, N] matrix, accumulated in fp32.
  *   dtype: 0 = float, 1 = bfloat16, 2 = half (x and out have the same type).
  *   N must be a multiple of 8 and at most rb_colsum_noalloc_max_cols() (8192); larger inputs are
- *   refused with return code -10 and a message on stderr.  Other non-zero codes: -3 bad shape,
- *   -11/-12/-13 CUDA runtime failure during set-up, a positive value is a cudaError_t of the launch.
+ *   refused with return code -10 and a message on stderr.  Other non-zero codes: -1 unknown dtype
+ *   code and -3 bad shape (both returned before anything is queued on the stream), -11/-12/-13 CUDA
+ *   runtime failure during set-up, a positive value is a cudaError_t of the launch.
  *
  * Things to know:
  *   - The scratch is a static device array of 8 * 8192 floats (256 KB) plus a 256-byte counter block.

@@ -734,16 +734,6 @@ static int g_xfc_persistent = 0;
 RB_API void rb_xfc_set_persistent(int on) { g_xfc_persistent = on ? 1 : 0; }
 RB_API int rb_xfc_get_persistent(void) { return g_xfc_persistent; }
 
-static int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1)
-      n = 148;
-  }
-  return n;
-}
-
 template <int MODE>
 static int launch_persistent(const CUtensorMap& a, const CUtensorMap& b, const GemmParams& p, int n_m_tiles, int n_n_tiles,
                              cudaStream_t st) {

@@ -165,6 +165,10 @@ def _acc_for(outs, width, default_counter):
     if _DEFER is not None:
         return _DEFER.slot(outs, width), None
     ws = workspace(outs[0].device if outs[0] is not None else torch.cuda.current_device())
+    if DeferredColumns.REPLICAS * len(outs) * width > ws.colacc.numel():
+        raise KernelError(f"{len(outs)} column vector(s) of width {width} exceed the shared column workspace "
+                          f"({ws.colacc.numel()} floats for {DeferredColumns.REPLICAS} replicas); reduce inside a "
+                          "deferred_columns plan instead")
     return ws.colacc, default_counter(ws)
 
 
@@ -288,6 +292,102 @@ def bias_gelu_bwd(da, x, bias, dbias, dx_out):
           _p(dbias), _I(T), _I(Fd), _stream())
 
 
+# ----------------------------------------------------------------------------- encoder GEMMs (tcgen05, fused epilogues)
+L_NT, L_NN, L_TN = 0, 1, 2
+E_STORE, E_BIAS_GELU, E_BIAS_DROPOUT_RESID, E_ADD, E_GELU_BWD, E_SPLITK = 0, 1, 2, 3, 4, 5
+
+
+class _SplitKScratch:
+    """fp32 partial-sum tiles and per-tile arrival counters of the split-K weight-gradient GEMMs.  Both are zero
+    between launches by contract of the kernel (the last CTA of a tile re-zeroes what it consumed).  Grows on
+    demand, so the shapes of a training step must have been seen once before the step is captured in a graph."""
+
+    def __init__(self):
+        self.buf = None
+        self.counters = None
+
+    def get(self, device, floats: int, tiles: int):
+        if self.buf is None or self.buf.numel() < floats:
+            self.buf = torch.zeros(floats, dtype=torch.float32, device=device)
+        if self.counters is None or self.counters.numel() < tiles:
+            self.counters = torch.zeros(max(tiles, 256), dtype=torch.int32, device=device)
+        return self.buf, self.counters
+
+
+_SK: dict = {}
+
+
+def enc_gemm_supported(t: torch.Tensor, *dims: int) -> bool:
+    """The own GEMMs serve 16-bit CUDA tensors whose feature dimensions are multiples of 64."""
+    return bool(t.is_cuda and t.dtype in (torch.bfloat16, torch.float16) and all(d % 64 == 0 for d in dims)
+                and os.environ.get("RENEE_B200_OWN_GEMM", "1") != "0")
+
+
+def _enc_gemm(layout, epi, A, B, C, M, N, K, bias=None, R=None, F=None, p=0.0, rng=None, stream=0, colacc=None,
+              col_tot=0, col_off=0, bn=0):
+    dev = C.device
+    ws = workspace(dev)
+    sk_buf, sk_cnt, splits = None, None, 1
+    if layout == L_TN:
+        bn_o, sp_o, tiles_o = _I(0), _I(0), _I(0)
+        lib().rb_enc_gemm_plan(_I(layout), _I(M), _I(N), _I(K), _I(bn), _c.byref(bn_o), _c.byref(sp_o), _c.byref(tiles_o))
+        splits = sp_o.value
+        if splits > 1:
+            key = dev.index if dev.index is not None else torch.cuda.current_device()
+            sk_buf, sk_cnt = _SK.setdefault(key, _SplitKScratch()).get(dev, tiles_o.value * 128 * bn_o.value, tiles_o.value)
+    _call("rb_enc_gemm", _I(DT[C.dtype]), _I(layout), _I(epi), _p(A), _p(B), _p(C), _I(M), _I(N), _I(K),
+          _I(A.stride(0)), _I(B.stride(0)), _I(C.stride(0)), _p(bias), _p(R), _I(R.stride(0) if R is not None else 0),
+          _p(F), _I(F.stride(0) if F is not None else 0), _F(p), _p(rng.dev if rng is not None else None), _U(stream),
+          _p(colacc), _I(col_tot), _I(col_off), _p(sk_buf), _p(sk_cnt), _I(splits), _I(bn), _p(ws.status), _stream())
+
+
+def linear_fwd(x, W, out, epi="store", bias=None, resid=None, pre_out=None, p=0.0, rng=None, stream=0, bn=0):
+    """``out = epilogue(x @ W.T)`` for ``x [T, K]``, ``W [N, K]`` (an ``nn.Linear`` weight):
+
+    * ``store``: the product;
+    * ``bias_gelu``: ``pre_out = x W^T + bias`` (kept for the backward pass), ``out = gelu(pre_out)``;
+    * ``bias_dropout_resid``: ``out = resid + dropout(x W^T + bias)`` — the input of the following LayerNorm."""
+    T, K = x.shape
+    N = W.shape[0]
+    code = {"store": E_STORE, "bias_gelu": E_BIAS_GELU, "bias_dropout_resid": E_BIAS_DROPOUT_RESID}[epi]
+    _enc_gemm(L_NT, code, x, W, out, T, N, K, bias=bias, R=resid, F=pre_out, p=p, rng=rng, stream=stream, bn=bn)
+    return out
+
+
+def linear_dgrad(dy, W, out, epi="store", resid=None, pre=None, dbias=None, bn=0):
+    """``out = epilogue(dy @ W)`` for ``dy [T, N]``, ``W [N, K]``:
+
+    * ``store``: the product;  ``add``: product ``+ resid`` (the residual branch's gradient);
+    * ``gelu_bwd``: product ``* gelu'(pre)`` with ``pre`` the stored pre-activation, and its column sums written
+      to ``dbias`` (through the active deferred-column plan, or at once when there is none)."""
+    T, N = dy.shape
+    K = W.shape[1]
+    code = {"store": E_STORE, "add": E_ADD, "gelu_bwd": E_GELU_BWD}[epi]
+    if code != E_GELU_BWD or dbias is None:
+        _enc_gemm(L_NN, code, dy, W, out, T, K, N, R=resid if code == E_ADD else pre, bn=bn)
+        return out
+    plan = _DEFER if _DEFER is not None else DeferredColumns(out.device, out.dtype)
+    acc = plan.slot([dbias], K)
+    _enc_gemm(L_NN, code, dy, W, out, T, K, N, R=pre, colacc=acc, col_tot=K, col_off=0, bn=bn)
+    if _DEFER is None:
+        plan.finalize()
+    return out
+
+
+def linear_wgrad(dy, x, dW, bn=0):
+    """``dW = dy.T @ x`` for ``dy [T, N]``, ``x [T, K]``, ``dW [N, K]`` (split over T, reduced in fp32)."""
+    T, N = dy.shape
+    K = x.shape[1]
+    _enc_gemm(L_TN, E_SPLITK, dy, x, dW, N, K, T, bn=bn)
+    return dW
+
+
+def ln_fwd(pre, gamma, beta, eps, y_out, mean, rstd):
+    T, H = pre.shape
+    _call("rb_ln_fwd", _I(DT[pre.dtype]), _p(pre), _p(gamma), _p(beta), _p(y_out), _p(mean), _p(rstd), _I(T), _I(H),
+          _F(eps), _stream())
+
+
 def colsum(x, out):
     T, N = x.shape
     acc, counter = _acc_for([out], N, lambda ws: ws.counters[2:])
@@ -374,11 +474,24 @@ def xfc_dw_sgd(Gt, ldG, X, W, M, hp_buf, mo, wd, tma_tiles=True, stochastic_roun
           _I(int(tma_tiles)), _I(1 if stochastic_round else 0), _p(ws.status), _stream())
 
 
+_SMS: dict = {}
+
+
+def sm_count(device=None) -> int:
+    """Number of SMs of ``device`` (the current one by default), queried once."""
+    idx = torch.device(device).index if device is not None and torch.device(device).index is not None \
+        else torch.cuda.current_device()
+    if idx not in _SMS:
+        _SMS[idx] = int(torch.cuda.get_device_properties(idx).multi_processor_count)
+    return _SMS[idx]
+
+
 def dx_splits(B: int, D: int, Lc: int) -> int:
-    """Split-K factor of the dX GEMM so that the grid covers the 148 SMs about once."""
+    """Split-K factor of the dX GEMM so that the grid covers the SMs about once."""
     tiles = ((B + 127) // 128) * ((D + 255) // 256)
     kb = (Lc + 63) // 64
-    return max(1, min(kb, (148 + tiles - 1) // tiles))
+    sms = sm_count()
+    return max(1, min(kb, (sms + tiles - 1) // tiles))
 
 
 def xfc_step(xfc, X, pos_rows, pos_labels, nnz, dX_out, hp, mo, wd, want_loss, wait=None, signal=None,
@@ -447,6 +560,51 @@ def xfc_topk(xfc, X, k):
 
 
 # ----------------------------------------------------------------------------- peer-memory collectives
+class _RawCudaBuffer:
+    """Device memory obtained from ``cudaMalloc`` by this library, exposed through
+    ``__cuda_array_interface__`` so that PyTorch can view it without owning it."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.ptr, self.nbytes = int(ptr), int(nbytes)
+        self.__cuda_array_interface__ = {"shape": (self.nbytes,), "typestr": "|u1", "data": (self.ptr, False),
+                                         "version": 2, "strides": None}
+
+
+def ipc_alloc(numel: int, dtype, device) -> torch.Tensor:
+    """A zero-filled tensor in its own ``cudaMalloc`` allocation (exportable with :func:`ipc_export`).  The
+    allocation lives until the process exits."""
+    esz = torch.empty((), dtype=dtype).element_size()
+    nbytes = (numel * esz + 255) // 256 * 256
+    out = _VP(0)
+    with torch.cuda.device(device):
+        rc = lib().rb_ipc_alloc(_LL(nbytes), _c.byref(out))
+    if rc != 0:
+        raise KernelError(f"rb_ipc_alloc({nbytes}) failed with CUDA error {rc}")
+    raw = torch.as_tensor(_RawCudaBuffer(out.value, nbytes), device=device)
+    return raw.view(dtype)[:numel]
+
+
+def ipc_export(t: torch.Tensor) -> bytes:
+    """CUDA IPC handle of the allocation ``t`` starts at (``t`` must come from :func:`ipc_alloc`)."""
+    n = lib().rb_ipc_handle_bytes()
+    buf = _c.create_string_buffer(n)
+    rc = lib().rb_ipc_export(_VP(t.data_ptr()), buf)
+    if rc != 0:
+        raise KernelError(f"cudaIpcGetMemHandle failed with CUDA error {rc}")
+    return bytes(buf.raw)
+
+
+def ipc_open(handle: bytes, device) -> int:
+    """Maps another process's allocation into this process (peer access enabled on demand); returns its
+    device address."""
+    out = _VP(0)
+    with torch.cuda.device(device):
+        rc = lib().rb_ipc_open(_c.c_char_p(handle), _c.byref(out))
+    if rc != 0:
+        raise KernelError(f"cudaIpcOpenMemHandle failed with CUDA error {rc}")
+    return int(out.value)
+
+
 def ptr_array(ptrs):
     """ctypes ``void*[n]`` from a list of integer device addresses (kept alive by the caller)."""
     return (_VP * len(ptrs))(*[_VP(int(x)) for x in ptrs])

@@ -22,9 +22,13 @@ AdamW                       all ranks (NVLS ``multimem.ld_reduce`` or peer loads
 
 Buffers that peers write or read (``X``, the ``dX`` partials) are double-buffered by step parity;
 flags carry the step number read from a device-resident counter, so the launch sequence is identical
-every step and can be replayed from a CUDA graph (two graphs, one per parity).  The symmetric
-allocations and their peer mappings come from ``torch.distributed._symmetric_memory``; NCCL remains
-for bootstrap, evaluation merges and scalars.  No TMA multicast is used anywhere.
+every step and can be replayed from a CUDA graph (two graphs, one per parity).  By default the
+buffers are plain ``cudaMalloc`` allocations mapped into the other ranks with CUDA IPC — peer-to-peer
+only, no NVLink multicast object is ever bound, so a rank that dies cannot fault the survivors' GPUs
+through one.  With ``use_nvls=True`` (or ``RENEE_B200_NVLS=1``; meant for benchmark runs) they come from
+``torch.distributed._symmetric_memory`` and the gradient reduction and parameter push go through the
+switch's multicast mapping (``multimem``).  NCCL remains for bootstrap, evaluation merges and scalars.
+No TMA multicast is used anywhere.
 
 Safety of the buffer reuse (rank r at step n+2 may overwrite what rank q read at step n): r can only
 reach step n+2's overwrite after finishing its own pull of step n+1, which waited for q's step-(n+1)
@@ -52,11 +56,12 @@ class PeerCollectives(TorchCollectives):
         super().__init__(ctx)
         self.shard_optimizer = shard_optimizer
         # NVLS (multimem loads/stores through the NVSwitch multicast mapping) for the gradient reduction
-        # and the parameter push when the symmetric allocation exposes a multicast address; pass
-        # use_nvls=False or set RENEE_B200_NVLS=0 to stay on plain peer loads/stores (do so in any run in
-        # which a rank may exit while the others keep going)
+        # and the parameter push is OPT-IN (use_nvls=True or RENEE_B200_NVLS=1): a crash, an OOM kill or a
+        # PeerFailure exit of one rank while its memory is bound to a multicast object can raise NVLink
+        # faults on the other ranks' GPUs, and the bounded flag waits do not cover a multimem access whose
+        # member has gone.  The default stays on plain peer loads/stores over CUDA IPC mappings.
         import os
-        self.use_nvls = (os.environ.get("RENEE_B200_NVLS", "1") != "0") if use_nvls is None else bool(use_nvls)
+        self.use_nvls = (os.environ.get("RENEE_B200_NVLS", "0") == "1") if use_nvls is None else bool(use_nvls)
         self._mc_grad = 0
         self._mc_p16 = 0
         self.p16 = None
@@ -73,6 +78,9 @@ class PeerCollectives(TorchCollectives):
 
     # ------------------------------------------------------------------ allocation
     def _symm(self, numel: int, dtype, name: str = "symmetric"):
+        """``(local tensor, [device address of the same buffer on every rank])``."""
+        if not self.use_nvls:
+            return self._ipc(numel, dtype, name)
         import torch.distributed._symmetric_memory as symm_mem
         whole = []
 
@@ -89,6 +97,26 @@ class PeerCollectives(TorchCollectives):
         mc = int(getattr(hdl, "multicast_ptr", 0) or 0) if self.use_nvls else 0
         self._last_multicast = mc + off if mc else 0
         return t, [int(p) + off for p in hdl.buffer_ptrs]
+
+    def _ipc(self, numel: int, dtype, name: str):
+        """Peer-mapped only: own ``cudaMalloc`` block, handles exchanged over the process group, every
+        peer's block opened with ``cudaIpcOpenMemHandle``.  Collective (every rank calls it in the same order)."""
+        from ..ops import cuda as cu
+        whole = []
+
+        def alloc(n, dt):
+            whole.append(cu.ipc_alloc(n, dt, self.ctx.device))
+            return whole[0]
+
+        t = guard.from_allocator(alloc, numel, dtype, name=f"{name}{len(self._handles)}")
+        off = guard.payload_offset_bytes()
+        handles = [None] * self.G
+        dist.all_gather_object(handles, cu.ipc_export(whole[0]), group=self.group)
+        ptrs = [whole[0].data_ptr() if r == self.rank else cu.ipc_open(handles[r], self.ctx.device)
+                for r in range(self.G)]
+        self._handles.append((whole[0], ptrs))
+        self._last_multicast = 0
+        return t, [p + off for p in ptrs]
 
     def setup(self, B_max: int, D: int) -> None:
         from ..ops import cuda as cu
@@ -159,11 +187,11 @@ class PeerCollectives(TorchCollectives):
         n = enc.numel
         cu.signal(self._flag_ptrs, self.G, F_ARA, self.rank, self.step)
         cu.grad_reduce_scatter(enc.g.dtype, self._grad_ptrs, n, self.G, self.rank, self.flags[F_ARA:], self.step, self.gsum,
-                               self._flag_ptrs, F_ARB, F_FOUND, self.counters[48:], 148 * 2, mc_grads=self._mc_grad)
+                               self._flag_ptrs, F_ARB, F_FOUND, self.counters[48:], cu.sm_count(self.ctx.device) * 2, mc_grads=self._mc_grad)
         cu.wait_flags(self.flags[F_ARB:], self.G, self.step, 1, 0, self.flags[F_FOUND:], hp.buf)
         cu.adamw_shard_push(enc.p16.dtype, enc.p32, enc.m, enc.v, self.gsum, self._p16_ptrs, n, enc.n_decay, self.G,
                             self.rank, hp.buf, beta1, beta2, eps, wd, 1.0 / self.G, self._flag_ptrs, F_ARC, self.step,
-                            self.counters[52:], 148 * 2, mc_p16=self._mc_p16)
+                            self.counters[52:], cu.sm_count(self.ctx.device) * 2, mc_p16=self._mc_p16)
         cu.wait_flags(self.flags[F_ARC:], self.G, self.step, 1, 0, None, None)
 
     def sync_master(self, enc) -> None:
@@ -216,6 +244,6 @@ class PeerCollectives(TorchCollectives):
         n = g.numel() // 8 * 8
         cu.signal(self._flag_ptrs, self.G, F_ARA, self.rank, self.step)
         cu.grad_allreduce(g.dtype, self._grad_ptrs, 0, n, self.G, self.rank, self.flags[F_ARA:], self._flag_ptrs, F_ARB,
-                          F_FOUND, self.step, 1, 0, self.counters[48:], 148 * 2)
+                          F_FOUND, self.step, 1, 0, self.counters[48:], cu.sm_count(self.ctx.device) * 2)
         cu.wait_flags(self.flags[F_ARB:], self.G, self.step, 1, 0, self.flags[F_FOUND:], hp.buf)
         return 1.0 / self.G

@@ -6,8 +6,12 @@ peer must be noticed on the HOST, before kernels that would wait for it are laun
 
 * every rank runs a :class:`Heartbeat` thread that stamps ``hb/<rank>`` in a ``torch.distributed``
   store (TCPStore / FileStore / HashStore) every ``interval`` seconds;
-* ``check()`` — called by the trainer before each step's launches — raises :class:`PeerFailure` if a
-  peer's stamp is older than ``timeout`` or if any rank has posted a failure with ``post_failure``;
+* the same thread reads the peers' stamps and the failure key once per interval (``poll``) and keeps the
+  verdict in a local field;
+* ``check()`` — called by the trainer before each step's launches — raises :class:`PeerFailure` if that
+  verdict says a peer's stamp is older than ``timeout`` or a rank has posted a failure with
+  ``post_failure``.  With the thread running it touches no store: a step of a millisecond must not pay
+  a dozen TCP round trips.  Without a thread (manual driving in tests) it polls the store itself;
 * the device-side waits are bounded anyway (they return a status word instead of hanging), so a
   failure that slips between two checks costs one timed-out step, not a hung GPU.
 
@@ -37,6 +41,7 @@ class Heartbeat:
         self._stop = threading.Event()
         self._thread = None
         self._start_time = clock()
+        self._failure: PeerFailure | None = None     # written by the thread, read by check()
 
     def _key(self, r: int) -> str:
         return f"hb/{r}"
@@ -51,8 +56,11 @@ class Heartbeat:
             while not self._stop.wait(self.interval):
                 try:
                     self.beat()
+                    f = self.poll()
                 except Exception:
                     return
+                if f is not None:
+                    self._failure = f
 
         self._thread = threading.Thread(target=loop, daemon=True, name=f"heartbeat-{self.rank}")
         self._thread.start()
@@ -86,11 +94,20 @@ class Heartbeat:
                 bad.append(r)
         return bad
 
-    def check(self) -> None:
+    def poll(self) -> PeerFailure | None:
+        """Reads the failure key and every peer's stamp from the store (blocking round trips)."""
         f = self._get("failure")
         if f is not None:
             r, _, msg = f.partition(":")
-            raise PeerFailure(f"rank {r} reported a failure: {msg}", [int(r)])
+            return PeerFailure(f"rank {r} reported a failure: {msg}", [int(r)])
         bad = self.stale_peers()
         if bad:
-            raise PeerFailure(f"no heartbeat from rank(s) {bad} for more than {self.timeout:.1f} s", bad)
+            return PeerFailure(f"no heartbeat from rank(s) {bad} for more than {self.timeout:.1f} s", bad)
+        return None
+
+    def check(self) -> None:
+        """Step-path check: a field read while the heartbeat thread runs, a direct ``poll`` otherwise."""
+        running = self._thread is not None and self._thread.is_alive() and not self._stop.is_set()
+        f = self._failure if running else (self._failure or self.poll())
+        if f is not None:
+            raise f

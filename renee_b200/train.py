@@ -151,6 +151,8 @@ class XCTrainer:
         self._graph_generation = -1
         self._pending_loss = None
         self._side_stream = None
+        self._aborted = False
+        self.n_captures = 0         # CUDA-graph captures so far (a benchmark checks that none lands in its timed region)
         self.watchdog = None        # optional parallel.watchdog.Heartbeat, consulted before each step's launches
         if cfg.default_impl:
             self._init_default()
@@ -272,9 +274,21 @@ class XCTrainer:
             self._device_step(b, B, nnz, False)
         self._graph_launches = cu.launch_count() - n0
         self._graphs[key] = graph
+        self.n_captures += 1
 
     def graph_active(self) -> bool:
         return bool(self._graphs)
+
+    def graphs_ready(self, b: int, B: int) -> bool:
+        """True once every graph that steps of this shape will replay exists: one per buffer parity with the
+        peer-memory backend, one otherwise.  Until then a step may still capture (synchronise + instantiate)."""
+        if not (self.cfg.cuda_graph and self.device.type == "cuda"
+                and getattr(self.comm, "graph_safe", self.G == 1)):
+            return True                                     # nothing will ever be captured
+        if self._graph_generation != self.encoder.generation:
+            return False
+        parities = (0, 1) if hasattr(self.comm, "host_step") else (self.comm.parity,)
+        return all((b, B, q) in self._graphs for q in parities)
 
     def launches_per_step(self) -> int:
         return int(getattr(self, "_graph_launches", 0))
@@ -282,8 +296,14 @@ class XCTrainer:
     def train_step(self, batch: XCBatch) -> torch.Tensor | None:
         """Runs one optimized step; returns the sampled loss tensor (device, un-normalised) on
         sampling steps, else ``None``.  No host synchronisation happens here."""
+        if self._aborted:
+            raise RuntimeError("this trainer was aborted after a peer or kernel failure; restart from a checkpoint")
         if self.watchdog is not None:
-            self.watchdog.check()       # a dead or failed peer is noticed on the host, before any kernel waits for it
+            try:
+                self.watchdog.check()   # a dead or failed peer is noticed on the host, before any kernel waits for it
+            except Exception:
+                self.abort()
+                raise
         if self.cfg.default_impl:
             return self.default_step(batch)
         self.stage_batch(batch)
@@ -460,6 +480,16 @@ class XCTrainer:
                 save_checkpoint(self, cfg.checkpoint_resume, mean_loss)
         self.epoch = cfg.epochs
 
+    def abort(self) -> None:
+        """After a peer or kernel failure: launch nothing more and wait for what is in flight (every device-side
+        wait is bounded, so this returns) before the process tears its memory mappings down."""
+        self._aborted = True
+        if self.device.type == "cuda":
+            try:
+                torch.cuda.synchronize()
+            except RuntimeError:
+                pass
+
     def check_device_status(self) -> None:
         """Raise (and tell the other ranks) if a bounded device-side wait has expired since the last check, or
         (guard mode) if something wrote outside a framework buffer."""
@@ -478,6 +508,7 @@ class XCTrainer:
         except cu.KernelError as exc:
             if self.watchdog is not None:
                 self.watchdog.post_failure(str(exc))
+            self.abort()
             raise
 
     def save(self, out_dir: str | None = None) -> str:

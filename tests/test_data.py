@@ -4,7 +4,7 @@ import scipy.sparse as sp
 import torch
 
 from renee_b200.data import xcrepo
-from renee_b200.data.collate import GlobalBatchSampler, XCCollator, micro_batch_rows
+from renee_b200.data.collate import GlobalBatchSampler, XCCollator
 from renee_b200.data.synthetic import SyntheticSpec, SyntheticXC, ZipfSampler
 from renee_b200.utils.sharding import batch_row_range, shard_labels
 
@@ -81,20 +81,17 @@ def test_collator_shards_positives_sorted_by_label():
     assert (seen.tocsr()[:, :1000] != lab[rows]).nnz == 0
 
 
-def test_collator_micro_batches_rebase_rows():
+def test_collator_layout_does_not_depend_on_accum():
+    """Global rows sorted by label for every ``accum``: the classifier splits the label axis, not the rows."""
     spec = SyntheticSpec(num_labels=500, seq_len=8, len_lo=2, len_hi=8, poisson_lam=2.0, seed=2)
     ids, mask, lab = SyntheticXC(spec).rows(np.arange(32))
     ds = xcrepo.InMemoryDataset(ids, mask, lab)
     sh = shard_labels(500, 1)
+    a = XCCollator(sh, ds, 0, accum=1, xfc_batch=30)(np.arange(30))
     b = XCCollator(sh, ds, 0, accum=4, xfc_batch=8)(np.arange(30))
-    assert b.micro_rows == micro_batch_rows(30, 8) == [(0, 8), (8, 16), (16, 24), (24, 30)]
-    off = b.micro_offsets.numpy()
-    assert off[0] == 0 and off[-1] == b.pos_rows.numel()
-    for i, (s, e) in enumerate(b.micro_rows):
-        r = b.pos_rows.numpy()[off[i]: off[i + 1]]
-        l = b.pos_labels.numpy()[off[i]: off[i + 1]]
-        assert (r >= 0).all() and (r < e - s).all() and (np.diff(l) >= 0).all()
-        assert len(r) == lab[s:e].nnz
+    assert (a.pos_rows == b.pos_rows).all() and (a.pos_labels == b.pos_labels).all()
+    assert (np.diff(b.pos_labels.numpy()) >= 0).all() and b.pos_rows.max() >= 8
+    assert b.pos_rows.numel() == lab[:30].nnz
 
 
 def test_sampler_same_on_every_rank_and_keeps_partial_batch():

@@ -117,3 +117,40 @@ def test_heartbeat_thread_runs_and_stops():
     with pytest.raises(PeerFailure):
         a.check()
     a.stop()
+
+
+def test_check_reads_no_store_while_the_thread_runs():
+    """A step of a millisecond cannot afford store round trips: with the thread alive, ``check`` is a field read."""
+    class Counting:
+        def __init__(self):
+            self.inner, self.calls = dist.HashStore(), 0
+
+        def set(self, k, v):
+            self.inner.set(k, v)
+
+        def check(self, keys):
+            self.calls += 1
+            return self.inner.check(keys)
+
+        def get(self, k):
+            self.calls += 1
+            return self.inner.get(k)
+
+    store = Counting()
+    a = Heartbeat(store, 0, 2, interval=0.05, timeout=0.3).start()
+    b = Heartbeat(store, 1, 2, interval=0.05, timeout=0.3).start()
+    time.sleep(0.12)
+    main_thread_calls = []
+    orig_check, orig_get = store.check, store.get
+    me = threading.get_ident()
+    store.check = lambda keys: (main_thread_calls.append(1) if threading.get_ident() == me else None, orig_check(keys))[1]
+    store.get = lambda k: (main_thread_calls.append(1) if threading.get_ident() == me else None, orig_get(k))[1]
+    for _ in range(1000):
+        a.check()
+    assert not main_thread_calls
+    b.stop()
+    time.sleep(0.6)                             # the thread of rank 0 notices within timeout + interval
+    with pytest.raises(PeerFailure):
+        a.check()
+    assert not main_thread_calls
+    a.stop()

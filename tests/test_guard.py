@@ -147,6 +147,8 @@ def test_symmetric_allocation_addresses_follow_the_payload(monkeypatch):
         assert pc._last_multicast == (1 << 40) + guard.BAND_BYTES
         t.fill_(1.0)
         guard.assert_clean()
+        # without NVLS the buffers come from plain CUDA IPC mappings instead (no multicast object at all)
         pc.use_nvls = False
-        pc._symm(10, torch.int32)
-        assert pc._last_multicast == 0
+        called = []
+        monkeypatch.setattr(fused.PeerCollectives, "_ipc", lambda self, n, dt, name: called.append((n, dt)) or ("t", [0]))
+        assert pc._symm(10, torch.int32) == ("t", [0]) and called == [(10, torch.int32)]

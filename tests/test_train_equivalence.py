@@ -92,3 +92,37 @@ def test_loss_scale_state_machine_skips_and_backs_off():
     assert hp.get_scale() == 2.0 ** 12 and float(hp.buf[HP.ADAM_STEP]) == 3
     off = HyperParams("cpu", enabled=False)
     assert off.get_scale() == 1.0
+
+
+def _fit_with_accum(accum, tmp_path, device="cpu", n=40, **kw):
+    """Trainer + loaders built the way ``cli.start`` builds them (global batch 16, 40 rows: the last batch of an
+    epoch is partial), one epoch."""
+    enc = EncoderConfig(vocab_size=30522, max_position_embeddings=32, dim=128, n_layers=2, n_heads=2,
+                        hidden_dim=512, dropout=0.0, attention_dropout=0.0)
+    base = dict(batch_size=16, epochs=1, seed=0, dropout=0.0, lr1=0.05, lr2=1e-3, warmup=2, wd1=1e-3, wd2=0.01,
+                maxlen=16, fp32encoder=True, accum=accum, noloss=True)
+    base.update(kw)
+    cfg = TrainConfig(**base)
+    spec = SyntheticSpec(num_labels=700, seq_len=16, len_lo=4, len_hi=16, poisson_lam=2.0, seed=0)
+    ids, mask, lab = SyntheticXC(spec).rows(np.arange(n))
+    ds = xcrepo.InMemoryDataset(ids, mask, lab)
+    sh = shard_labels(700, 1)
+    gbsz = cfg.batch_size
+    loader = PrefetchLoader(GlobalBatchSampler(n, gbsz, True, 0),
+                            XCCollator(sh, ds, 0, accum, max(1, gbsz // accum), True, False))
+    tr = XCTrainer(cfg, enc, sh, DistContext(device=torch.device(device)), steps_per_epoch=len(loader))
+    tr.fit(loader, log=lambda *a: None)
+    return tr
+
+
+def test_accum_through_the_loader_equals_accum_one(tmp_path):
+    """``--accum`` only bounds the classifier scratch (dl_base.py:317-340): the trained weights must not depend on it."""
+    ref = _fit_with_accum(1, tmp_path)
+    sd = ref.state_dict()
+    for accum in (2, 4):
+        tr = _fit_with_accum(accum, tmp_path)
+        assert tr.xfc.chunk <= (tr.Ls + accum - 1) // accum + 127      # Gt scratch is B x Ls/accum (128-label granularity)
+        for k, v in tr.state_dict().items():
+            if "k_lin.bias" in k:
+                continue        # its true gradient is zero (softmax is shift-invariant): Adam amplifies rounding noise
+            torch.testing.assert_close(v, sd[k], rtol=1e-3, atol=1e-5, msg=lambda m: f"accum={accum} {k}: {m}")

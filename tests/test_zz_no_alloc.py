@@ -45,3 +45,7 @@ def test_noalloc_colsum_matches_regular_entry_point_twice():
     rc = fn(ctypes.c_int(0), ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(out.data_ptr()), ctypes.c_int(8),
             ctypes.c_int(max_cols + 8), stream)
     assert rc == -10
+    # an unknown dtype code is refused before anything is queued on the stream
+    rc = fn(ctypes.c_int(7), ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(out.data_ptr()), ctypes.c_int(8),
+            ctypes.c_int(64), stream)
+    assert rc == -1
