@@ -8,6 +8,13 @@ xfc_scheduler_state_dict, tf_scheduler_state_dict``.  Added: ``dropout_rng`` (th
 kernel RNG), ``count`` (steps taken) and ``world_size``/``labels_per_rank`` so that a resume under a
 different sharding is refused instead of silently mis-loading.  Unlike the reference the new file is
 written to a temporary name and renamed, so a crash never leaves a truncated checkpoint.
+
+Interchangeable with files written by the reference: ``model_dict`` (same keys and shapes) and ``scaler``.
+NOT interchangeable: the optimizer and scheduler sub-dicts.  The reference stores apex/torch optimizer
+state dicts (``state`` / ``param_groups`` keyed by parameter index); here ``xfc_optimizer_state_dict`` is
+``{"momentum_buffer": [Ls, D]}``, ``tf_optimizer_state_dict`` holds the flat ``exp_avg`` / ``exp_avg_sq``
+buffers of the encoder engine and the schedulers store ``base_lr`` and their step.  A reference checkpoint
+can therefore initialise the weights of a run here, not resume its optimizer trajectory.
 """
 from __future__ import annotations
 

@@ -64,7 +64,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--synthetic-len-lo", type=int, default=6)
     p.add_argument("--no-cuda-graph", dest="cuda_graph", action="store_false", default=True)
     p.add_argument("--no-fused-comm", dest="fused_comm", action="store_false", default=True)
-    p.add_argument("--stochastic-round", action="store_true", default=False)
+    p.add_argument("--no-stochastic-round", dest="stochastic_round", action="store_false", default=True,
+                   help="with --fp16xfc: round the updated fp16 classifier weights to nearest instead of stochastically")
     p.add_argument("--cpu", action="store_true", default=False, help="force CPU (gloo) execution")
     p.add_argument("--heartbeat-timeout", type=float, default=60.0,
                    help="seconds without a peer heartbeat before a step is refused (0 disables the watchdog)")

@@ -11,48 +11,68 @@
 //              BIAS_GELU            F = acc + bias ;  C = gelu(F)                    (FFN-1 forward; F kept for backward)
 //              BIAS_DROPOUT_RESID   C = R + dropout(acc + bias)                      (out-proj / FFN-2 forward: the LayerNorm input)
 //              ADD                  C = acc + R                                      (dgrad joined with the residual gradient)
-//              GELU_BWD             C = acc * gelu'(F) ;  column sums of C -> bias gradient accumulators
+//              GELU_BWD             C = acc * gelu'(R) ;  column sums of C -> bias gradient accumulators
 //              SPLITK               fp32 partials reduced in L2, the last CTA of a tile converts and stores
 //
-// Structure: one CTA per SM walks the work items (tile x K-split); 320 threads = warp 0 TMA producer, warp 1
-// TMEM owner + MMA issuer, warps 2..9 epilogue (two warps per TMEM lane quarter, half of the tile's columns
-// each).  128 x BN x 64 tiles (BN = 64 / 128 / 256) in a 4-stage shared-memory ring that keeps streaming
-// across item boundaries; TMEM holds two accumulators so the epilogue of item i runs under the main loop of
-// item i + 1.  Every wait is bounded (tc.cuh): a protocol error ends with a status word, never with a hang.
-// No TMA multicast is used: every CTA loads its own operand tiles.
+// Structure.  Persistent CTAs walk the work items (tile x K-split).  320 threads: warp 0 TMA producer, warp 1
+// TMEM owner + MMA issuer, warps 2..9 epilogue (two groups of four warps, one TMEM lane quarter per warp, half
+// of the tile's columns per group).  The shared-memory ring keeps streaming across item boundaries and TMEM
+// holds two accumulators, so the epilogue of item i runs under the main loop of item i + 1.
+//
+// Two tile shapes.  NCTA = 1: a CTA owns a 128 x BN tile.  NCTA = 2 (`cta_group::2`): the two CTAs of a cluster
+// of two own a 256 x BN tile; each loads its 128 rows of A and HALF of the B columns, the leader CTA issues
+// MMAs that read both CTAs' shared memory and write 128 accumulator rows into each CTA's TMEM.  The kernel is
+// bound by the rate at which an SM can fetch operand rows, and the pair fetches 128 + BN/2 rows per k block and
+// CTA instead of 128 + BN for the same MMA work.  Loads are plain TMA tile loads (no multicast); a pair's loads
+// count their bytes on the leader's barrier and one `tcgen05.commit` arrives on both CTAs' barriers.
+//
+// Epilogue.  Output tiles are staged in 128-byte-swizzled shared-memory panels ([128 rows x 64 columns] of 16-bit
+// elements) and written with TMA stores, which clip at the matrix edge; tile-shaped inputs (residual, stored
+// pre-activation) are fetched into the same panels by TMA while the tile's main loop still runs and are updated
+// in place.  Every global access of the epilogue is therefore a full-line bulk copy.
+//
+// Every wait is bounded (tc.cuh): a protocol error ends with a status word, never with a hang.
 #include <type_traits>
 #include "tc.cuh"
 
 namespace rb {
 namespace eg {
 
-constexpr int BM = 128;
+constexpr int BM = 128;                         // accumulator rows per CTA
 constexpr int BK = 64;
-constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2;            // 16 KB
-constexpr int B_BYTES_MAX = 256 * BK * 2;       // 32 KB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES_MAX;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int PANEL_BYTES = BM * 64 * 2;        // one staging panel: 128 rows x 64 x 16 bit
+constexpr int N_PANELS = 4;                     // two per epilogue group
 constexpr int THREADS = 320;
 constexpr int ACC_BUFS = 2;
 constexpr int ACC_STRIDE = 256;                 // TMEM columns between the two accumulators
 constexpr int TMEM_COLS = ACC_BUFS * ACC_STRIDE;
+constexpr int kPrefetch = 8;                    // k blocks between the L2 prefetch of a tile and its load
+
+// Shared memory: the operand ring plus, for epilogues that stage tiles, four panels.  The main loop is bound by
+// load latency over the bytes in flight, so the split-K epilogue (no panels) gets the deeper ring.
+template <int NCTA, bool STAGED> struct Cfg {
+  static constexpr int kBMax = (NCTA == 1 ? 256 : 128) * BK * 2;        // B bytes per stage and CTA, at most
+  static constexpr int kStage = A_BYTES + kBMax;                        // 48 KB / 32 KB
+  static constexpr int kStages = NCTA == 1 ? (STAGED ? 3 : 4) : (STAGED ? 4 : 6);
+  static constexpr int kPanels = STAGED ? N_PANELS : 0;
+  static constexpr int kSmem = kStages * kStage + kPanels * PANEL_BYTES + 1024 + 512;
+};
 
 enum Layout : int { L_NT = 0, L_NN = 1, L_TN = 2 };
 enum Epi : int { E_STORE = 0, E_BIAS_GELU = 1, E_BIAS_DROPOUT_RESID = 2, E_ADD = 3, E_GELU_BWD = 4, E_SPLITK = 5 };
 
 struct Params {
   int M, N;                      // output rows / columns
-  int BN;                        // N tile: 64, 128 or 256
-  int n_m_tiles, n_n_tiles;
+  int BN;                        // N tile: 64, 128 or 256 (NCTA = 2: 128 or 256)
+  int n_m_tiles, n_n_tiles;      // tiles of (128 NCTA) x BN
   int splits, kb_total, kb_per_split;
-  void* C; int ldc;
+  void* C; int ldc;              // direct stores of the split-K fix-up only
   const void* bias;              // [N]                             BIAS_GELU, BIAS_DROPOUT_RESID
-  const void* R; int ldr;        // residual (BIAS_DROPOUT_RESID, ADD) or stored pre-activation F (GELU_BWD)
-  void* F; int ldf;              // pre-activation output           BIAS_GELU
   float p; const int* seed; uint32_t stream;        // dropout      BIAS_DROPOUT_RESID
   float* colacc; int col_tot; int col_off;          // GELU_BWD: replicas of [col_tot] floats, this vector at col_off
-  float* sk_scratch; unsigned* sk_counters;         // SPLITK: [tiles][BM*BN] fp32 (zero between launches), [tiles]
+  float* sk_scratch; unsigned* sk_counters;         // SPLITK: [tiles][128 NCTA x BN] fp32 (zero between launches), [tiles]
+  int prefetch;                  // request operand tiles into L2 kPrefetch k blocks ahead of their load
   int* status;
 };
 
@@ -65,8 +85,7 @@ template <typename T> __device__ __forceinline__ uint4 pack8(const float* v) {
   for (int i = 0; i < 8; ++i) e[i] = from_f<T>(v[i]);
   return raw;
 }
-template <typename T> __device__ __forceinline__ void unpack8_ldg(const T* p, float* out) {
-  const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p));
+template <typename T> __device__ __forceinline__ void unpack8(const uint4& raw, float* out) {
   const T* e = reinterpret_cast<const T*>(&raw);
 #pragma unroll
   for (int i = 0; i < 8; ++i) out[i] = to_f(e[i]);
@@ -87,134 +106,62 @@ __device__ __forceinline__ float warp_colsum32(float (&v)[32], int lane) {
   return v[0];
 }
 
-// One 32-column fragment of one output row: v[j] is the accumulator of (row, col0 + j).
-template <typename T, int EPI>
-__device__ __forceinline__ void epilogue_fragment(const Params& p, float (&v)[32], int row, bool row_ok, int col0,
-                                                  int lane, uint32_t seed, float inv_keep, int tile, int r, int c_in_tile) {
-  T* C = reinterpret_cast<T*>(p.C);
-  if (EPI == E_STORE || (EPI == E_SPLITK && p.splits == 1)) {
-    if (row_ok) {
-#pragma unroll
-      for (int j8 = 0; j8 < 4; ++j8) {
-        const int c = col0 + 8 * j8;
-        if (c < p.N) *reinterpret_cast<uint4*>(C + (size_t)row * p.ldc + c) = pack8<T>(v + 8 * j8);
-      }
-    }
-  } else if (EPI == E_SPLITK) {
-    if (row_ok) {
-      float* s = p.sk_scratch + (size_t)tile * (BM * p.BN) + (size_t)r * p.BN + c_in_tile;
-#pragma unroll
-      for (int j4 = 0; j4 < 8; ++j4)
-        if (col0 + 4 * j4 < p.N) red_add_f32x4(s + 4 * j4, v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]);
-    }
-  } else if (EPI == E_BIAS_GELU) {
-    if (row_ok) {
-      T* F = reinterpret_cast<T*>(p.F);
-#pragma unroll
-      for (int j8 = 0; j8 < 4; ++j8) {
-        const int c = col0 + 8 * j8;
-        if (c < p.N) {
-          float b[8], f[8], a[8];
-          unpack8_ldg<T>(reinterpret_cast<const T*>(p.bias) + c, b);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            f[j] = round_through<T>(v[8 * j8 + j] + b[j]);      // backward differentiates at the stored value
-            a[j] = gelu_f(f[j]);
-          }
-          *reinterpret_cast<uint4*>(F + (size_t)row * p.ldf + c) = pack8<T>(f);
-          *reinterpret_cast<uint4*>(C + (size_t)row * p.ldc + c) = pack8<T>(a);
-        }
-      }
-    }
-  } else if (EPI == E_BIAS_DROPOUT_RESID) {
-    if (row_ok) {
-#pragma unroll
-      for (int j8 = 0; j8 < 4; ++j8) {
-        const int c = col0 + 8 * j8;
-        if (c < p.N) {
-          float b[8], res[8], o[8];
-          unpack8_ldg<T>(reinterpret_cast<const T*>(p.bias) + c, b);
-          unpack8_ldg<T>(reinterpret_cast<const T*>(p.R) + (size_t)row * p.ldr + c, res);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            float t = v[8 * j8 + j] + b[j];
-            if (p.p > 0.f) t = keep(seed, p.stream, (uint32_t)(row * p.N + c + j), p.p) ? t * inv_keep : 0.f;
-            o[j] = res[j] + t;
-          }
-          *reinterpret_cast<uint4*>(C + (size_t)row * p.ldc + c) = pack8<T>(o);
-        }
-      }
-    }
-  } else if (EPI == E_ADD) {
-    if (row_ok) {
-#pragma unroll
-      for (int j8 = 0; j8 < 4; ++j8) {
-        const int c = col0 + 8 * j8;
-        if (c < p.N) {
-          float res[8], o[8];
-          unpack8_ldg<T>(reinterpret_cast<const T*>(p.R) + (size_t)row * p.ldr + c, res);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] = v[8 * j8 + j] + res[j];
-          *reinterpret_cast<uint4*>(C + (size_t)row * p.ldc + c) = pack8<T>(o);
-        }
-      }
-    }
-  } else {  // E_GELU_BWD
-#pragma unroll
-    for (int j8 = 0; j8 < 4; ++j8) {
-      const int c = col0 + 8 * j8;
-      if (row_ok && c < p.N) {
-        float f[8];
-        unpack8_ldg<T>(reinterpret_cast<const T*>(p.R) + (size_t)row * p.ldr + c, f);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[8 * j8 + j] = round_through<T>(v[8 * j8 + j] * gelu_grad_f(f[j]));
-        *reinterpret_cast<uint4*>(C + (size_t)row * p.ldc + c) = pack8<T>(v + 8 * j8);
-      } else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[8 * j8 + j] = 0.f;
-      }
-    }
-    if (p.colacc != nullptr) {
-      const float s = warp_colsum32(v, lane);        // lane L: sum of column col0 + L over this warp's 32 rows
-      if (col0 + lane < p.N)
-        atomicAdd(p.colacc + (size_t)(blockIdx.x % kColReplicas) * p.col_tot + p.col_off + col0 + lane, s);
-    }
-  }
-}
+// Byte offset of the 16-byte chunk `chunk` (8 columns) of row r inside a 128-byte-swizzled panel.
+__device__ __forceinline__ uint32_t panel_off(int r, int chunk) { return (uint32_t)r * 128u + (uint32_t)((chunk ^ (r & 7)) << 4); }
 
-template <typename T, int LAYOUT, int EPI>
+template <typename T, int LAYOUT, int EPI, int NCTA>
 __global__ void __launch_bounds__(THREADS, 1)
-enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
+enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
+                const __grid_constant__ CUtensorMap tmF, const Params p) {
+  using C_ = Cfg<NCTA, EPI != E_SPLITK>;
   constexpr bool A_MN = (LAYOUT == L_TN);
   constexpr bool B_MN = (LAYOUT != L_NT);
-  constexpr int FMT = (sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value) ? 1 : 0;
+  constexpr int FMT = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+  constexpr int STAGES = C_::kStages;
+  constexpr int STAGE = C_::kStage;
+  constexpr bool HAS_IN = (EPI == E_BIAS_DROPOUT_RESID || EPI == E_ADD || EPI == E_GELU_BWD);   // tile-shaped input R
+  constexpr bool STAGED = (EPI != E_SPLITK);                                                     // outputs through panels
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint8_t* panels = smem + STAGES * STAGE;                       // [N_PANELS][PANEL_BYTES], 1024-byte aligned
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(panels + C_::kPanels * PANEL_BYTES);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tmem_full_bar = empty_bar + STAGES;          // [ACC_BUFS]
-  uint64_t* tmem_empty_bar = tmem_full_bar + ACC_BUFS;   // [ACC_BUFS]
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(tmem_empty_bar + ACC_BUFS);
+  uint64_t* tmem_empty_bar = tmem_full_bar + ACC_BUFS;   // [ACC_BUFS]  (used in the leader CTA)
+  uint64_t* in_bar = tmem_empty_bar + ACC_BUFS;          // [N_PANELS]  R panel has landed
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(in_bar + N_PANELS);
   volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
   volatile int* s_last = s_abort + 1;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t rank = NCTA == 2 ? tc::cluster_ctarank() : 0u;
+  const int unit = NCTA == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;          // which persistent worker
+  const int n_units = NCTA == 2 ? (int)(gridDim.x >> 1) : (int)gridDim.x;
   const int n_items = p.n_m_tiles * p.n_n_tiles * p.splits;
-  const uint32_t b_bytes = (uint32_t)p.BN * BK * 2;
+  const int b_rows = p.BN / NCTA;                                                 // B rows (N index) this CTA loads
+  const uint32_t stage_tx = (uint32_t)NCTA * (A_BYTES + (uint32_t)b_rows * BK * 2);
 
   if (threadIdx.x == 0) {
     tc::prefetch_tmap(&tmA);
     tc::prefetch_tmap(&tmB);
+    if (STAGED) tc::prefetch_tmap(&tmC);
+    if (HAS_IN) tc::prefetch_tmap(&tmR);
+    if (EPI == E_BIAS_GELU) tc::prefetch_tmap(&tmF);
     for (int s = 0; s < STAGES; ++s) { tc::mbar_init(full_bar + s, 1); tc::mbar_init(empty_bar + s, 1); }
-    for (int a = 0; a < ACC_BUFS; ++a) { tc::mbar_init(tmem_full_bar + a, 1); tc::mbar_init(tmem_empty_bar + a, 8); }
+    for (int a = 0; a < ACC_BUFS; ++a) { tc::mbar_init(tmem_full_bar + a, 1); tc::mbar_init(tmem_empty_bar + a, 8 * NCTA); }
+    for (int a = 0; a < N_PANELS; ++a) tc::mbar_init(in_bar + a, 1);
     *s_abort = 0;
     *s_last = 0;
     tc::fence_barrier_init();
   }
-  if (warp == 1) tc::tmem_alloc(tmem_ptr_smem, TMEM_COLS);
+  if (warp == 1) {
+    if (NCTA == 2) tc::tmem_alloc_pair(tmem_ptr_smem, TMEM_COLS); else tc::tmem_alloc(tmem_ptr_smem, TMEM_COLS);
+  }
   tc::tc_fence_before();
   __syncthreads();
+  if (NCTA == 2) tc::cluster_sync_all();            // the peer's barriers exist before anything arrives on them
   tc::tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
   bool aborted = false;
@@ -222,35 +169,63 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   if (warp == 0 && lane == 0) {
     // ---------------- TMA producer: one continuous stream of (item, k block) stages
     int it = 0;
-    for (int item = blockIdx.x; item < n_items && !aborted; item += gridDim.x) {
+    for (int item = unit; item < n_items && !aborted; item += n_units) {
       const int tile = item / p.splits, split = item - tile * p.splits;
-      const int m0 = (tile / p.n_n_tiles) * BM, n0 = (tile % p.n_n_tiles) * p.BN;
+      const int m0 = (tile / p.n_n_tiles) * (BM * NCTA) + (int)rank * BM;
+      const int n0 = (tile % p.n_n_tiles) * p.BN + (int)rank * b_rows;
       const int kb0 = split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
-        if (!tc::mbar_wait(empty_bar + s, ph ^ 1, aborted, p.status, tc::SITE_EMPTY, kb)) break;
-        uint8_t* sA = smem + s * STAGE_BYTES;
-        uint8_t* sB = sA + A_BYTES;
-        tc::mbar_expect_tx(full_bar + s, A_BYTES + b_bytes);
-        if (A_MN) {
-          tc::tma_load_2d(sA, &tmA, full_bar + s, m0, kb * BK);
-          tc::tma_load_2d(sA + 8192, &tmA, full_bar + s, m0 + 64, kb * BK);
-        } else {
-          tc::tma_load_2d(sA, &tmA, full_bar + s, kb * BK, m0);
+        // operand tiles that are not in L2 (weights, activations saved by the forward pass) cost a DRAM round
+        // trip each; the ring holds only 3-4 stages, so the tiles of k block kb + kPrefetch are requested into
+        // L2 now (no shared memory involved)
+        if (p.prefetch && kb + kPrefetch < kb1) {
+          const int kp = (kb + kPrefetch) * BK;
+          if (A_MN) { tc::tma_prefetch_2d(&tmA, m0, kp); tc::tma_prefetch_2d(&tmA, m0 + 64, kp); }
+          else tc::tma_prefetch_2d(&tmA, kp, m0);
+          if (B_MN) { for (int i = 0; i < b_rows / 64; ++i) tc::tma_prefetch_2d(&tmB, n0 + 64 * i, kp); }
+          else tc::tma_prefetch_2d(&tmB, kp, n0);
         }
-        if (B_MN) {
-          for (int i = 0; i < p.BN / 64; ++i) tc::tma_load_2d(sB + i * 8192, &tmB, full_bar + s, n0 + 64 * i, kb * BK);
+        if (!tc::mbar_wait(empty_bar + s, ph ^ 1, aborted, p.status, tc::SITE_EMPTY, kb)) break;
+        uint8_t* sA = smem + s * STAGE;
+        uint8_t* sB = sA + A_BYTES;
+        if (NCTA == 1) {
+          tc::mbar_expect_tx(full_bar + s, stage_tx);
+          if (A_MN) {
+            tc::tma_load_2d(sA, &tmA, full_bar + s, m0, kb * BK);
+            tc::tma_load_2d(sA + 8192, &tmA, full_bar + s, m0 + 64, kb * BK);
+          } else {
+            tc::tma_load_2d(sA, &tmA, full_bar + s, kb * BK, m0);
+          }
+          if (B_MN) {
+            for (int i = 0; i < b_rows / 64; ++i) tc::tma_load_2d(sB + i * 8192, &tmB, full_bar + s, n0 + 64 * i, kb * BK);
+          } else {
+            tc::tma_load_2d(sB, &tmB, full_bar + s, kb * BK, n0);
+          }
         } else {
-          tc::tma_load_2d(sB, &tmB, full_bar + s, kb * BK, n0);
+          // the leader's barrier counts the bytes of both CTAs' loads; only the leader announces them
+          const uint32_t lbar = tc::leader_addr(tc::smem_u32(full_bar + s));
+          if (rank == 0) tc::mbar_expect_tx(full_bar + s, stage_tx);
+          if (A_MN) {
+            tc::tma_load_2d_pair(sA, &tmA, lbar, m0, kb * BK);
+            tc::tma_load_2d_pair(sA + 8192, &tmA, lbar, m0 + 64, kb * BK);
+          } else {
+            tc::tma_load_2d_pair(sA, &tmA, lbar, kb * BK, m0);
+          }
+          if (B_MN) {
+            for (int i = 0; i < b_rows / 64; ++i) tc::tma_load_2d_pair(sB + i * 8192, &tmB, lbar, n0 + 64 * i, kb * BK);
+          } else {
+            tc::tma_load_2d_pair(sB, &tmB, lbar, kb * BK, n0);
+          }
         }
       }
     }
-  } else if (warp == 1 && lane == 0) {
-    // ---------------- MMA issuer: accumulator (t_local & 1), reused every second item once the epilogue drained it
-    const uint32_t idesc = tc::make_idesc(FMT, A_MN ? 1 : 0, B_MN ? 1 : 0, BM, p.BN);
+  } else if (warp == 1 && lane == 0 && rank == 0) {
+    // ---------------- MMA issuer (leader CTA): accumulator (t_local & 1), reused once the epilogue(s) drained it
+    const uint32_t idesc = tc::make_idesc(FMT, A_MN ? 1 : 0, B_MN ? 1 : 0, BM * NCTA, p.BN);
     int it = 0, t_local = 0;
-    for (int item = blockIdx.x; item < n_items && !aborted; item += gridDim.x, ++t_local) {
+    for (int item = unit; item < n_items && !aborted; item += n_units, ++t_local) {
       const int tile = item / p.splits, split = item - tile * p.splits;
       const int kb0 = split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
       const int buf = t_local & 1;
@@ -263,90 +238,242 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const uint32_t ph = (it / STAGES) & 1;
         if (!tc::mbar_wait(full_bar + s, ph, aborted, p.status, tc::SITE_FULL, kb)) break;
         tc::tc_fence_after();
-        const uint32_t sA = tc::smem_u32(smem + s * STAGE_BYTES);
+        const uint32_t sA = tc::smem_u32(smem + s * STAGE);
         const uint32_t sB = sA + A_BYTES;
 #pragma unroll
         for (int k = 0; k < BK / 16; ++k) {
           const uint64_t ad = A_MN ? tc::make_smem_desc(sA + k * 2048, 8192, 1024) : tc::make_smem_desc(sA + k * 32, 16, 1024);
           const uint64_t bd = B_MN ? tc::make_smem_desc(sB + k * 2048, 8192, 1024) : tc::make_smem_desc(sB + k * 32, 16, 1024);
-          tc::umma_f16(d_tmem, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          if (NCTA == 2) tc::umma_f16_pair(d_tmem, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          else tc::umma_f16(d_tmem, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
         }
-        tc::umma_commit(empty_bar + s);
+        if (NCTA == 2) tc::umma_commit_pair(empty_bar + s); else tc::umma_commit(empty_bar + s);
       }
       if (aborted) break;
-      tc::umma_commit(tmem_full_bar + buf);
+      if (NCTA == 2) tc::umma_commit_pair(tmem_full_bar + buf); else tc::umma_commit(tmem_full_bar + buf);
     }
   } else if (warp >= 2) {
-    // ---------------- epilogue: 8 warps; warp w reads TMEM lanes 32 (w & 3) .. +31, columns of half (w - 2) / 4
+    // ---------------- epilogue: group g = (warp - 2) / 4 owns columns [g BN/2, (g + 1) BN/2) of the CTA's 128 rows
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;
-    const int r = quarter * 32 + lane;
-    const int half_cols = p.BN >> 1;
+    const int g = (warp - 2) >> 2;
+    const int r = quarter * 32 + lane;                    // row of the CTA's accumulator = TMEM lane
+    const int half_cols = p.BN >> 1;                      // 32, 64 or 128
+    const int n_pan = half_cols >= 64 ? half_cols / 64 : (g == 0 ? 1 : 0);   // BN = 64: group 0 takes the one panel
+    const int g_col = half_cols >= 64 ? g * half_cols : 0;
+    const int bar_id = 2 + g;                             // named barrier of this group (128 threads)
+    const bool elected = (warp == 2 + 4 * g) && lane == 0;                   // first warp of the group, lane 0
+    uint8_t* my_panels = panels + g * 2 * PANEL_BYTES;
+    uint64_t* my_in_bar = in_bar + g * 2;
     uint32_t seed = 0u;
     float inv_keep = 1.f;
     if (EPI == E_BIAS_DROPOUT_RESID && p.p > 0.f) { seed = (uint32_t)(*p.seed); inv_keep = 1.f / (1.f - p.p); }
-    int t_local = 0;
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++t_local) {
+    int t_local = 0, pan_count = 0;
+    for (int item = unit; item < n_items; item += n_units, ++t_local) {
       const int tile = item / p.splits;
-      const int m0 = (tile / p.n_n_tiles) * BM, n0 = (tile % p.n_n_tiles) * p.BN;
+      const int m0 = (tile / p.n_n_tiles) * (BM * NCTA) + (int)rank * BM;
+      const int n0 = (tile % p.n_n_tiles) * p.BN;
       const int row = m0 + r;
-      const bool row_ok = row < p.M;
       const int buf = t_local & 1;
       const uint32_t use = (uint32_t)(t_local >> 1);
+      if (HAS_IN && elected) {
+        // fetch this tile's R panels while its main loop runs; the panels are free once the previous item's
+        // stores have read them
+        tc::tma_store_wait_read<0>();
+        for (int pi = 0; pi < n_pan; ++pi) {
+          tc::mbar_expect_tx(my_in_bar + pi, PANEL_BYTES);
+          tc::tma_load_2d(my_panels + pi * PANEL_BYTES, &tmR, my_in_bar + pi, n0 + g_col + 64 * pi, m0);
+        }
+      }
       if (!tc::mbar_wait(tmem_full_bar + buf, use & 1, aborted, p.status, tc::SITE_TMEM_FULL, item)) *s_abort = 1;
       asm volatile("bar.sync 1, 256;" ::: "memory");
       if (*s_abort) break;                                   // the same answer in all eight warps
       tc::tc_fence_after();
-      const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * ACC_STRIDE + (uint32_t)(half * half_cols);
-      for (int c0 = 0; c0 < half_cols; c0 += 32) {
-        float v[32];
-        tc::tmem_ld32(tbase + c0, v);
-        const int c_in_tile = half * half_cols + c0;
-        epilogue_fragment<T, EPI>(p, v, row, row_ok, n0 + c_in_tile, lane, seed, inv_keep, tile, r, c_in_tile);
+      const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * ACC_STRIDE + (uint32_t)g_col;
+      if (STAGED) {
+        for (int pi = 0; pi < n_pan; ++pi, ++pan_count) {
+          const int pcol = n0 + g_col + 64 * pi;             // first column of the panel
+          // staging buffer(s): R panels are updated in place; a two-output epilogue fills both buffers per
+          // panel; a one-output epilogue alternates between them
+          uint8_t* pan = my_panels + (HAS_IN ? pi : (EPI == E_BIAS_GELU ? 0 : (pan_count & 1))) * PANEL_BYTES;
+          uint8_t* pan2 = my_panels + PANEL_BYTES;           // BIAS_GELU: the activation panel
+          if (HAS_IN) {
+            if (!tc::mbar_wait(my_in_bar + pi, (uint32_t)t_local & 1, aborted, p.status, tc::SITE_FULL, 2000 + pi)) *s_abort = 1;
+          } else {
+            // the buffer is free once the store issued from it earlier has read it
+            if (elected) { if (EPI == E_BIAS_GELU) tc::tma_store_wait_read<0>(); else tc::tma_store_wait_read<1>(); }
+            asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+          }
+          float colsum[2] = {0.f, 0.f};
+#pragma unroll
+          for (int hc = 0; hc < 2; ++hc) {                   // two 32-column fragments per panel
+            float v[32];
+            tc::tmem_ld32(tbase + 64 * pi + 32 * hc, v);
+#pragma unroll
+            for (int j8 = 0; j8 < 4; ++j8) {
+              const int chunk = 4 * hc + j8;
+              const int c = pcol + 8 * chunk;
+              const uint32_t off = panel_off(r, chunk);
+              uint4* slot = reinterpret_cast<uint4*>(pan + off);
+              float o[8];
+              if (EPI == E_STORE) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = v[8 * j8 + j];
+              } else if (EPI == E_BIAS_GELU) {
+                float b[8], a[8];
+                if (c < p.N) unpack8<T>(__ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.bias) + c)), b);
+                else {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) b[j] = 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  o[j] = round_through<T>(v[8 * j8 + j] + b[j]);     // the backward pass differentiates at the stored value
+                  a[j] = gelu_f(o[j]);
+                }
+                *reinterpret_cast<uint4*>(pan2 + off) = pack8<T>(a);
+              } else if (EPI == E_BIAS_DROPOUT_RESID) {
+                float b[8], res[8];
+                if (c < p.N) unpack8<T>(__ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.bias) + c)), b);
+                else {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) b[j] = 0.f;
+                }
+                unpack8<T>(*slot, res);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  float t = v[8 * j8 + j] + b[j];
+                  if (p.p > 0.f) t = keep(seed, p.stream, (uint32_t)(row * p.N + c + j), p.p) ? t * inv_keep : 0.f;
+                  o[j] = res[j] + t;
+                }
+              } else if (EPI == E_ADD) {
+                float res[8];
+                unpack8<T>(*slot, res);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = v[8 * j8 + j] + res[j];
+              } else {   // E_GELU_BWD: rows past M read F = 0 and a zero accumulator, so they add nothing to the sums
+                float f[8];
+                unpack8<T>(*slot, f);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  o[j] = round_through<T>(v[8 * j8 + j] * gelu_grad_f(f[j]));
+                  v[8 * j8 + j] = o[j];
+                }
+              }
+              *slot = pack8<T>(o);
+            }
+            if (EPI == E_GELU_BWD && p.colacc != nullptr) colsum[hc] = warp_colsum32(v, lane);
+          }
+          if (EPI == E_GELU_BWD && p.colacc != nullptr) {
+#pragma unroll
+            for (int hc = 0; hc < 2; ++hc) {
+              const int c = pcol + 32 * hc + lane;           // lane L holds the sum of column L of the fragment
+              if (c < p.N) atomicAdd(p.colacc + (size_t)(blockIdx.x % kColReplicas) * p.col_tot + p.col_off + c, colsum[hc]);
+            }
+          }
+          tc::fence_proxy_async();                 // generic-proxy writes of the panel before the async-proxy store
+          asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+          if (elected) {
+            if (EPI == E_BIAS_GELU) {
+              tc::tma_store_2d(&tmF, pan, pcol, m0);
+              tc::tma_store_2d(&tmC, pan2, pcol, m0);
+            } else {
+              tc::tma_store_2d(&tmC, pan, pcol, m0);
+            }
+            tc::tma_store_commit();
+          }
+        }
+      }
+      if (EPI == E_SPLITK) {
+        const uint32_t tsk = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * ACC_STRIDE + (uint32_t)(g * half_cols);
+        for (int c0 = 0; c0 < half_cols; c0 += 32) {
+          float v[32];
+          tc::tmem_ld32(tsk + c0, v);
+          const int c_in_tile = g * half_cols + c0;
+          const int col0 = n0 + c_in_tile;
+          if (row < p.M) {
+            if (p.splits == 1) {
+#pragma unroll
+              for (int j8 = 0; j8 < 4; ++j8)
+                if (col0 + 8 * j8 < p.N)
+                  *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.C) + (size_t)row * p.ldc + col0 + 8 * j8) = pack8<T>(v + 8 * j8);
+            } else {
+              float* s = p.sk_scratch + (size_t)tile * (BM * NCTA * p.BN) + (size_t)((int)rank * BM + r) * p.BN + c_in_tile;
+#pragma unroll
+              for (int j4 = 0; j4 < 8; ++j4)
+                if (col0 + 4 * j4 < p.N) red_add_f32x4(s + 4 * j4, v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]);
+            }
+          }
+        }
       }
       // every tcgen05.ld of this item has completed (tmem_ld32 waits): hand the accumulator back to the MMA warp
       tc::tc_fence_before();
       __syncwarp();
-      if (lane == 0) tc::mbar_arrive(tmem_empty_bar + buf);
+      if (lane == 0) {
+        if (NCTA == 2) tc::mbar_arrive_leader(tmem_empty_bar + buf); else tc::mbar_arrive(tmem_empty_bar + buf);
+      }
       if (EPI == E_SPLITK && p.splits > 1) {
-        // split-K fix-up: the CTA that adds the last partial of a tile converts the sum and re-zeroes the scratch
+        // split-K fix-up: the CTA that adds the last partial of its half of a tile converts the sum and re-zeroes
+        // the scratch (each CTA of a pair counts its own half)
+        unsigned* cnt = p.sk_counters + (size_t)tile * NCTA + rank;
         __threadfence();
         asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (threadIdx.x == 64) *s_last = (atomicAdd(p.sk_counters + tile, 1u) == (unsigned)(p.splits - 1)) ? 1 : 0;
+        if (threadIdx.x == 64) *s_last = (atomicAdd(cnt, 1u) == (unsigned)(p.splits - 1)) ? 1 : 0;
         asm volatile("bar.sync 1, 256;" ::: "memory");
         if (*s_last) {
+          // this CTA's 128 x BN block of the tile's scratch is contiguous: walk it with coalesced 16-byte accesses,
+          // several loads in flight per thread
           __threadfence();
-          if (row_ok) {
-            T* C = reinterpret_cast<T*>(p.C);
-            float* srow = p.sk_scratch + (size_t)tile * (BM * p.BN) + (size_t)r * p.BN + half * half_cols;
-            for (int c = 0; c < half_cols; c += 8) {
-              const int col = n0 + half * half_cols + c;
-              if (col < p.N) {
-                const float4 x0 = __ldcg(reinterpret_cast<const float4*>(srow + c));
-                const float4 x1 = __ldcg(reinterpret_cast<const float4*>(srow + c + 4));
-                __stcg(reinterpret_cast<float4*>(srow + c), make_float4(0.f, 0.f, 0.f, 0.f));
-                __stcg(reinterpret_cast<float4*>(srow + c + 4), make_float4(0.f, 0.f, 0.f, 0.f));
-                const float o[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-                *reinterpret_cast<uint4*>(C + (size_t)row * p.ldc + col) = pack8<T>(o);
+          T* C = reinterpret_cast<T*>(p.C);
+          float4* blk = reinterpret_cast<float4*>(p.sk_scratch + (size_t)tile * (BM * NCTA * p.BN) + (size_t)((int)rank * BM) * p.BN);
+          const int n4 = BM * p.BN / 4;
+          const int bn4 = p.BN / 4;
+          const int et = (int)threadIdx.x - 64;
+          for (int base = et; base < n4; base += 256 * 4) {
+            float4 x[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int i4 = base + 256 * u;
+              x[u] = i4 < n4 ? __ldcg(blk + i4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int i4 = base + 256 * u;
+              if (i4 < n4) {
+                __stcg(blk + i4, make_float4(0.f, 0.f, 0.f, 0.f));
+                const int rr = i4 / bn4, cc = (i4 - rr * bn4) * 4;
+                const int grow = m0 + rr, gcol = n0 + cc;
+                if (grow < p.M && gcol < p.N) {
+                  uint2 o;
+                  T* e = reinterpret_cast<T*>(&o);
+                  e[0] = from_f<T>(x[u].x); e[1] = from_f<T>(x[u].y); e[2] = from_f<T>(x[u].z); e[3] = from_f<T>(x[u].w);
+                  *reinterpret_cast<uint2*>(C + (size_t)grow * p.ldc + gcol) = o;
+                }
               }
             }
           }
-          if (threadIdx.x == 64) p.sk_counters[tile] = 0u;
+          if (threadIdx.x == 64) *cnt = 0u;
         }
       }
     }
+    if (STAGED && elected) tc::tma_store_wait_all();       // the stores have left shared memory and are globally visible
   }
   tc::tc_fence_before();
   __syncthreads();
+  if (NCTA == 2) tc::cluster_sync_all();                   // the peer no longer reads this CTA's memory or barriers
   if (warp == 1) {
     tc::tc_fence_after();
-    tc::tmem_dealloc(tmem_base, TMEM_COLS);
+    if (NCTA == 2) tc::tmem_dealloc_pair(tmem_base, TMEM_COLS); else tc::tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
+
+}  // namespace eg
+}  // namespace rb
 
 // ------------------------------------------------------------------------------------ LayerNorm of a stored input
 // y = LN(pre) with the row statistics kept for the backward pass; `pre` was written by the BIAS_DROPOUT_RESID
 // epilogue.  One warp per row, 16-byte accesses.
+namespace rb {
+namespace eg {
 template <typename T, int NV>
 __global__ void __launch_bounds__(128) ln_fwd_kernel(const T* __restrict__ pre, const T* __restrict__ gamma,
                                                      const T* __restrict__ beta, T* __restrict__ y,
@@ -394,120 +521,167 @@ __global__ void __launch_bounds__(128) ln_fwd_kernel(const T* __restrict__ pre, 
   }
   if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
 }
-
 }  // namespace eg
 }  // namespace rb
 
 using namespace rb;
 using namespace rb::eg;
 
-template <typename T, int LAYOUT, int EPI>
-static int launch_enc_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int ctas, cudaStream_t st) {
+struct Maps { CUtensorMap a, b, c, r, f; };
+
+template <typename T, int LAYOUT, int EPI, int NCTA>
+static int launch_enc_gemm(const Maps& m, const Params& p, int units, cudaStream_t st) {
   static bool attr_set = false;
-  auto k = enc_gemm_kernel<T, LAYOUT, EPI>;
+  auto k = enc_gemm_kernel<T, LAYOUT, EPI, NCTA>;
+  constexpr int smem = Cfg<NCTA, EPI != E_SPLITK>::kSmem;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -5;
+    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -5;
     attr_set = true;
   }
-  k<<<ctas, THREADS, SMEM_BYTES, st>>>(ta, tb, p);
-  return 0;
+  if (NCTA == 1) {
+    k<<<units, THREADS, smem, st>>>(m.a, m.b, m.c, m.r, m.f, p);
+    return 0;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * units, 1, 1);
+  cfg.blockDim = dim3(THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, k, m.a, m.b, m.c, m.r, m.f, p);
+  return e == cudaSuccess ? 0 : (int)e;
 }
 
-template <typename T>
-static int dispatch_enc_gemm(int layout, int epi, const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int ctas,
-                             cudaStream_t st) {
+template <typename T, int NCTA>
+static int dispatch_enc_gemm(int layout, int epi, const Maps& m, const Params& p, int units, cudaStream_t st) {
   if (layout == L_NT) {
-    if (epi == E_STORE) return launch_enc_gemm<T, L_NT, E_STORE>(ta, tb, p, ctas, st);
-    if (epi == E_BIAS_GELU) return launch_enc_gemm<T, L_NT, E_BIAS_GELU>(ta, tb, p, ctas, st);
-    if (epi == E_BIAS_DROPOUT_RESID) return launch_enc_gemm<T, L_NT, E_BIAS_DROPOUT_RESID>(ta, tb, p, ctas, st);
+    if (epi == E_STORE) return launch_enc_gemm<T, L_NT, E_STORE, NCTA>(m, p, units, st);
+    if (epi == E_BIAS_GELU) return launch_enc_gemm<T, L_NT, E_BIAS_GELU, NCTA>(m, p, units, st);
+    if (epi == E_BIAS_DROPOUT_RESID) return launch_enc_gemm<T, L_NT, E_BIAS_DROPOUT_RESID, NCTA>(m, p, units, st);
   } else if (layout == L_NN) {
-    if (epi == E_STORE) return launch_enc_gemm<T, L_NN, E_STORE>(ta, tb, p, ctas, st);
-    if (epi == E_ADD) return launch_enc_gemm<T, L_NN, E_ADD>(ta, tb, p, ctas, st);
-    if (epi == E_GELU_BWD) return launch_enc_gemm<T, L_NN, E_GELU_BWD>(ta, tb, p, ctas, st);
+    if (epi == E_STORE) return launch_enc_gemm<T, L_NN, E_STORE, NCTA>(m, p, units, st);
+    if (epi == E_ADD) return launch_enc_gemm<T, L_NN, E_ADD, NCTA>(m, p, units, st);
+    if (epi == E_GELU_BWD) return launch_enc_gemm<T, L_NN, E_GELU_BWD, NCTA>(m, p, units, st);
   } else if (layout == L_TN) {
-    if (epi == E_SPLITK) return launch_enc_gemm<T, L_TN, E_SPLITK>(ta, tb, p, ctas, st);
+    if (epi == E_SPLITK) return launch_enc_gemm<T, L_TN, E_SPLITK, NCTA>(m, p, units, st);
   }
   return -4;
 }
 
-// N tile: the candidate with the fewest rounds x tile cost over the SMs (small problems want more, smaller tiles)
-static int pick_bn(int M, int N, int forced) {
-  if (forced == 64 || forced == 128 || forced == 256) return forced;
+// Tile shape and K-splits.  The kernel is bound by operand fetch: an SM sustains about one 128-byte operand row
+// per 3.3 clocks, a k block of a CTA costs max(rows fetched x 3.3, MMA clocks = 2 BN) clocks, and the work is
+// spread over the units (SMs, or SM pairs) in rounds.  Candidates: (NCTA, BN) with NCTA in {1, 2}.
+struct Plan { int ncta, bn, splits, tiles; };
+
+static int g_prefetch = 0;
+RB_API void rb_enc_gemm_set_prefetch(int on) { g_prefetch = on ? 1 : 0; }
+
+static Plan make_plan(int layout, int M, int N, int K, int bn_forced, int ncta_forced) {
   const int sms = sm_count();
-  const int mt = (M + BM - 1) / BM;
-  int best = 256;
-  long best_cost = -1;
-  for (int bn = 256; bn >= 64; bn >>= 1) {
-    if (bn > 64 && bn / 2 >= N) continue;                  // a narrower tile already covers every column
-    const long tiles = (long)mt * ((N + bn - 1) / bn);
-    const long cost = ((tiles + sms - 1) / sms) * (bn + 48);
-    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+  const int kb = (K + BK - 1) / BK;
+  Plan best{1, 128, 1, 1};
+  double best_cost = -1.0;
+  for (int ncta = 1; ncta <= 2; ++ncta) {
+    if (ncta_forced && ncta != ncta_forced) continue;
+    for (int bn = 256; bn >= 64; bn >>= 1) {
+      if (bn_forced && bn != bn_forced) continue;
+      if (ncta == 2 && bn < 128) continue;
+      if (!bn_forced && bn > 64 && bn / 2 >= N) continue;            // a narrower tile already covers every column
+      const int tiles = ((M + BM * ncta - 1) / (BM * ncta)) * ((N + bn - 1) / bn);
+      const int units = sms / ncta;
+      int splits = 1;
+      if (layout == L_TN) {
+        splits = units / tiles;
+        if (splits < 1) splits = 1;
+        if (splits > 16) splits = 16;
+        if (splits > kb) splits = kb;
+      }
+      const int kb_per = (kb + splits - 1) / splits;
+      splits = (kb + kb_per - 1) / kb_per;
+      const long items = (long)tiles * splits;
+      const long rounds = (items + units - 1) / units;
+      const double fetch = (128.0 + bn / ncta) * 3.3, mma = 2.0 * bn;
+      const double cost = rounds * (kb_per * (fetch > mma ? fetch : mma) + 1500.0 + (splits > 1 ? 6.0 * bn : 0.0));
+      if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = Plan{ncta, bn, splits, tiles}; }
+    }
   }
   return best;
+}
+
+// What rb_enc_gemm will use for (M, N, K): tile shape, K-splits for layout TN, and the sizes of the split-K
+// scratch (floats) and counters (words) it needs when splits > 1.
+RB_API int rb_enc_gemm_plan(int layout, int M, int N, int K, int bn_forced, int ncta_forced, int* ncta_out, int* bn_out,
+                            int* splits_out, long long* scratch_floats, int* counter_words) {
+  const Plan pl = make_plan(layout, M, N, K, bn_forced, ncta_forced);
+  *ncta_out = pl.ncta; *bn_out = pl.bn; *splits_out = pl.splits;
+  *scratch_floats = (long long)pl.tiles * BM * pl.ncta * pl.bn;
+  *counter_words = pl.tiles * pl.ncta;
+  return 0;
 }
 
 // C = op(A) op(B) with a fused epilogue; see the head of this file.  Leading dimensions in elements.
 //   layout 0 (NT): A[M, lda>=K], B[N, ldb>=K];  1 (NN): A[M, lda>=K], B[K, ldb>=N];  2 (TN): A[K, lda>=M], B[K, ldb>=N]
 //   dtype: RB_BF16 or RB_F16 (operands, C, bias, R and F all have it; accumulation is fp32)
-//   splits (TN only): K-splits; > 1 needs sk_scratch of n_tiles * 128 * BN floats (zero on entry, left zero) and
-//   sk_counters of n_tiles words (zero on entry, left zero).  bn_forced: 0 = choose.
+//   R [M, ldr]: residual (BIAS_DROPOUT_RESID, ADD) or stored pre-activation (GELU_BWD); F [M, ldf]: pre-activation
+//   output (BIAS_GELU).  Layout TN with more than one K-split needs sk_scratch / sk_counters of the sizes
+//   rb_enc_gemm_plan reports (zero on entry, left zero).  bn_forced / ncta_forced: 0 = choose.
 // Returns 0, or -3 for an unsupported shape (the caller then uses the library GEMM).
 RB_API int rb_enc_gemm(int dtype, int layout, int epi, const void* A, const void* B, void* C, int M, int N, int K, int lda,
                        int ldb, int ldc, const void* bias, const void* R, int ldr, void* F, int ldf, float p_drop,
                        const int* seed, unsigned stream_id, float* colacc, int col_tot, int col_off, float* sk_scratch,
-                       unsigned* sk_counters, int splits, int bn_forced, int* status, cudaStream_t st) {
+                       unsigned* sk_counters, int bn_forced, int ncta_forced, int* status, cudaStream_t st) {
   if (dtype != RB_BF16 && dtype != RB_F16) return -1;
   if (M < 1 || N < 1 || K < 1 || N % 8 || lda % 8 || ldb % 8 || ldc % 8 || ldr % 8 || ldf % 8) return -3;
   if (layout == L_TN && M % 8) return -3;
-  const bool bf16 = dtype == RB_BF16;
-  const int BN = pick_bn(M, N, bn_forced);
-  CUtensorMap ta, tb;
-  int rc;
-  if (layout == L_TN) rc = tc::make_tmap_2d(&ta, A, K, M, lda, 64, 64, bf16);
-  else rc = tc::make_tmap_2d(&ta, A, M, K, lda, 64, BM, bf16);
-  if (rc) return rc;
-  if (layout == L_NT) rc = tc::make_tmap_2d(&tb, B, N, K, ldb, 64, BN, bf16);
-  else rc = tc::make_tmap_2d(&tb, B, K, N, ldb, 64, 64, bf16);
-  if (rc) return rc;
-  Params p{};
-  p.M = M; p.N = N; p.BN = BN;
-  p.n_m_tiles = (M + BM - 1) / BM; p.n_n_tiles = (N + BN - 1) / BN;
-  p.kb_total = (K + BK - 1) / BK;
-  if (layout != L_TN || splits < 1) splits = 1;
-  if (splits > p.kb_total) splits = p.kb_total;
-  p.kb_per_split = (p.kb_total + splits - 1) / splits;
-  p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
-  if (p.splits > 1 && (sk_scratch == nullptr || sk_counters == nullptr)) return -3;
-  p.C = C; p.ldc = ldc; p.bias = bias; p.R = R; p.ldr = ldr; p.F = F; p.ldf = ldf;
-  p.p = p_drop; p.seed = seed; p.stream = stream_id;
-  p.colacc = colacc; p.col_tot = col_tot; p.col_off = col_off;
-  p.sk_scratch = sk_scratch; p.sk_counters = sk_counters; p.status = status;
   if ((epi == E_BIAS_GELU || epi == E_BIAS_DROPOUT_RESID) && bias == nullptr) return -3;
   if ((epi == E_BIAS_DROPOUT_RESID || epi == E_ADD || epi == E_GELU_BWD) && R == nullptr) return -3;
   if (epi == E_BIAS_GELU && F == nullptr) return -3;
   if (epi == E_BIAS_DROPOUT_RESID && p_drop > 0.f && seed == nullptr) return -3;
+  const bool bf16 = dtype == RB_BF16;
+  const Plan pl = make_plan(layout, M, N, K, bn_forced, ncta_forced);
+  const int BN = pl.bn, b_rows = BN / pl.ncta;
+  Maps m;
+  int rc;
+  if (layout == L_TN) rc = tc::make_tmap_2d(&m.a, A, K, M, lda, 64, 64, bf16);
+  else rc = tc::make_tmap_2d(&m.a, A, M, K, lda, 64, BM, bf16);
+  if (rc) return rc;
+  if (layout == L_NT) rc = tc::make_tmap_2d(&m.b, B, N, K, ldb, 64, b_rows, bf16);
+  else rc = tc::make_tmap_2d(&m.b, B, K, N, ldb, 64, 64, bf16);
+  if (rc) return rc;
+  // output / input panels: [128 rows x 64 columns] boxes of the row-major [M, N] matrices
+  rc = tc::make_tmap_2d(&m.c, C, M, N, ldc, 64, BM, bf16);
+  if (rc) return rc;
+  m.r = m.c;
+  m.f = m.c;
+  if (R != nullptr && (rc = tc::make_tmap_2d(&m.r, R, M, N, ldr, 64, BM, bf16)) != 0) return rc;
+  if (F != nullptr && (rc = tc::make_tmap_2d(&m.f, F, M, N, ldf, 64, BM, bf16)) != 0) return rc;
+  Params p{};
+  p.M = M; p.N = N; p.BN = BN;
+  p.n_m_tiles = (M + BM * pl.ncta - 1) / (BM * pl.ncta); p.n_n_tiles = (N + BN - 1) / BN;
+  p.kb_total = (K + BK - 1) / BK;
+  p.splits = pl.splits;
+  p.kb_per_split = (p.kb_total + p.splits - 1) / p.splits;
+  if (p.splits > 1 && (sk_scratch == nullptr || sk_counters == nullptr)) return -3;
+  p.C = C; p.ldc = ldc; p.bias = bias;
+  p.p = p_drop; p.seed = seed; p.stream = stream_id;
+  p.colacc = colacc; p.col_tot = col_tot; p.col_off = col_off;
+  p.sk_scratch = sk_scratch; p.sk_counters = sk_counters; p.status = status;
+  p.prefetch = g_prefetch;
   const int n_items = p.n_m_tiles * p.n_n_tiles * p.splits;
-  const int ctas = n_items < sm_count() ? n_items : sm_count();
-  rc = bf16 ? dispatch_enc_gemm<__nv_bfloat16>(layout, epi, ta, tb, p, ctas, st)
-            : dispatch_enc_gemm<__half>(layout, epi, ta, tb, p, ctas, st);
+  const int max_units = sm_count() / pl.ncta;
+  const int units = n_items < max_units ? n_items : max_units;
+  if (pl.ncta == 2)
+    rc = bf16 ? dispatch_enc_gemm<__nv_bfloat16, 2>(layout, epi, m, p, units, st) : dispatch_enc_gemm<__half, 2>(layout, epi, m, p, units, st);
+  else
+    rc = bf16 ? dispatch_enc_gemm<__nv_bfloat16, 1>(layout, epi, m, p, units, st) : dispatch_enc_gemm<__half, 1>(layout, epi, m, p, units, st);
   if (rc) return rc;
   RB_LAUNCH_CHECK();
-  return 0;
-}
-
-// What rb_enc_gemm will use for (M, N, K): N tile, K-splits for layout TN, number of tiles (scratch sizing).
-RB_API int rb_enc_gemm_plan(int layout, int M, int N, int K, int bn_forced, int* bn_out, int* splits_out, int* tiles_out) {
-  const int BN = pick_bn(M, N, bn_forced);
-  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  int splits = 1;
-  if (layout == L_TN) {
-    const int kb = (K + BK - 1) / BK;
-    splits = sm_count() / tiles;
-    if (splits < 1) splits = 1;
-    if (splits > 16) splits = 16;
-    if (splits > kb) splits = kb;
-  }
-  *bn_out = BN; *splits_out = splits; *tiles_out = tiles;
   return 0;
 }
 

@@ -29,15 +29,22 @@ class KernelError(RuntimeError):
 def lib():
     global _LIB
     if _LIB is None:
-        if not _build.is_current():
-            if os.environ.get("RENEE_B200_NO_BUILD") == "1" or not _has_nvcc():
-                if not os.path.exists(_build.LIB):
-                    raise KernelError(f"{_build.LIB} is missing and cannot be built here; run "
-                                      "`python -m renee_b200.ops.build`")
-            else:
-                _build.build()
-        _LIB = ctypes.CDLL(_build.LIB)
+        _load()
     return _LIB
+
+
+def _load():
+    global _LIB
+    if not _build.is_current():
+        if os.environ.get("RENEE_B200_NO_BUILD") == "1" or not _has_nvcc():
+            if not os.path.exists(_build.LIB):
+                raise KernelError(f"{_build.LIB} is missing and cannot be built here; run "
+                                  "`python -m renee_b200.ops.build`")
+        else:
+            _build.build()
+    _LIB = ctypes.CDLL(_build.LIB)
+    if os.environ.get("RENEE_B200_GEMM_PREFETCH", "0") == "1":
+        _LIB.rb_enc_gemm_set_prefetch(_I(1))
 
 
 def _has_nvcc() -> bool:
@@ -324,37 +331,44 @@ def enc_gemm_supported(t: torch.Tensor, *dims: int) -> bool:
 
 
 def _enc_gemm(layout, epi, A, B, C, M, N, K, bias=None, R=None, F=None, p=0.0, rng=None, stream=0, colacc=None,
-              col_tot=0, col_off=0, bn=0):
+              col_tot=0, col_off=0, bn=0, ncta=0):
     dev = C.device
     ws = workspace(dev)
-    sk_buf, sk_cnt, splits = None, None, 1
+    sk_buf, sk_cnt = None, None
+    if not bn:
+        bn = int(os.environ.get("RENEE_B200_GEMM_BN", "0"))        # experiments: force the N tile / the tile shape
+    if not ncta:
+        ncta = int(os.environ.get("RENEE_B200_GEMM_NCTA", "0"))
     if layout == L_TN:
-        bn_o, sp_o, tiles_o = _I(0), _I(0), _I(0)
-        lib().rb_enc_gemm_plan(_I(layout), _I(M), _I(N), _I(K), _I(bn), _c.byref(bn_o), _c.byref(sp_o), _c.byref(tiles_o))
-        splits = sp_o.value
-        if splits > 1:
+        ncta_o, bn_o, sp_o, words_o, floats_o = _I(0), _I(0), _I(0), _I(0), _LL(0)
+        lib().rb_enc_gemm_plan(_I(layout), _I(M), _I(N), _I(K), _I(bn), _I(ncta), _c.byref(ncta_o), _c.byref(bn_o),
+                               _c.byref(sp_o), _c.byref(floats_o), _c.byref(words_o))
+        if sp_o.value > 1:
             key = dev.index if dev.index is not None else torch.cuda.current_device()
-            sk_buf, sk_cnt = _SK.setdefault(key, _SplitKScratch()).get(dev, tiles_o.value * 128 * bn_o.value, tiles_o.value)
+            sk_buf, sk_cnt = _SK.setdefault(key, _SplitKScratch()).get(dev, floats_o.value, words_o.value)
     _call("rb_enc_gemm", _I(DT[C.dtype]), _I(layout), _I(epi), _p(A), _p(B), _p(C), _I(M), _I(N), _I(K),
           _I(A.stride(0)), _I(B.stride(0)), _I(C.stride(0)), _p(bias), _p(R), _I(R.stride(0) if R is not None else 0),
           _p(F), _I(F.stride(0) if F is not None else 0), _F(p), _p(rng.dev if rng is not None else None), _U(stream),
-          _p(colacc), _I(col_tot), _I(col_off), _p(sk_buf), _p(sk_cnt), _I(splits), _I(bn), _p(ws.status), _stream())
+          _p(colacc), _I(col_tot), _I(col_off), _p(sk_buf), _p(sk_cnt), _I(bn), _I(ncta), _p(ws.status), _stream())
 
 
-def linear_fwd(x, W, out, epi="store", bias=None, resid=None, pre_out=None, p=0.0, rng=None, stream=0, bn=0):
+def linear_fwd(x, W, out, epi="store", bias=None, resid=None, pre_out=None, p=0.0, rng=None, stream=0, bn=0, ncta=0):
     """``out = epilogue(x @ W.T)`` for ``x [T, K]``, ``W [N, K]`` (an ``nn.Linear`` weight):
 
     * ``store``: the product;
     * ``bias_gelu``: ``pre_out = x W^T + bias`` (kept for the backward pass), ``out = gelu(pre_out)``;
-    * ``bias_dropout_resid``: ``out = resid + dropout(x W^T + bias)`` — the input of the following LayerNorm."""
+    * ``bias_dropout_resid``: ``out = resid + dropout(x W^T + bias)`` — the input of the following LayerNorm.
+
+    ``bn`` / ``ncta`` force the N tile (64, 128, 256) and the tile shape (1: one CTA per 128-row tile, 2: a CTA
+    pair per 256-row tile); 0 lets the library choose."""
     T, K = x.shape
     N = W.shape[0]
     code = {"store": E_STORE, "bias_gelu": E_BIAS_GELU, "bias_dropout_resid": E_BIAS_DROPOUT_RESID}[epi]
-    _enc_gemm(L_NT, code, x, W, out, T, N, K, bias=bias, R=resid, F=pre_out, p=p, rng=rng, stream=stream, bn=bn)
+    _enc_gemm(L_NT, code, x, W, out, T, N, K, bias=bias, R=resid, F=pre_out, p=p, rng=rng, stream=stream, bn=bn, ncta=ncta)
     return out
 
 
-def linear_dgrad(dy, W, out, epi="store", resid=None, pre=None, dbias=None, bn=0):
+def linear_dgrad(dy, W, out, epi="store", resid=None, pre=None, dbias=None, bn=0, ncta=0):
     """``out = epilogue(dy @ W)`` for ``dy [T, N]``, ``W [N, K]``:
 
     * ``store``: the product;  ``add``: product ``+ resid`` (the residual branch's gradient);
@@ -364,21 +378,21 @@ def linear_dgrad(dy, W, out, epi="store", resid=None, pre=None, dbias=None, bn=0
     K = W.shape[1]
     code = {"store": E_STORE, "add": E_ADD, "gelu_bwd": E_GELU_BWD}[epi]
     if code != E_GELU_BWD or dbias is None:
-        _enc_gemm(L_NN, code, dy, W, out, T, K, N, R=resid if code == E_ADD else pre, bn=bn)
+        _enc_gemm(L_NN, code, dy, W, out, T, K, N, R=resid if code == E_ADD else pre, bn=bn, ncta=ncta)
         return out
     plan = _DEFER if _DEFER is not None else DeferredColumns(out.device, out.dtype)
     acc = plan.slot([dbias], K)
-    _enc_gemm(L_NN, code, dy, W, out, T, K, N, R=pre, colacc=acc, col_tot=K, col_off=0, bn=bn)
+    _enc_gemm(L_NN, code, dy, W, out, T, K, N, R=pre, colacc=acc, col_tot=K, col_off=0, bn=bn, ncta=ncta)
     if _DEFER is None:
         plan.finalize()
     return out
 
 
-def linear_wgrad(dy, x, dW, bn=0):
+def linear_wgrad(dy, x, dW, bn=0, ncta=0):
     """``dW = dy.T @ x`` for ``dy [T, N]``, ``x [T, K]``, ``dW [N, K]`` (split over T, reduced in fp32)."""
     T, N = dy.shape
     K = x.shape[1]
-    _enc_gemm(L_TN, E_SPLITK, dy, x, dW, N, K, T, bn=bn)
+    _enc_gemm(L_TN, E_SPLITK, dy, x, dW, N, K, T, bn=bn, ncta=ncta)
     return dW
 
 

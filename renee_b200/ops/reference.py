@@ -212,7 +212,7 @@ def xfc_dx(Gt, W, scale):
     return scale * (Gt.float().t() @ W.float())
 
 
-def xfc_dw_sgd(Gt, X, W, M, lr, mo, wd, dW_acc=None):
+def xfc_dw_sgd(Gt, X, W, M, lr, mo, wd, dW_acc=None, sr_seed=None):
     """``dW = Gt · X`` then SGD with momentum and L2 weight decay applied in place on ``W``/``M``
     (torch/apex SGD semantics: ``g += wd·W; M = mo·M + g; W -= lr·M``; a zero-initialised ``M``
     makes the first step ``M = g``).  With ``dW_acc`` the gradient is only accumulated."""
@@ -220,14 +220,32 @@ def xfc_dw_sgd(Gt, X, W, M, lr, mo, wd, dW_acc=None):
     if dW_acc is not None:
         dW_acc += dW
         return
-    sgd_update(W, M, dW, lr, mo, wd)
+    sgd_update(W, M, dW, lr, mo, wd, sr_seed)
 
 
-def sgd_update(W, M, dW, lr, mo, wd):
+def stochastic_round_fp16(x: torch.Tensor, seed: int, stream: int = 0x5152) -> torch.Tensor:
+    """fp32 -> fp16 with stochastic rounding, the arithmetic of the dW kernel's epilogue (``sr_half``): add
+    13 uniform random bits below the mantissa bits fp16 keeps, then truncate.  Unbiased in fp16's normal range.
+    The random bits come from the counter-based hash of the element index."""
+    from .rng import mix32
+    idx = torch.arange(x.numel(), dtype=torch.int64, device=x.device)
+    rnd = mix32(int(seed), stream, idx) & 0x1FFF
+    bits = x.float().contiguous().view(torch.int32).view(-1).to(torch.int64) & 0xFFFFFFFF
+    bits = ((bits + rnd) & 0xFFFFFFFF) & ~0x1FFF
+    bits = torch.where(bits >= 2 ** 31, bits - 2 ** 32, bits).to(torch.int32)
+    return bits.view(torch.float32).view(x.shape).to(torch.float16)      # exact: the dropped bits are zero
+
+
+def sgd_update(W, M, dW, lr, mo, wd, sr_seed=None):
+    """``sr_seed``: round the new fp16 weights stochastically (fp16 storage only) instead of to nearest."""
     g = dW.float() + wd * W.float()
     m = mo * M.float() + g
     M.copy_(m.to(M.dtype))
-    W.copy_((W.float() - lr * M.float()).to(W.dtype))
+    w = W.float() - lr * M.float()
+    if sr_seed is not None and W.dtype == torch.float16:
+        W.copy_(stochastic_round_fp16(w, sr_seed))
+    else:
+        W.copy_(w.to(W.dtype))
 
 
 def topk_logits(X, W, k):

@@ -73,7 +73,7 @@ class TrainConfig:
     evaluation_epochs: int = 5       # main.py:184
     cuda_graph: bool = True
     fused_comm: bool = True
-    stochastic_round: bool = False
+    stochastic_round: bool = True     # fp16 W storage: round the updated weights stochastically (see models/xfc.py)
     overlap_dw: bool = False         # issue the last dW+SGD kernel on a side stream, under the encoder backward
     out_dir: str = ""
 

@@ -34,40 +34,45 @@ SHAPES = [(1024, 768, 2304), (8192, 768, 768), (1024, 768, 3072), (8192, 3072, 7
           (333, 512, 128), (129, 64, 64)]
 
 
+NCTA = [0, 1, 2]       # 0: the library chooses; 1: one CTA per 128-row tile; 2: a CTA pair (cta_group::2) per 256-row tile
+
+
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("T,K,N", SHAPES)
-@pytest.mark.parametrize("bn", [0, 64, 128])
-def test_linear_fwd_store(dt, T, K, N, bn):
-    if bn and (T > 2000 or dt == torch.float16):
+@pytest.mark.parametrize("bn,ncta", [(0, 0), (64, 1), (128, 1), (256, 1), (128, 2), (256, 2)])
+def test_linear_fwd_store(dt, T, K, N, bn, ncta):
+    if bn and (T > 2000 or dt == torch.float16) and not (bn == 256 and N >= 768):
         pytest.skip("forced tile sizes are covered on the small shapes")
     torch.manual_seed(T + K)
     x = torch.randn(T, K, device=dev()).to(dt)
     W = (torch.randn(N, K, device=dev()) * 0.05).to(dt)
     out = torch.full((T, N), 7.0, device=dev(), dtype=dt)
-    cu().linear_fwd(x, W, out, bn=bn)
+    cu().linear_fwd(x, W, out, bn=bn, ncta=ncta)
     want = x.float() @ W.float().t()
     assert _rel(out, want) < 1e-2
     cu().check_status()
 
 
+@pytest.mark.parametrize("ncta", NCTA)
 @pytest.mark.parametrize("T,K,N", [(1024, 768, 3072), (8192, 768, 3072), (200, 128, 512)])
-def test_linear_fwd_bias_gelu(T, K, N):
+def test_linear_fwd_bias_gelu(T, K, N, ncta):
     dt = torch.bfloat16
     torch.manual_seed(1)
     x = torch.randn(T, K, device=dev()).to(dt)
     W = (torch.randn(N, K, device=dev()) * 0.05).to(dt)
     b = torch.randn(N, device=dev()).to(dt)
     act, pre = torch.empty(T, N, device=dev(), dtype=dt), torch.empty(T, N, device=dev(), dtype=dt)
-    cu().linear_fwd(x, W, act, "bias_gelu", bias=b, pre_out=pre)
+    cu().linear_fwd(x, W, act, "bias_gelu", bias=b, pre_out=pre, ncta=ncta)
     f = x.float() @ W.float().t() + b.float()
     assert _rel(pre, f) < 1e-2
     want = torch.nn.functional.gelu(pre.float())          # GELU of the stored (rounded) pre-activation
     torch.testing.assert_close(act.float(), want, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("ncta", NCTA)
 @pytest.mark.parametrize("p", [0.0, 0.1])
 @pytest.mark.parametrize("T,K,N", [(1024, 768, 768), (8192, 3072, 768), (1000, 3072, 768), (90, 512, 128)])
-def test_linear_fwd_bias_dropout_resid_then_ln(T, K, N, p):
+def test_linear_fwd_bias_dropout_resid_then_ln(T, K, N, p, ncta):
     """The GEMM epilogue + the LayerNorm kernel equal the stand-alone bias+dropout+residual+LayerNorm op applied
     to the plain product, with the SAME dropout mask (the backward pass regenerates it from the element index)."""
     dt = torch.bfloat16
@@ -78,7 +83,7 @@ def test_linear_fwd_bias_dropout_resid_then_ln(T, K, N, p):
     res = torch.randn(T, N, device=dev()).to(dt)
     rng = _rng()
     pre = torch.empty(T, N, device=dev(), dtype=dt)
-    cu().linear_fwd(x, W, pre, "bias_dropout_resid", bias=b, resid=res, p=p, rng=rng, stream=11)
+    cu().linear_fwd(x, W, pre, "bias_dropout_resid", bias=b, resid=res, p=p, rng=rng, stream=11, ncta=ncta)
     prod = (x.float() @ W.float().t())
     yr, prer, mr, rr = ref.bias_dropout_add_ln_fwd(prod, b.float(), res.float(), gam.float(), bet.float(), 1e-12, p,
                                                    rng.seed, 11)
@@ -98,23 +103,25 @@ def test_linear_fwd_bias_dropout_resid_then_ln(T, K, N, p):
     torch.testing.assert_close(y.float(), want, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("ncta", NCTA)
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("T,N,K", [(1024, 768, 768), (8192, 2304, 768), (1000, 3072, 768), (8192, 768, 3072), (77, 512, 128)])
-def test_linear_dgrad_store_and_add(dt, T, N, K):
+def test_linear_dgrad_store_and_add(dt, T, N, K, ncta):
     torch.manual_seed(3)
     dy = torch.randn(T, N, device=dev()).to(dt)
     W = (torch.randn(N, K, device=dev()) * 0.05).to(dt)
     res = torch.randn(T, K, device=dev()).to(dt)
     want = dy.float() @ W.float()
     out = torch.empty(T, K, device=dev(), dtype=dt)
-    cu().linear_dgrad(dy, W, out)
+    cu().linear_dgrad(dy, W, out, ncta=ncta)
     assert _rel(out, want) < 1e-2
-    cu().linear_dgrad(dy, W, out, "add", resid=res)
+    cu().linear_dgrad(dy, W, out, "add", resid=res, ncta=ncta)
     assert _rel(out, want + res.float()) < 1e-2
 
 
+@pytest.mark.parametrize("ncta", NCTA)
 @pytest.mark.parametrize("T,N,K", [(1024, 768, 3072), (8192, 768, 3072), (300, 128, 512)])
-def test_linear_dgrad_gelu_bwd_with_bias_gradient(T, N, K):
+def test_linear_dgrad_gelu_bwd_with_bias_gradient(T, N, K, ncta):
     dt = torch.bfloat16
     torch.manual_seed(4)
     dy = torch.randn(T, N, device=dev()).to(dt)
@@ -122,7 +129,7 @@ def test_linear_dgrad_gelu_bwd_with_bias_gradient(T, N, K):
     f = torch.randn(T, K, device=dev()).to(dt)
     out = torch.empty(T, K, device=dev(), dtype=dt)
     dbias = torch.full((K,), 9.0, device=dev(), dtype=dt)
-    cu().linear_dgrad(dy, W, out, "gelu_bwd", pre=f, dbias=dbias)
+    cu().linear_dgrad(dy, W, out, "gelu_bwd", pre=f, dbias=dbias, ncta=ncta)
     ff = f.float().requires_grad_(True)
     torch.nn.functional.gelu(ff).backward(dy.float() @ W.float())
     want = ff.grad
@@ -132,7 +139,7 @@ def test_linear_dgrad_gelu_bwd_with_bias_gradient(T, N, K):
     plan = cu().DeferredColumns(dev(), dt)
     dbias2 = torch.zeros(K, device=dev(), dtype=dt)
     with cu().deferred_columns(plan):
-        cu().linear_dgrad(dy, W, out, "gelu_bwd", pre=f, dbias=dbias2)
+        cu().linear_dgrad(dy, W, out, "gelu_bwd", pre=f, dbias=dbias2, ncta=ncta)
     plan.finalize()
     torch.testing.assert_close(dbias2.float(), dbias.float(), rtol=1e-2, atol=1e-2 * (T ** 0.5))
 
@@ -140,14 +147,15 @@ def test_linear_dgrad_gelu_bwd_with_bias_gradient(T, N, K):
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("T,N,K", [(1024, 768, 768), (8192, 768, 768), (8192, 2304, 768), (1024, 3072, 768), (8192, 768, 3072),
                                    (1000, 768, 3072), (77, 128, 512), (4096, 64, 64)])
-def test_linear_wgrad_split_k(dt, T, N, K):
+@pytest.mark.parametrize("ncta", NCTA)
+def test_linear_wgrad_split_k(dt, T, N, K, ncta):
     torch.manual_seed(5)
     dy = (torch.randn(T, N, device=dev()) * 0.1).to(dt)
     x = torch.randn(T, K, device=dev()).to(dt)
     dW = torch.full((N, K), 3.0, device=dev(), dtype=dt)
     want = dy.float().t() @ x.float()
     for _ in range(2):           # the scratch and the counters are left zero: a second call gives the same result
-        cu().linear_wgrad(dy, x, dW)
+        cu().linear_wgrad(dy, x, dW, ncta=ncta)
         assert _rel(dW, want) < 1e-2
     sk = cu()._SK.get(0)
     if sk is not None and sk.buf is not None:

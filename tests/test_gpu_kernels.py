@@ -356,6 +356,55 @@ def test_trainer_step_on_gpu_tracks_cpu_reference():
         torch.testing.assert_close(sa[k].cpu(), sb[k], rtol=5e-3, atol=2e-4, msg=lambda m: f"{k}: {m}")
 
 
+@pytest.mark.parametrize("accum", [1, 2, 4])
+def test_trainer_on_tensor_core_path_tracks_cpu_fp32_trainer(accum):
+    """bf16 encoder on the own tcgen05 GEMMs + fp16 classifier on the tcgen05 classifier kernels (the benchmark's
+    path), three steps at dropout 0 with a partial final batch, against the CPU fp32 trainer; also with split
+    accumulation (label chunks), whose result must not depend on ``accum``."""
+    import numpy as np
+    from renee_b200.data import xcrepo
+    from renee_b200.data.collate import GlobalBatchSampler, PrefetchLoader, XCCollator
+    from renee_b200.data.synthetic import SyntheticSpec, SyntheticXC
+    from renee_b200.models.encoder import EncoderConfig
+    from renee_b200.parallel.dist import DistContext
+    from renee_b200.train import TrainConfig, XCTrainer
+    from renee_b200.utils.sharding import shard_labels
+
+    enc = EncoderConfig(vocab_size=30522, max_position_embeddings=32, dim=128, n_layers=2, n_heads=2,
+                        hidden_dim=512, dropout=0.0, attention_dropout=0.0)
+    L = 3000
+    spec = SyntheticSpec(num_labels=L, seq_len=16, len_lo=4, len_hi=16, poisson_lam=2.0, seed=0)
+    ids, mask, lab = SyntheticXC(spec).rows(np.arange(80))
+    ds = xcrepo.InMemoryDataset(ids, mask, lab)
+    sh = shard_labels(L, 1)
+
+    def make(device, **kw):
+        cfg = TrainConfig(batch_size=32, epochs=1, seed=0, dropout=0.0, lr1=0.05, lr2=1e-5, warmup=1, wd1=1e-3,
+                          maxlen=16, noloss=True, accum=accum, stochastic_round=False, **kw)
+        loader = PrefetchLoader(GlobalBatchSampler(80, 32, True, 0),
+                                XCCollator(sh, ds, 0, accum, max(1, 32 // accum), True))
+        return XCTrainer(cfg, enc, sh, DistContext(device=torch.device(device)), steps_per_epoch=3), loader
+
+    a, la = make("cuda:0", fp16xfc=True)                       # bf16 encoder, fp16 W + momentum
+    b, lb = make("cpu", fp32encoder=True, fp16xfc=False)
+    assert a.encoder.own_gemm and a.xfc.dtype == torch.float16
+    assert a.xfc.chunk <= (a.Ls + accum - 1) // accum + 127     # Gt scratch is B x Ls/accum at 128-label granularity
+    b.load_state_dict({k: v.cpu() for k, v in a.state_dict().items()})
+    w0 = a.state_dict()["xfc_weight"].cpu()
+    for ba, bb in zip(la.epoch(0), lb.epoch(0)):               # 32 + 32 + 16 rows
+        a.train_step(ba)
+        b.train_step(bb)
+    torch.cuda.synchronize()
+    cu().check_status()
+    sa, sb = a.state_dict(), b.state_dict()
+    moved = (sb["xfc_weight"] - w0).abs().max()
+    err = (sa["xfc_weight"].cpu() - sb["xfc_weight"]).abs().max()
+    assert moved > 1e-2 and err < 0.05 * moved + 1e-3, (float(err), float(moved))
+    for k in sa:
+        if k != "xfc_weight":
+            torch.testing.assert_close(sa[k].cpu(), sb[k], rtol=1e-2, atol=1e-4, msg=lambda m: f"{k}: {m}")
+
+
 def test_xfc_dw_sgd_both_kernels_agree_and_stochastic_rounding_is_unbiased():
     B, D, Lc = 128, 768, 512
     X, W, rows, labels = _xfc_problem(B, D, Lc, 200)

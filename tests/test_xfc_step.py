@@ -85,3 +85,36 @@ def test_topk_chunked_equals_full():
     v, i = xfc.topk(X, 7)
     vr, ir = torch.topk(X @ xfc.W.t(), 7, dim=1)
     torch.testing.assert_close(v, vr); assert torch.equal(i, ir)
+
+
+def test_fp16_weight_storage_drift_against_fp32_masters_late_in_the_schedule():
+    """fp16 storage of W and momentum vs the reference's fp32 masters (dl_base.py:185, 562) over 400 steps at
+    a learning rate typical of the end of the cosine schedule, where an update lr*M is far below half an fp16
+    ulp of W (|W| ~ 0.03: ulp 1.5e-5).  Round-to-nearest loses most of the update; stochastic rounding (the
+    default, same arithmetic as the dW kernel's epilogue) follows the fp32 trajectory in expectation."""
+    torch.manual_seed(0)
+    Ls, D, B, steps = 256, 64, 32, 400
+    lr, mo, wd = 2e-5, 0.9, 1e-4
+    W0 = (torch.randn(Ls, D) * 0.03)
+    W32, M32 = W0.clone(), torch.zeros(Ls, D)
+    Wrn, Mrn = W0.half(), torch.zeros(Ls, D, dtype=torch.float16)
+    Wsr, Msr = W0.half(), torch.zeros(Ls, D, dtype=torch.float16)
+    start = Wrn.float().clone()
+    for t in range(steps):
+        X = torch.randn(B, D).abs() * 0.5                      # one-signed features: every weight drifts one way
+        Gt = (torch.rand(Ls, B) * 0.02)                       # sigmoid(z) - y of mostly-negative labels: small, one-signed
+        Gt[torch.randint(0, Ls, (8,)), torch.randint(0, B, (8,))] -= 1.0
+        ref.xfc_dw_sgd(Gt, X, W32, M32, lr, mo, wd)
+        ref.xfc_dw_sgd(Gt.half(), X.half(), Wrn, Mrn, lr, mo, wd)
+        ref.xfc_dw_sgd(Gt.half(), X.half(), Wsr, Msr, lr, mo, wd, sr_seed=1000 + t)
+    moved = (W32 - start).abs().mean()                        # how far fp32 masters travelled
+    err_rn = (Wrn.float() - W32).abs().mean()
+    err_sr = (Wsr.float() - W32).abs().mean()
+    # stochastic rounding stays within rounding noise of the fp32 trajectory; round-to-nearest falls behind by a
+    # large part of the distance travelled
+    assert err_sr < 0.35 * moved, (float(err_sr), float(moved))
+    assert err_rn > 1.3 * err_sr, (float(err_rn), float(err_sr))
+    # and the MEAN displacement (what matters for tail labels) is kept by SR, largely lost by RN
+    d32, drn, dsr = (W32 - start).mean(), (Wrn.float() - start).mean(), (Wsr.float() - start).mean()
+    assert abs(dsr - d32) < 0.2 * abs(d32)
+    assert abs(drn - d32) > 3.0 * abs(dsr - d32)
