@@ -117,9 +117,17 @@ class FlatEncoder:
         self._plan = None
         self.generation = 0
         self.own_gemm = False
+        self._wgrad_stream = None
         if self.device.type == "cuda" and act_dtype != torch.float32:
+            import os
             from ..ops import cuda as cu
             self.own_gemm = cu.enc_gemm_supported(self.p16, H, Fd)
+            if self.own_gemm and os.environ.get("RENEE_B200_WGRAD_STREAM", "1") != "0":
+                # weight-gradient GEMMs are off the critical path of the backward pass (nothing reads them before
+                # the optimizer): they run on a second stream, where they fill the SMs that the data-gradient
+                # GEMMs' last partial wave of tiles leaves idle (and, at small token counts, the SMs those GEMMs
+                # never use).  Captured into the step's CUDA graph as parallel branches.
+                self._wgrad_stream = torch.cuda.Stream(device=self.device)
 
     # ------------------------------------------------------------------ parameter views
     def view(self, buf: torch.Tensor, name: str) -> torch.Tensor:
@@ -302,6 +310,22 @@ class FlatEncoder:
         else:
             self._backward(d_emb, on_layer_done)
 
+    def _wgrad(self, dy, x, dW) -> None:
+        """``dW = dy^T x`` on the weight-gradient stream (ordered after everything issued so far on the current one)."""
+        from ..ops import cuda as cu
+        side = self._wgrad_stream
+        if side is None:
+            cu.linear_wgrad(dy, x, dW)
+            return
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            cu.linear_wgrad(dy, x, dW)
+
+    def _wgrad_join(self) -> None:
+        """The current stream waits for the weight-gradient GEMMs issued so far (their inputs may be overwritten next)."""
+        if self._wgrad_stream is not None:
+            torch.cuda.current_stream().wait_stream(self._wgrad_stream)
+
     def _backward(self, d_emb: torch.Tensor, on_layer_done=None) -> None:
         cfg, A, fw = self.cfg, self._acts, self._fw
         b, S, pd, pa, rng = fw["b"], fw["S"], fw["pd"], fw["pa"], fw["rng"]
@@ -333,25 +357,29 @@ class FlatEncoder:
                 self.view(G, pre + "ffn.lin2.bias"), A["dh_b"][:T], L["f2"][:T])
             if self.own_gemm:
                 from ..ops import cuda as cu
-                cu.linear_wgrad(d_f2, L["a1"][:T], self.view(G, pre + "ffn.lin2.weight"))
+                self._wgrad(d_f2, L["a1"][:T], self.view(G, pre + "ffn.lin2.weight"))
                 df1 = A["df1"][:T]
                 cu.linear_dgrad(d_f2, self.view(P, pre + "ffn.lin2.weight"), df1, "gelu_bwd", pre=L["f1"][:T],
                                 dbias=self.view(G, pre + "ffn.lin1.bias"))
-                cu.linear_wgrad(df1, L["h1"][:T], self.view(G, pre + "ffn.lin1.weight"))
+                self._wgrad(df1, L["h1"][:T], self.view(G, pre + "ffn.lin1.weight"))
                 dh1 = cu.linear_dgrad(df1, self.view(P, pre + "ffn.lin1.weight"), dh, "add", resid=d_pre2)
+                if d_f2 is d_pre2:
+                    self._wgrad_join()      # without dropout d_f2 is the shared buffer the next kernel overwrites
                 d_pre1, d_ao = ops.bias_dropout_add_ln_bwd(
                     dh1, L["pre1"][:T], self.view(P, pre + "sa_layer_norm.weight"), L["mean1"][:T], L["rstd1"][:T],
                     fw["po"], rng, sb + _S_ATTN,
                     self.view(G, pre + "sa_layer_norm.weight"), self.view(G, pre + "sa_layer_norm.bias"),
                     self.view(G, pre + "attention.out_lin.bias"), A["dh_b"][:T], L["ao"][:T])
-                cu.linear_wgrad(d_ao, L["ctx"][:T], self.view(G, pre + "attention.out_lin.weight"))
+                self._wgrad(d_ao, L["ctx"][:T], self.view(G, pre + "attention.out_lin.weight"))
                 dctx = A["dctx"][:T]
                 cu.linear_dgrad(d_ao, self.view(P, pre + "attention.out_lin.weight"), dctx)
                 dqkv = A["dqkv"][:T]
                 ops.attention_bwd(dctx, L["qkv"][:T], self._qkv(P, l, "bias"), mask, cfg.n_heads, pa, rng,
                                   sb + _S_PROBS, L["att"], dqkv, self._qkv(G, l, "bias"))
-                cu.linear_wgrad(dqkv, h_in, self._qkv(G, l, "weight"))
+                self._wgrad(dqkv, h_in, self._qkv(G, l, "weight"))
                 cu.linear_dgrad(dqkv, self._qkv(P, l, "weight"), dh, "add", resid=d_pre1)
+                # the next layer overwrites the shared gradient buffers (dh_b, df1, dqkv) the GEMMs above read
+                self._wgrad_join()
                 if on_layer_done is not None:
                     on_layer_done(l)
                 continue

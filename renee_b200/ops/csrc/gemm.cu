@@ -42,21 +42,19 @@ constexpr int BM = 128;                         // accumulator rows per CTA
 constexpr int BK = 64;
 constexpr int A_BYTES = BM * BK * 2;            // 16 KB
 constexpr int PANEL_BYTES = BM * 64 * 2;        // one staging panel: 128 rows x 64 x 16 bit
-constexpr int N_PANELS = 4;                     // two per epilogue group
+constexpr int N_PANELS = 2;                     // one per epilogue group
 constexpr int THREADS = 320;
 constexpr int ACC_BUFS = 2;
 constexpr int ACC_STRIDE = 256;                 // TMEM columns between the two accumulators
 constexpr int TMEM_COLS = ACC_BUFS * ACC_STRIDE;
-constexpr int kPrefetch = 8;                    // k blocks between the L2 prefetch of a tile and its load
 
-// Shared memory: the operand ring plus, for epilogues that stage tiles, four panels.  The main loop is bound by
-// load latency over the bytes in flight, so the split-K epilogue (no panels) gets the deeper ring.
-template <int NCTA, bool STAGED> struct Cfg {
-  static constexpr int kBMax = (NCTA == 1 ? 256 : 128) * BK * 2;        // B bytes per stage and CTA, at most
-  static constexpr int kStage = A_BYTES + kBMax;                        // 48 KB / 32 KB
-  static constexpr int kStages = NCTA == 1 ? (STAGED ? 3 : 4) : (STAGED ? 4 : 6);
+// Shared memory: the operand ring plus, for epilogues that stage tiles, one panel per epilogue group.  The main
+// loop is bound by load latency over the bytes in flight, so the ring takes everything else (192 KB).
+constexpr int RING_BYTES = 192 * 1024;          // operand bytes in flight per CTA
+constexpr int MAX_STAGES = 8;                   // a stage is 16 KB of A + BN / NCTA rows of B: 24 KB (8 stages) .. 48 KB (4)
+template <bool STAGED> struct Cfg {
   static constexpr int kPanels = STAGED ? N_PANELS : 0;
-  static constexpr int kSmem = kStages * kStage + kPanels * PANEL_BYTES + 1024 + 512;
+  static constexpr int kSmem = RING_BYTES + kPanels * PANEL_BYTES + 1024 + 512;
 };
 
 enum Layout : int { L_NT = 0, L_NN = 1, L_TN = 2 };
@@ -72,7 +70,6 @@ struct Params {
   float p; const int* seed; uint32_t stream;        // dropout      BIAS_DROPOUT_RESID
   float* colacc; int col_tot; int col_off;          // GELU_BWD: replicas of [col_tot] floats, this vector at col_off
   float* sk_scratch; unsigned* sk_counters;         // SPLITK: [tiles][128 NCTA x BN] fp32 (zero between launches), [tiles]
-  int prefetch;                  // request operand tiles into L2 kPrefetch k blocks ahead of their load
   int* status;
 };
 
@@ -114,22 +111,20 @@ __global__ void __launch_bounds__(THREADS, 1)
 enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
                 const __grid_constant__ CUtensorMap tmF, const Params p) {
-  using C_ = Cfg<NCTA, EPI != E_SPLITK>;
+  using C_ = Cfg<EPI != E_SPLITK>;
   constexpr bool A_MN = (LAYOUT == L_TN);
   constexpr bool B_MN = (LAYOUT != L_NT);
   constexpr int FMT = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
-  constexpr int STAGES = C_::kStages;
-  constexpr int STAGE = C_::kStage;
   constexpr bool HAS_IN = (EPI == E_BIAS_DROPOUT_RESID || EPI == E_ADD || EPI == E_GELU_BWD);   // tile-shaped input R
   constexpr bool STAGED = (EPI != E_SPLITK);                                                     // outputs through panels
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* panels = smem + STAGES * STAGE;                       // [N_PANELS][PANEL_BYTES], 1024-byte aligned
+  uint8_t* panels = smem + RING_BYTES;                           // [N_PANELS][PANEL_BYTES], 1024-byte aligned
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(panels + C_::kPanels * PANEL_BYTES);
-  uint64_t* empty_bar = full_bar + STAGES;
-  uint64_t* tmem_full_bar = empty_bar + STAGES;          // [ACC_BUFS]
+  uint64_t* empty_bar = full_bar + MAX_STAGES;
+  uint64_t* tmem_full_bar = empty_bar + MAX_STAGES;      // [ACC_BUFS]
   uint64_t* tmem_empty_bar = tmem_full_bar + ACC_BUFS;   // [ACC_BUFS]  (used in the leader CTA)
-  uint64_t* in_bar = tmem_empty_bar + ACC_BUFS;          // [N_PANELS]  R panel has landed
+  uint64_t* in_bar = tmem_empty_bar + ACC_BUFS;          // [N_PANELS]  a group's R panel has landed
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(in_bar + N_PANELS);
   volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
   volatile int* s_last = s_abort + 1;
@@ -141,7 +136,9 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   const int n_units = NCTA == 2 ? (int)(gridDim.x >> 1) : (int)gridDim.x;
   const int n_items = p.n_m_tiles * p.n_n_tiles * p.splits;
   const int b_rows = p.BN / NCTA;                                                 // B rows (N index) this CTA loads
-  const uint32_t stage_tx = (uint32_t)NCTA * (A_BYTES + (uint32_t)b_rows * BK * 2);
+  const int STAGE = A_BYTES + b_rows * BK * 2;                                    // 24, 32 or 48 KB
+  const int STAGES = min(MAX_STAGES, RING_BYTES / STAGE);
+  const uint32_t stage_tx = (uint32_t)NCTA * (uint32_t)STAGE;
 
   if (threadIdx.x == 0) {
     tc::prefetch_tmap(&tmA);
@@ -149,7 +146,7 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     if (STAGED) tc::prefetch_tmap(&tmC);
     if (HAS_IN) tc::prefetch_tmap(&tmR);
     if (EPI == E_BIAS_GELU) tc::prefetch_tmap(&tmF);
-    for (int s = 0; s < STAGES; ++s) { tc::mbar_init(full_bar + s, 1); tc::mbar_init(empty_bar + s, 1); }
+    for (int s = 0; s < MAX_STAGES; ++s) { tc::mbar_init(full_bar + s, 1); tc::mbar_init(empty_bar + s, 1); }
     for (int a = 0; a < ACC_BUFS; ++a) { tc::mbar_init(tmem_full_bar + a, 1); tc::mbar_init(tmem_empty_bar + a, 8 * NCTA); }
     for (int a = 0; a < N_PANELS; ++a) tc::mbar_init(in_bar + a, 1);
     *s_abort = 0;
@@ -168,25 +165,14 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
   if (warp == 0 && lane == 0) {
     // ---------------- TMA producer: one continuous stream of (item, k block) stages
-    int it = 0;
+    int s = 0;
+    uint32_t ph = 0;
     for (int item = unit; item < n_items && !aborted; item += n_units) {
       const int tile = item / p.splits, split = item - tile * p.splits;
       const int m0 = (tile / p.n_n_tiles) * (BM * NCTA) + (int)rank * BM;
       const int n0 = (tile % p.n_n_tiles) * p.BN + (int)rank * b_rows;
       const int kb0 = split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
-      for (int kb = kb0; kb < kb1; ++kb, ++it) {
-        const int s = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1;
-        // operand tiles that are not in L2 (weights, activations saved by the forward pass) cost a DRAM round
-        // trip each; the ring holds only 3-4 stages, so the tiles of k block kb + kPrefetch are requested into
-        // L2 now (no shared memory involved)
-        if (p.prefetch && kb + kPrefetch < kb1) {
-          const int kp = (kb + kPrefetch) * BK;
-          if (A_MN) { tc::tma_prefetch_2d(&tmA, m0, kp); tc::tma_prefetch_2d(&tmA, m0 + 64, kp); }
-          else tc::tma_prefetch_2d(&tmA, kp, m0);
-          if (B_MN) { for (int i = 0; i < b_rows / 64; ++i) tc::tma_prefetch_2d(&tmB, n0 + 64 * i, kp); }
-          else tc::tma_prefetch_2d(&tmB, kp, n0);
-        }
+      for (int kb = kb0; kb < kb1; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
         if (!tc::mbar_wait(empty_bar + s, ph ^ 1, aborted, p.status, tc::SITE_EMPTY, kb)) break;
         uint8_t* sA = smem + s * STAGE;
         uint8_t* sB = sA + A_BYTES;
@@ -224,7 +210,8 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   } else if (warp == 1 && lane == 0 && rank == 0) {
     // ---------------- MMA issuer (leader CTA): accumulator (t_local & 1), reused once the epilogue(s) drained it
     const uint32_t idesc = tc::make_idesc(FMT, A_MN ? 1 : 0, B_MN ? 1 : 0, BM * NCTA, p.BN);
-    int it = 0, t_local = 0;
+    int s = 0, t_local = 0;
+    uint32_t ph = 0;
     for (int item = unit; item < n_items && !aborted; item += n_units, ++t_local) {
       const int tile = item / p.splits, split = item - tile * p.splits;
       const int kb0 = split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
@@ -233,9 +220,7 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if (!tc::mbar_wait(tmem_empty_bar + buf, (use & 1) ^ 1, aborted, p.status, tc::SITE_TMEM_EMPTY, item)) break;
       tc::tc_fence_after();
       const uint32_t d_tmem = tmem_base + (uint32_t)buf * ACC_STRIDE;
-      for (int kb = kb0; kb < kb1; ++kb, ++it) {
-        const int s = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1;
+      for (int kb = kb0; kb < kb1; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
         if (!tc::mbar_wait(full_bar + s, ph, aborted, p.status, tc::SITE_FULL, kb)) break;
         tc::tc_fence_after();
         const uint32_t sA = tc::smem_u32(smem + s * STAGE);
@@ -262,12 +247,13 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int g_col = half_cols >= 64 ? g * half_cols : 0;
     const int bar_id = 2 + g;                             // named barrier of this group (128 threads)
     const bool elected = (warp == 2 + 4 * g) && lane == 0;                   // first warp of the group, lane 0
-    uint8_t* my_panels = panels + g * 2 * PANEL_BYTES;
-    uint64_t* my_in_bar = in_bar + g * 2;
+    uint8_t* pan = panels + g * PANEL_BYTES;              // this group's staging panel
+    uint64_t* my_in_bar = in_bar + g;
     uint32_t seed = 0u;
     float inv_keep = 1.f;
     if (EPI == E_BIAS_DROPOUT_RESID && p.p > 0.f) { seed = (uint32_t)(*p.seed); inv_keep = 1.f / (1.f - p.p); }
-    int t_local = 0, pan_count = 0;
+    int t_local = 0;
+    uint32_t in_count = 0;                                // R panels fetched so far (parity of my_in_bar)
     for (int item = unit; item < n_items; item += n_units, ++t_local) {
       const int tile = item / p.splits;
       const int m0 = (tile / p.n_n_tiles) * (BM * NCTA) + (int)rank * BM;
@@ -275,14 +261,12 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const int row = m0 + r;
       const int buf = t_local & 1;
       const uint32_t use = (uint32_t)(t_local >> 1);
-      if (HAS_IN && elected) {
-        // fetch this tile's R panels while its main loop runs; the panels are free once the previous item's
-        // stores have read them
+      if (HAS_IN && elected && n_pan > 0) {
+        // fetch the tile's first R panel while its main loop still runs; the panel is free once the stores
+        // issued from it have read it
         tc::tma_store_wait_read<0>();
-        for (int pi = 0; pi < n_pan; ++pi) {
-          tc::mbar_expect_tx(my_in_bar + pi, PANEL_BYTES);
-          tc::tma_load_2d(my_panels + pi * PANEL_BYTES, &tmR, my_in_bar + pi, n0 + g_col + 64 * pi, m0);
-        }
+        tc::mbar_expect_tx(my_in_bar, PANEL_BYTES);
+        tc::tma_load_2d(pan, &tmR, my_in_bar, n0 + g_col, m0);
       }
       if (!tc::mbar_wait(tmem_full_bar + buf, use & 1, aborted, p.status, tc::SITE_TMEM_FULL, item)) *s_abort = 1;
       asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -290,36 +274,39 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       tc::tc_fence_after();
       const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * ACC_STRIDE + (uint32_t)g_col;
       if (STAGED) {
-        for (int pi = 0; pi < n_pan; ++pi, ++pan_count) {
+        for (int pi = 0; pi < n_pan; ++pi) {
           const int pcol = n0 + g_col + 64 * pi;             // first column of the panel
-          // staging buffer(s): R panels are updated in place; a two-output epilogue fills both buffers per
-          // panel; a one-output epilogue alternates between them
-          uint8_t* pan = my_panels + (HAS_IN ? pi : (EPI == E_BIAS_GELU ? 0 : (pan_count & 1))) * PANEL_BYTES;
-          uint8_t* pan2 = my_panels + PANEL_BYTES;           // BIAS_GELU: the activation panel
+          // the accumulator fragments of the panel: 64 columns of this thread's row
+          float v[2][32];
+          tc::tmem_ld32(tbase + 64 * pi, v[0]);
+          tc::tmem_ld32(tbase + 64 * pi + 32, v[1]);
           if (HAS_IN) {
-            if (!tc::mbar_wait(my_in_bar + pi, (uint32_t)t_local & 1, aborted, p.status, tc::SITE_FULL, 2000 + pi)) *s_abort = 1;
+            if (pi > 0 && elected) {                         // later panels: fetched once the previous store has read the buffer
+              tc::tma_store_wait_read<0>();
+              tc::mbar_expect_tx(my_in_bar, PANEL_BYTES);
+              tc::tma_load_2d(pan, &tmR, my_in_bar, pcol, m0);
+            }
+            if (!tc::mbar_wait(my_in_bar, in_count & 1, aborted, p.status, tc::SITE_FULL, 2000 + pi)) *s_abort = 1;
+            ++in_count;
           } else {
-            // the buffer is free once the store issued from it earlier has read it
-            if (elected) { if (EPI == E_BIAS_GELU) tc::tma_store_wait_read<0>(); else tc::tma_store_wait_read<1>(); }
+            if (elected) tc::tma_store_wait_read<0>();       // the buffer is free once the previous store has read it
             asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
           }
           float colsum[2] = {0.f, 0.f};
 #pragma unroll
           for (int hc = 0; hc < 2; ++hc) {                   // two 32-column fragments per panel
-            float v[32];
-            tc::tmem_ld32(tbase + 64 * pi + 32 * hc, v);
 #pragma unroll
             for (int j8 = 0; j8 < 4; ++j8) {
               const int chunk = 4 * hc + j8;
               const int c = pcol + 8 * chunk;
-              const uint32_t off = panel_off(r, chunk);
-              uint4* slot = reinterpret_cast<uint4*>(pan + off);
+              uint4* slot = reinterpret_cast<uint4*>(pan + panel_off(r, chunk));
+              float* a = &v[hc][8 * j8];
               float o[8];
               if (EPI == E_STORE) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) o[j] = v[8 * j8 + j];
+                for (int j = 0; j < 8; ++j) o[j] = a[j];
               } else if (EPI == E_BIAS_GELU) {
-                float b[8], a[8];
+                float b[8];
                 if (c < p.N) unpack8<T>(__ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.bias) + c)), b);
                 else {
 #pragma unroll
@@ -327,10 +314,9 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                  o[j] = round_through<T>(v[8 * j8 + j] + b[j]);     // the backward pass differentiates at the stored value
-                  a[j] = gelu_f(o[j]);
+                  o[j] = round_through<T>(a[j] + b[j]);      // the backward pass differentiates at the stored value
+                  a[j] = gelu_f(o[j]);                       // second output, staged after the first has left
                 }
-                *reinterpret_cast<uint4*>(pan2 + off) = pack8<T>(a);
               } else if (EPI == E_BIAS_DROPOUT_RESID) {
                 float b[8], res[8];
                 if (c < p.N) unpack8<T>(__ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.bias) + c)), b);
@@ -341,7 +327,7 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 unpack8<T>(*slot, res);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                  float t = v[8 * j8 + j] + b[j];
+                  float t = a[j] + b[j];
                   if (p.p > 0.f) t = keep(seed, p.stream, (uint32_t)(row * p.N + c + j), p.p) ? t * inv_keep : 0.f;
                   o[j] = res[j] + t;
                 }
@@ -349,19 +335,19 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 float res[8];
                 unpack8<T>(*slot, res);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) o[j] = v[8 * j8 + j] + res[j];
+                for (int j = 0; j < 8; ++j) o[j] = a[j] + res[j];
               } else {   // E_GELU_BWD: rows past M read F = 0 and a zero accumulator, so they add nothing to the sums
                 float f[8];
                 unpack8<T>(*slot, f);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                  o[j] = round_through<T>(v[8 * j8 + j] * gelu_grad_f(f[j]));
-                  v[8 * j8 + j] = o[j];
+                  o[j] = round_through<T>(a[j] * gelu_grad_f(f[j]));
+                  a[j] = o[j];
                 }
               }
               *slot = pack8<T>(o);
             }
-            if (EPI == E_GELU_BWD && p.colacc != nullptr) colsum[hc] = warp_colsum32(v, lane);
+            if (EPI == E_GELU_BWD && p.colacc != nullptr) colsum[hc] = warp_colsum32(v[hc], lane);
           }
           if (EPI == E_GELU_BWD && p.colacc != nullptr) {
 #pragma unroll
@@ -373,13 +359,24 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           tc::fence_proxy_async();                 // generic-proxy writes of the panel before the async-proxy store
           asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
           if (elected) {
-            if (EPI == E_BIAS_GELU) {
-              tc::tma_store_2d(&tmF, pan, pcol, m0);
-              tc::tma_store_2d(&tmC, pan2, pcol, m0);
-            } else {
-              tc::tma_store_2d(&tmC, pan, pcol, m0);
-            }
+            tc::tma_store_2d(EPI == E_BIAS_GELU ? &tmF : &tmC, pan, pcol, m0);
             tc::tma_store_commit();
+          }
+          if (EPI == E_BIAS_GELU) {
+            // second output through the same panel: C = gelu(F), held in the fragment registers
+            if (elected) tc::tma_store_wait_read<0>();
+            asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+#pragma unroll
+            for (int hc = 0; hc < 2; ++hc)
+#pragma unroll
+              for (int j8 = 0; j8 < 4; ++j8)
+                *reinterpret_cast<uint4*>(pan + panel_off(r, 4 * hc + j8)) = pack8<T>(&v[hc][8 * j8]);
+            tc::fence_proxy_async();
+            asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+            if (elected) {
+              tc::tma_store_2d(&tmC, pan, pcol, m0);
+              tc::tma_store_commit();
+            }
           }
         }
       }
@@ -533,7 +530,7 @@ template <typename T, int LAYOUT, int EPI, int NCTA>
 static int launch_enc_gemm(const Maps& m, const Params& p, int units, cudaStream_t st) {
   static bool attr_set = false;
   auto k = enc_gemm_kernel<T, LAYOUT, EPI, NCTA>;
-  constexpr int smem = Cfg<NCTA, EPI != E_SPLITK>::kSmem;
+  constexpr int smem = Cfg<EPI != E_SPLITK>::kSmem;
   if (!attr_set) {
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -5;
     attr_set = true;
@@ -574,15 +571,24 @@ static int dispatch_enc_gemm(int layout, int epi, const Maps& m, const Params& p
   return -4;
 }
 
-// Tile shape and K-splits.  The kernel is bound by operand fetch: an SM sustains about one 128-byte operand row
-// per 3.3 clocks, a k block of a CTA costs max(rows fetched x 3.3, MMA clocks = 2 BN) clocks, and the work is
-// spread over the units (SMs, or SM pairs) in rounds.  Candidates: (NCTA, BN) with NCTA in {1, 2}.
+// Tile shape and K-splits from a cost model calibrated on B200 (clocks per CTA):
+//   * a k block costs max(MMA time = 2 BN, operand bytes of the CTA / fetch rate); with every SM busy an SM sustains
+//     about 29 bytes per clock from L2 (the L2-to-SM fabric, about 8 TB/s in total, is the shared limit), with
+//     fewer SMs busy proportionally more, down to a floor of about 3900 clocks of load latency divided by the
+//     number of ring stages (192 KB / stage size: 4 to 8);
+//   * work is spread over the units (SMs, or SM pairs) in rounds;
+//   * about 3000 clocks of start-up per kernel (TMEM allocation, barrier set-up, first load);
+//   * the epilogue of a CTA's last tile is exposed: per 64-column panel about 1200 clocks (store), 2400 (two
+//     outputs), 2800 (a tile-shaped input fetched after the previous panel has left; the first panel's input is
+//     fetched under the main loop);
+//   * a K-split costs about 10000 clocks (partial sums through L2 atomics, the last CTA's conversion pass).
 struct Plan { int ncta, bn, splits, tiles; };
 
-static int g_prefetch = 0;
-RB_API void rb_enc_gemm_set_prefetch(int on) { g_prefetch = on ? 1 : 0; }
+static int g_max_units = 0;
+// Experiments: cap the number of persistent workers (0 = one per SM / SM pair).
+RB_API void rb_enc_gemm_set_max_units(int n) { g_max_units = n; }
 
-static Plan make_plan(int layout, int M, int N, int K, int bn_forced, int ncta_forced) {
+static Plan make_plan(int layout, int epi, int M, int N, int K, int bn_forced, int ncta_forced) {
   const int sms = sm_count();
   const int kb = (K + BK - 1) / BK;
   Plan best{1, 128, 1, 1};
@@ -595,20 +601,28 @@ static Plan make_plan(int layout, int M, int N, int K, int bn_forced, int ncta_f
       if (!bn_forced && bn > 64 && bn / 2 >= N) continue;            // a narrower tile already covers every column
       const int tiles = ((M + BM * ncta - 1) / (BM * ncta)) * ((N + bn - 1) / bn);
       const int units = sms / ncta;
-      int splits = 1;
-      if (layout == L_TN) {
-        splits = units / tiles;
-        if (splits < 1) splits = 1;
-        if (splits > 16) splits = 16;
-        if (splits > kb) splits = kb;
+      const int max_splits = layout == L_TN ? (kb < 16 ? kb : 16) : 1;
+      for (int splits = 1; splits <= max_splits; splits *= 2) {
+        const int kb_per = (kb + splits - 1) / splits;
+        const int eff_splits = (kb + kb_per - 1) / kb_per;
+        if (eff_splits != splits && splits > 1) continue;
+        const long items = (long)tiles * eff_splits;
+        const long rounds = (items + units - 1) / units;
+        const double busy = (double)(items < units ? items : units) * ncta / sms;      // fraction of the SMs at work
+        const double bytes = A_BYTES + (double)(bn / ncta) * BK * 2;
+        double t_kb = bytes / (29.0 / (busy > 0.25 ? busy : 0.25));
+        const int stages = (int)(RING_BYTES / bytes) < MAX_STAGES ? (int)(RING_BYTES / bytes) : MAX_STAGES;
+        if (t_kb < 3900.0 / stages) t_kb = 3900.0 / stages;          // load latency over the ring depth
+        if (t_kb < 2.0 * bn) t_kb = 2.0 * bn;
+        const int n_pan = bn >= 128 ? bn / 128 : 1;
+        double tail;
+        if (epi == E_SPLITK) tail = 800.0 * n_pan;
+        else if (epi == E_STORE) tail = 1200.0 * n_pan;
+        else if (epi == E_BIAS_GELU) tail = 2400.0 * n_pan;
+        else tail = 1200.0 + 2800.0 * (n_pan - 1);
+        const double cost = 3000.0 + rounds * (kb_per * t_kb) + tail + (eff_splits > 1 ? 10000.0 : 0.0);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = Plan{ncta, bn, eff_splits, tiles}; }
       }
-      const int kb_per = (kb + splits - 1) / splits;
-      splits = (kb + kb_per - 1) / kb_per;
-      const long items = (long)tiles * splits;
-      const long rounds = (items + units - 1) / units;
-      const double fetch = (128.0 + bn / ncta) * 3.3, mma = 2.0 * bn;
-      const double cost = rounds * (kb_per * (fetch > mma ? fetch : mma) + 1500.0 + (splits > 1 ? 6.0 * bn : 0.0));
-      if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = Plan{ncta, bn, splits, tiles}; }
     }
   }
   return best;
@@ -616,9 +630,9 @@ static Plan make_plan(int layout, int M, int N, int K, int bn_forced, int ncta_f
 
 // What rb_enc_gemm will use for (M, N, K): tile shape, K-splits for layout TN, and the sizes of the split-K
 // scratch (floats) and counters (words) it needs when splits > 1.
-RB_API int rb_enc_gemm_plan(int layout, int M, int N, int K, int bn_forced, int ncta_forced, int* ncta_out, int* bn_out,
-                            int* splits_out, long long* scratch_floats, int* counter_words) {
-  const Plan pl = make_plan(layout, M, N, K, bn_forced, ncta_forced);
+RB_API int rb_enc_gemm_plan(int layout, int epi, int M, int N, int K, int bn_forced, int ncta_forced, int* ncta_out,
+                            int* bn_out, int* splits_out, long long* scratch_floats, int* counter_words) {
+  const Plan pl = make_plan(layout, epi, M, N, K, bn_forced, ncta_forced);
   *ncta_out = pl.ncta; *bn_out = pl.bn; *splits_out = pl.splits;
   *scratch_floats = (long long)pl.tiles * BM * pl.ncta * pl.bn;
   *counter_words = pl.tiles * pl.ncta;
@@ -644,7 +658,7 @@ RB_API int rb_enc_gemm(int dtype, int layout, int epi, const void* A, const void
   if (epi == E_BIAS_GELU && F == nullptr) return -3;
   if (epi == E_BIAS_DROPOUT_RESID && p_drop > 0.f && seed == nullptr) return -3;
   const bool bf16 = dtype == RB_BF16;
-  const Plan pl = make_plan(layout, M, N, K, bn_forced, ncta_forced);
+  const Plan pl = make_plan(layout, epi, M, N, K, bn_forced, ncta_forced);
   const int BN = pl.bn, b_rows = BN / pl.ncta;
   Maps m;
   int rc;
@@ -672,9 +686,9 @@ RB_API int rb_enc_gemm(int dtype, int layout, int epi, const void* A, const void
   p.p = p_drop; p.seed = seed; p.stream = stream_id;
   p.colacc = colacc; p.col_tot = col_tot; p.col_off = col_off;
   p.sk_scratch = sk_scratch; p.sk_counters = sk_counters; p.status = status;
-  p.prefetch = g_prefetch;
   const int n_items = p.n_m_tiles * p.n_n_tiles * p.splits;
-  const int max_units = sm_count() / pl.ncta;
+  int max_units = sm_count() / pl.ncta;
+  if (g_max_units > 0 && g_max_units < max_units) max_units = g_max_units;
   const int units = n_items < max_units ? n_items : max_units;
   if (pl.ncta == 2)
     rc = bf16 ? dispatch_enc_gemm<__nv_bfloat16, 2>(layout, epi, m, p, units, st) : dispatch_enc_gemm<__half, 2>(layout, epi, m, p, units, st);

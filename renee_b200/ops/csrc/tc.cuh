@@ -77,13 +77,6 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* t
       : "memory");
 }
 
-// Request a tile into L2 only (no destination in shared memory, no completion to wait for).
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* tmap, int x, int y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
-               ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y)
-               : "memory");
-}
-
 // Tile store shared -> global (bulk async group); out-of-range parts of the box are clipped.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, const void* smem_src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"

@@ -43,8 +43,8 @@ def _load():
         else:
             _build.build()
     _LIB = ctypes.CDLL(_build.LIB)
-    if os.environ.get("RENEE_B200_GEMM_PREFETCH", "0") == "1":
-        _LIB.rb_enc_gemm_set_prefetch(_I(1))
+    if os.environ.get("RENEE_B200_GEMM_MAX_UNITS"):
+        _LIB.rb_enc_gemm_set_max_units(_I(int(os.environ["RENEE_B200_GEMM_MAX_UNITS"])))
 
 
 def _has_nvcc() -> bool:
@@ -341,7 +341,7 @@ def _enc_gemm(layout, epi, A, B, C, M, N, K, bias=None, R=None, F=None, p=0.0, r
         ncta = int(os.environ.get("RENEE_B200_GEMM_NCTA", "0"))
     if layout == L_TN:
         ncta_o, bn_o, sp_o, words_o, floats_o = _I(0), _I(0), _I(0), _I(0), _LL(0)
-        lib().rb_enc_gemm_plan(_I(layout), _I(M), _I(N), _I(K), _I(bn), _I(ncta), _c.byref(ncta_o), _c.byref(bn_o),
+        lib().rb_enc_gemm_plan(_I(layout), _I(epi), _I(M), _I(N), _I(K), _I(bn), _I(ncta), _c.byref(ncta_o), _c.byref(bn_o),
                                _c.byref(sp_o), _c.byref(floats_o), _c.byref(words_o))
         if sp_o.value > 1:
             key = dev.index if dev.index is not None else torch.cuda.current_device()
