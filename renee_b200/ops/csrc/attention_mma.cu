@@ -206,6 +206,8 @@ template <typename T, int SP>
 __global__ void __launch_bounds__(SP * 2, SP == 128 ? 2 : 1) attention_fwd_mma_kernel(
     const T* __restrict__ qkv, const T* __restrict__ bqkv, const int* __restrict__ mask, T* __restrict__ ctx,
     T* __restrict__ probs, int S, int H, int nh, float p, const int* __restrict__ seed_ptr, uint32_t stream) {
+  rb::grid_dep_wait();        // launched with launch_pdl: nothing above touches global memory
+  rb::grid_dep_launch();      // the kernel that follows may start its set-up; it waits for this grid before reading
   extern __shared__ __align__(128) uint8_t sm_raw[];
   T* sQ = reinterpret_cast<T*>(sm_raw);
   T* sK = sQ + SP * RP;
@@ -302,6 +304,8 @@ __global__ void __launch_bounds__(SP * 2) attention_bwd_mma_kernel(
     const T* __restrict__ dctx, const T* __restrict__ qkv, const T* __restrict__ bqkv, const T* __restrict__ probs,
     T* __restrict__ dqkv, int S, int H, int nh, float p, const int* __restrict__ seed_ptr, uint32_t stream,
     float* __restrict__ bias_acc) {
+  rb::grid_dep_wait();
+  rb::grid_dep_launch();
   extern __shared__ __align__(128) uint8_t sm_raw[];
   constexpr int PP = SP + 8;   // 4-byte fragment stores of a quad group land on distinct banks
   T* sQ = reinterpret_cast<T*>(sm_raw);
@@ -420,7 +424,7 @@ static int launch_fwd(const void* qkv, const void* bqkv, const int* mask, void* 
   constexpr size_t smem = fwd_smem<SP>(sizeof(T));
   if (smem > 48 * 1024 &&
       cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -5;
-  k<<<dim3(nh, b), SP * 2, smem, st>>>((const T*)qkv, (const T*)bqkv, mask, (T*)ctx, (T*)probs, S, H, nh, p, seed, stream_id);
+  rb::launch_pdl(k, dim3(nh, b), dim3(SP * 2), smem, st, (const T*)qkv, (const T*)bqkv, mask, (T*)ctx, (T*)probs, S, H, nh, p, seed, stream_id);
   return 0;
 }
 
@@ -431,8 +435,8 @@ static int launch_bwd(const void* dctx, const void* qkv, const void* bqkv, const
   constexpr size_t smem = bwd_smem<SP>(sizeof(T));
   if (smem > 48 * 1024 &&
       cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -5;
-  k<<<dim3(nh, b), SP * 2, smem, st>>>((const T*)dctx, (const T*)qkv, (const T*)bqkv, (const T*)probs, (T*)dqkv, S, H, nh, p,
-                                       seed, stream_id, bias_acc);
+  rb::launch_pdl(k, dim3(nh, b), dim3(SP * 2), smem, st, (const T*)dctx, (const T*)qkv, (const T*)bqkv, (const T*)probs,
+                 (T*)dqkv, S, H, nh, p, seed, stream_id, bias_acc);
   return 0;
 }
 

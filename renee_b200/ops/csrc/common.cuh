@@ -151,6 +151,36 @@ inline int sm_count() {
   return n;
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-stream-serialization attribute may
+// start (set up barriers, allocate TMEM, fetch descriptors) while its predecessor in the stream is still running,
+// once every CTA of the predecessor has executed launch_dependents (or exited); it must execute grid_dep_wait
+// before its first access to global memory, which blocks until the predecessor has completed and its writes are
+// visible.  Without the launch attribute both instructions do nothing.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Host side: one switch for the whole library and a launch helper that sets the attribute.  A kernel launched
+// through launch_pdl MUST execute grid_dep_wait() before its first access to global memory.
+inline int& pdl_flag() {
+  static int on = 1;
+  return on;
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_flag() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Counter-based dropout RNG; must stay bit-identical to renee_b200/ops/rng.py::mix32
 __device__ __forceinline__ uint32_t mix32(uint32_t seed, uint32_t stream, uint32_t idx) {
   uint32_t x = idx * 0x9E3779B1u + seed;

@@ -170,6 +170,7 @@ __global__ void __launch_bounds__(128) embed_ln_fwd_kernel(
     const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y,
     float* __restrict__ mean, float* __restrict__ rstd, int rows, int H, int S, float eps, float p,
     const int* __restrict__ seed_ptr, uint32_t stream) {
+  grid_dep_launch();
   const int lane = threadIdx.x & 31;
   const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (row >= rows) return;
@@ -247,6 +248,8 @@ __global__ void __launch_bounds__(128, 6) ln_bwd_kernel(
     float* __restrict__ acc, unsigned* __restrict__ counter, T* __restrict__ dgamma, T* __restrict__ dbeta,
     T* __restrict__ dbias, int rows, int H, int S, int pad_id, float p, const int* __restrict__ seed_ptr,
     uint32_t stream) {
+  grid_dep_wait();            // launched with launch_pdl: nothing above touches global memory
+  grid_dep_launch();
   extern __shared__ __align__(16) float sm[];  // [warps][3][H]
   const int lane = threadIdx.x & 31;
   const int wib = threadIdx.x >> 5;
@@ -612,9 +615,10 @@ RB_API int rb_bias_dropout_add_ln_bwd(int dtype, const void* dy, const void* pre
   const int blocks = ln_bwd_blocks(rows, 1, false);
   const size_t smem = 4 * 3 * (size_t)H * sizeof(float);
   DISPATCH_T(dtype, DISPATCH_NV(H, (cudaFuncSetAttribute(ln_bwd_kernel<T, NV, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                                    ln_bwd_kernel<T, NV, false><<<blocks, 128, smem, st>>>(
-      (const T*)dy, (const T*)pre, nullptr, nullptr, nullptr, (const T*)gamma, mean, rstd, (T*)d_pre, (T*)d_branch,
-      nullptr, nullptr, acc, counter, (T*)dgamma, (T*)dbeta, (T*)dbias, rows, H, 1, 0, p, seed, stream_id))));
+                                    launch_pdl(ln_bwd_kernel<T, NV, false>, dim3(blocks), dim3(128), smem, st,
+      (const T*)dy, (const T*)pre, (const int*)nullptr, (const T*)nullptr, (const T*)nullptr, (const T*)gamma, mean, rstd,
+      (T*)d_pre, (T*)d_branch, (T*)nullptr, (T*)nullptr, acc, counter, (T*)dgamma, (T*)dbeta, (T*)dbias, rows, H, 1, 0, p,
+      seed, stream_id))));
   RB_LAUNCH_CHECK();
   return 0;
 }
@@ -627,9 +631,10 @@ RB_API int rb_embed_ln_bwd(int dtype, const void* dy, const int* ids, const void
   const int blocks = ln_bwd_blocks(rows, S, true);
   const size_t smem = 4 * 3 * (size_t)H * sizeof(float);
   DISPATCH_T(dtype, DISPATCH_NV(H, (cudaFuncSetAttribute(ln_bwd_kernel<T, NV, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                                    ln_bwd_kernel<T, NV, true><<<blocks, 128, smem, st>>>(
-      (const T*)dy, nullptr, ids, (const T*)word, (const T*)pos, (const T*)gamma, mean, rstd, nullptr, nullptr,
-      (T*)dword, (T*)dpos, acc, counter, (T*)dgamma, (T*)dbeta, nullptr, rows, H, S, pad_id, p, seed, stream_id))));
+                                    launch_pdl(ln_bwd_kernel<T, NV, true>, dim3(blocks), dim3(128), smem, st,
+      (const T*)dy, (const T*)nullptr, ids, (const T*)word, (const T*)pos, (const T*)gamma, mean, rstd, (T*)nullptr,
+      (T*)nullptr, (T*)dword, (T*)dpos, acc, counter, (T*)dgamma, (T*)dbeta, (T*)nullptr, rows, H, S, pad_id, p, seed,
+      stream_id))));
   RB_LAUNCH_CHECK();
   return 0;
 }

@@ -162,6 +162,9 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   tc::tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
   bool aborted = false;
+  // everything above touched no global memory: it may have run under the tail of the previous kernel
+  grid_dep_wait();
+  grid_dep_launch();
 
   if (warp == 0 && lane == 0) {
     // ---------------- TMA producer: one continuous stream of (item, k block) stages
@@ -452,7 +455,7 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
       }
     }
-    if (STAGED && elected) tc::tma_store_wait_all();       // the stores have left shared memory and are globally visible
+    if (STAGED && elected) tc::tma_store_wait_read<0>();   // the stores have read shared memory; they complete before the grid does
   }
   tc::tc_fence_before();
   __syncthreads();
@@ -476,6 +479,8 @@ __global__ void __launch_bounds__(128) ln_fwd_kernel(const T* __restrict__ pre, 
                                                      const T* __restrict__ beta, T* __restrict__ y,
                                                      float* __restrict__ mean, float* __restrict__ rstd, int rows, int H,
                                                      float eps) {
+  grid_dep_wait();            // launched with launch_pdl: nothing above touches global memory
+  grid_dep_launch();          // the kernel that follows may start its set-up now; it waits for this grid before reading
   const int lane = threadIdx.x & 31;
   const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (row >= rows) return;
@@ -526,6 +531,9 @@ using namespace rb::eg;
 
 struct Maps { CUtensorMap a, b, c, r, f; };
 
+// Programmatic dependent launch (a kernel's set-up overlaps the previous kernel's tail): on by default.
+RB_API void rb_enc_gemm_set_pdl(int on) { pdl_flag() = on ? 1 : 0; }
+
 template <typename T, int LAYOUT, int EPI, int NCTA>
 static int launch_enc_gemm(const Maps& m, const Params& p, int units, cudaStream_t st) {
   static bool attr_set = false;
@@ -535,22 +543,27 @@ static int launch_enc_gemm(const Maps& m, const Params& p, int units, cudaStream
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -5;
     attr_set = true;
   }
-  if (NCTA == 1) {
-    k<<<units, THREADS, smem, st>>>(m.a, m.b, m.c, m.r, m.f, p);
-    return 0;
-  }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(2 * units, 1, 1);
+  cfg.gridDim = dim3(NCTA * units, 1, 1);
   cfg.blockDim = dim3(THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
+  cudaLaunchAttribute attr[2];
+  int n_attr = 0;
+  if (NCTA == 2) {
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = 2;
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = 1;
+    ++n_attr;
+  }
+  if (pdl_flag()) {
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = n_attr;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, k, m.a, m.b, m.c, m.r, m.f, p);
   return e == cudaSuccess ? 0 : (int)e;
 }
@@ -715,9 +728,9 @@ RB_API int rb_ln_fwd(int dtype, const void* pre, const void* gamma, const void* 
   if (H % 8 || rows < 1) return -3;
   const int blocks = (rows + 3) / 4;
   switch (dtype) {
-    case RB_F32: { using T = float; EG_DISPATCH_NV(H, (ln_fwd_kernel<T, NV><<<blocks, 128, 0, st>>>((const T*)pre, (const T*)gamma, (const T*)beta, (T*)y, mean, rstd, rows, H, eps))); break; }
-    case RB_BF16: { using T = __nv_bfloat16; EG_DISPATCH_NV(H, (ln_fwd_kernel<T, NV><<<blocks, 128, 0, st>>>((const T*)pre, (const T*)gamma, (const T*)beta, (T*)y, mean, rstd, rows, H, eps))); break; }
-    case RB_F16: { using T = __half; EG_DISPATCH_NV(H, (ln_fwd_kernel<T, NV><<<blocks, 128, 0, st>>>((const T*)pre, (const T*)gamma, (const T*)beta, (T*)y, mean, rstd, rows, H, eps))); break; }
+    case RB_F32: { using T = float; EG_DISPATCH_NV(H, (launch_pdl(ln_fwd_kernel<T, NV>, dim3(blocks), dim3(128), 0, st, (const T*)pre, (const T*)gamma, (const T*)beta, (T*)y, mean, rstd, rows, H, eps))); break; }
+    case RB_BF16: { using T = __nv_bfloat16; EG_DISPATCH_NV(H, (launch_pdl(ln_fwd_kernel<T, NV>, dim3(blocks), dim3(128), 0, st, (const T*)pre, (const T*)gamma, (const T*)beta, (T*)y, mean, rstd, rows, H, eps))); break; }
+    case RB_F16: { using T = __half; EG_DISPATCH_NV(H, (launch_pdl(ln_fwd_kernel<T, NV>, dim3(blocks), dim3(128), 0, st, (const T*)pre, (const T*)gamma, (const T*)beta, (T*)y, mean, rstd, rows, H, eps))); break; }
     default: return -1;
   }
   RB_LAUNCH_CHECK();

@@ -43,6 +43,8 @@ def _load():
         else:
             _build.build()
     _LIB = ctypes.CDLL(_build.LIB)
+    if os.environ.get("RENEE_B200_PDL", "1") == "0":
+        _LIB.rb_enc_gemm_set_pdl(_I(0))
     if os.environ.get("RENEE_B200_GEMM_MAX_UNITS"):
         _LIB.rb_enc_gemm_set_max_units(_I(int(os.environ["RENEE_B200_GEMM_MAX_UNITS"])))
 
