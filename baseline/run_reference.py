@@ -200,9 +200,15 @@ def run_reference(args, c) -> dict | None:
     except torch.cuda.OutOfMemoryError as exc:
         msg = str(exc).splitlines()[0][:300]
         print(f"reference arm, rank {rank}: {msg}", file=sys.stderr, flush=True)
+        out = {"impl": "reference", "unavailable": f"reference ran out of device memory: {msg}"}
         if G > 1:
-            os._exit(0 if rank else 3)     # the other ranks sit in a collective: leave without joining it
-        return {"impl": "reference", "unavailable": f"reference ran out of device memory: {msg}"}
+            # ranks that did not fail sit in a collective: print the verdict and leave without joining it
+            if rank == 0:
+                import json
+                print(json.dumps(out), flush=True)
+            sys.stdout.flush()
+            os._exit(0)
+        return out
     if state["ev0"] is None or state["ev1"] is None:
         return {"impl": "reference", "unavailable": "reference loop ended before the timed region"} if rank == 0 else None
     ms = state["ev0"].elapsed_time(state["ev1"])

@@ -81,6 +81,13 @@ class FlatEncoder:
             names.append(("__bottleneck__.transformer_weight", (self.bottleneck_dims, H)))
         decay = [(n, s) for n, s in names if not _no_decay(n)]
         nodecay = [(n, s) for n, s in names if _no_decay(n)]
+        # the (decayed) block LayerNorm weights go behind the last layer's matrices: a layer's matrices are then one
+        # contiguous range whose gradients are final as soon as the backward pass leaves the layer, while every
+        # vector-shaped gradient (LayerNorm, biases: converted by one launch at the end of the pass) sits in the
+        # tail of the buffer — which is what lets the gradient reduction start layer by layer under the backward pass
+        ln_w = [(n, s) for n, s in decay if n.endswith("layer_norm.weight")]
+        decay = [(n, s) for n, s in decay if not n.endswith("layer_norm.weight") and not n.startswith("__bottleneck__")] \
+            + ln_w + [(n, s) for n, s in decay if n.startswith("__bottleneck__")]
         self.slots: dict[str, _Slot] = {}
         off = 0
         for n, s in decay:
@@ -295,9 +302,10 @@ class FlatEncoder:
     # ------------------------------------------------------------------ backward
     def backward(self, d_emb: torch.Tensor, on_layer_done=None) -> None:
         """``d_emb [b, D]`` fp32 → gradients of every parameter written into the flat ``g`` buffer
-        (overwritten, not accumulated).  ``on_layer_done(lo, hi)`` is called with the flat range
-        whose gradients have just become final, so a caller can start reducing it across ranks while
-        the remaining layers are still being differentiated."""
+        (overwritten, not accumulated).  ``on_layer_done(l)`` is called when the gradients of layer ``l``'s
+        matrices (one contiguous range of the flat buffer) have become final, and ``on_layer_done(-1)`` at the
+        end of the pass (embeddings, bottleneck, LayerNorm parameters and biases), so a caller can reduce the
+        buffer across ranks piece by piece while the remaining layers are still being differentiated."""
         if self.g.is_cuda:
             # column sums (LN gammas/betas, all bias gradients) are accumulated by the kernels and converted
             # by ONE launch at the end of the pass instead of a serial tail inside each kernel
@@ -309,6 +317,8 @@ class FlatEncoder:
             self._plan.finalize()
         else:
             self._backward(d_emb, on_layer_done)
+        if on_layer_done is not None:
+            on_layer_done(-1)       # embeddings and every vector-shaped gradient are final: the whole buffer is
 
     def _wgrad(self, dy, x, dW) -> None:
         """``dW = dy^T x`` on the weight-gradient stream (ordered after everything issued so far on the current one)."""
@@ -415,5 +425,3 @@ class FlatEncoder:
                          self.view(G, "embeddings.word_embeddings.weight"),
                          self.view(G, "embeddings.position_embeddings.weight"),
                          self.view(G, "embeddings.LayerNorm.weight"), self.view(G, "embeddings.LayerNorm.bias"))
-        if on_layer_done is not None:
-            on_layer_done(-1)

@@ -179,16 +179,17 @@ __global__ void __launch_bounds__(256) grad_allreduce_kernel(PeerPtrs grads, lon
 //       to its slice of the fp32 master weights / moments and stores the new 16-bit weights of the slice
 //       into EVERY rank's compute copy (all-gather of parameters), then raises "slice pushed".
 // NVLink traffic equals that of the all-reduce it replaces; the AdamW traffic to HBM drops by 1/G.
+// [v0, v1): the 8-element vectors of the flat buffer this rank reduces in this launch (its slice of the whole
+// buffer, or its slice of one bucket when the reduction is overlapped with the backward pass); tag_a: value the
+// peers' progress flags must have reached; flag_b_base < 0: no "slice reduced" signal after this launch.
 template <typename T>
-__global__ void __launch_bounds__(256) grad_reduce_scatter_kernel(PeerPtrs grads, long long n, int G, int my_rank,
-                                                                  const uint32_t* __restrict__ my_flags_a, StepTag tag,
-                                                                  float* __restrict__ gsum, PeerPtrs flags, int flag_b_base,
-                                                                  int found_base, unsigned* __restrict__ counter,
-                                                                  int* status, const void* mc_grads) {
-  const bool ok = block_wait_flags(my_flags_a, G, tag.value(), status, 5);
-  const long long n_vec = n / 8;
-  const long long per = (n_vec + G - 1) / G;
-  const long long v0 = min(n_vec, per * my_rank), v1 = min(n_vec, per * (my_rank + 1));
+__global__ void __launch_bounds__(256) grad_reduce_scatter_kernel(PeerPtrs grads, long long v0, long long v1, int G,
+                                                                  int my_rank, const uint32_t* __restrict__ my_flags_a,
+                                                                  StepTag tag_a, StepTag tag, float* __restrict__ gsum,
+                                                                  PeerPtrs flags, int flag_b_base, int found_base,
+                                                                  unsigned* __restrict__ counter, int* status,
+                                                                  const void* mc_grads) {
+  const bool ok = block_wait_flags(my_flags_a, G, tag_a.value(), status, 5);
   bool bad = false;
   if (ok) {
     for (long long i = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < v1; i += (long long)gridDim.x * blockDim.x) {
@@ -217,6 +218,7 @@ __global__ void __launch_bounds__(256) grad_reduce_scatter_kernel(PeerPtrs grads
   if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) {
     for (int q = 0; q < G; ++q) reinterpret_cast<uint32_t*>(flags.p[q])[found_base + my_rank] = 1u;
   }
+  if (flag_b_base < 0) return;       // an intermediate bucket: the last launch of the step signals for all of them
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -230,26 +232,30 @@ __global__ void __launch_bounds__(256) grad_reduce_scatter_kernel(PeerPtrs grads
   }
 }
 
+// Ranges of 8-element vectors this rank updates: [v0, v1) of the flat buffer, whose reduced gradients start at
+// vector g0 of gsum.  One range for the whole-buffer slice, one per bucket when the reduction was overlapped.
+constexpr int kMaxRanges = 16;
+struct VecRanges { int n; long long v0[kMaxRanges], v1[kMaxRanges], g0[kMaxRanges]; };
+
 template <typename T>
 __global__ void __launch_bounds__(256) adamw_shard_push_kernel(float* __restrict__ p32, float* __restrict__ m,
                                                                float* __restrict__ v, const float* __restrict__ gsum,
-                                                               PeerPtrs p16, long long n, long long n_decay, int G, int my_rank,
+                                                               PeerPtrs p16, VecRanges rg, long long n_decay, int G, int my_rank,
                                                                const float* __restrict__ hp, float beta1, float beta2,
                                                                float eps, float wd, float grad_mult, PeerPtrs flags,
                                                                int flag_c_base, StepTag tag, unsigned* __restrict__ counter,
                                                                void* mc_p16) {
-  const long long n_vec = n / 8;
-  const long long per = (n_vec + G - 1) / G;
-  const long long v0 = min(n_vec, per * my_rank), v1 = min(n_vec, per * (my_rank + 1));
   if (hp[HP_FOUND_INF] == 0.f) {
     const float lr = hp[HP_LR_ENC];
     const float step = hp[HP_ADAM_STEP] + 1.0f;
     const float inv_scale = hp[HP_INV_SCALE] * grad_mult;
     const float inv_bc1 = 1.f / (1.f - powf(beta1, step)), inv_bc2 = 1.f / (1.f - powf(beta2, step));
+    for (int ri = 0; ri < rg.n; ++ri) {
+    const long long v0 = rg.v0[ri], v1 = rg.v1[ri], g0 = rg.g0[ri];
     for (long long i = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < v1; i += (long long)gridDim.x * blockDim.x) {
       const size_t e = (size_t)i * 8;
       float gg[8], pp[8], mm[8], vv[8];
-      load8(gsum + (i - v0) * 8, gg);
+      load8(gsum + (g0 + i - v0) * 8, gg);
       load8(p32 + e, pp);
       load8(m + e, mm);
       load8(v + e, vv);
@@ -273,6 +279,7 @@ __global__ void __launch_bounds__(256) adamw_shard_push_kernel(float* __restrict
       } else {
         for (int q = 0; q < G; ++q) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p16.p[q]) + e) = out;
       }
+    }
     }
   }
   __threadfence_system();
@@ -369,18 +376,58 @@ RB_API int rb_grad_allreduce(int dtype, void* const* grads, long long lo, long l
   return 0;
 }
 
+// Reduce-scatter of vectors [v0, v1) (8 elements each) of the flat gradient buffer into gsum[0 .. (v1-v0)*8): the
+// sums over all ranks.  Waits until every rank's progress flag (class A) has reached step * mul_a + add_a; with
+// flag_b_base >= 0 raises "reduced" (class B, value step) on every rank afterwards.
+RB_API int rb_grad_reduce_scatter_range(int dtype, void* const* grads, long long v0, long long v1, int G, int my_rank,
+                                        const unsigned* my_flags_a, const unsigned* step_ptr, unsigned mul_a, unsigned add_a,
+                                        float* gsum, void* const* flags, int flag_b_base, int found_base, unsigned* counter,
+                                        int blocks, int* status, const void* mc_grads, cudaStream_t st) {
+  if (G > kMaxPeers || v0 < 0 || v1 < v0) return -3;
+  if (blocks < 1) blocks = 1;
+  PeerPtrs g = make_ptrs(grads, G), f = make_ptrs(flags, G);
+  const StepTag tag_a{step_ptr, mul_a, add_a}, tag{step_ptr, 1u, 0u};
+  if (dtype == RB_BF16)
+    grad_reduce_scatter_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(g, v0, v1, G, my_rank, my_flags_a, tag_a, tag, gsum, f, flag_b_base, found_base, counter, status, mc_grads);
+  else if (dtype == RB_F16)
+    grad_reduce_scatter_kernel<__half><<<blocks, 256, 0, st>>>(g, v0, v1, G, my_rank, my_flags_a, tag_a, tag, gsum, f, flag_b_base, found_base, counter, status, mc_grads);
+  else
+    return -1;
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+// This rank's contiguous 1/G slice of the whole buffer (n elements), progress tag = step.
 RB_API int rb_grad_reduce_scatter(int dtype, void* const* grads, long long n, int G, int my_rank,
                                   const unsigned* my_flags_a, const unsigned* step_ptr, float* gsum, void* const* flags,
                                   int flag_b_base, int found_base, unsigned* counter, int blocks, int* status,
                                   const void* mc_grads, cudaStream_t st) {
-  if (G > kMaxPeers || n % 8) return -3;
+  if (n % 8) return -3;
+  const long long n_vec = n / 8, per = (n_vec + G - 1) / G;
+  const long long v0 = per * my_rank < n_vec ? per * my_rank : n_vec;
+  const long long v1 = per * (my_rank + 1) < n_vec ? per * (my_rank + 1) : n_vec;
+  return rb_grad_reduce_scatter_range(dtype, grads, v0, v1, G, my_rank, my_flags_a, step_ptr, 1u, 0u, gsum, flags,
+                                      flag_b_base, found_base, counter, blocks, status, mc_grads, st);
+}
+
+// AdamW on the vector ranges [v0[i], v1[i]) whose reduced gradients start at vector g0[i] of gsum, then the push of
+// the updated 16-bit values into every rank's compute copy and the "pushed" flag (class C).
+RB_API int rb_adamw_ranges_push(int dtype, float* p32, float* m, float* v, const float* gsum, void* const* p16,
+                                int n_ranges, const long long* v0, const long long* v1, const long long* g0,
+                                long long n_decay, int G, int my_rank, const float* hp, float beta1, float beta2, float eps,
+                                float wd, float grad_mult, void* const* flags, int flag_c_base, const unsigned* step_ptr,
+                                unsigned* counter, int blocks, void* mc_p16, cudaStream_t st) {
+  if (G > kMaxPeers || n_decay % 8 || n_ranges < 0 || n_ranges > kMaxRanges) return -3;
   if (blocks < 1) blocks = 1;
-  PeerPtrs g = make_ptrs(grads, G), f = make_ptrs(flags, G);
+  VecRanges rg{};
+  rg.n = n_ranges;
+  for (int i = 0; i < n_ranges; ++i) { rg.v0[i] = v0[i]; rg.v1[i] = v1[i]; rg.g0[i] = g0[i]; }
+  PeerPtrs pp = make_ptrs(p16, G), f = make_ptrs(flags, G);
   const StepTag tag{step_ptr, 1u, 0u};
   if (dtype == RB_BF16)
-    grad_reduce_scatter_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(g, n, G, my_rank, my_flags_a, tag, gsum, f, flag_b_base, found_base, counter, status, mc_grads);
+    adamw_shard_push_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(p32, m, v, gsum, pp, rg, n_decay, G, my_rank, hp, beta1, beta2, eps, wd, grad_mult, f, flag_c_base, tag, counter, mc_p16);
   else if (dtype == RB_F16)
-    grad_reduce_scatter_kernel<__half><<<blocks, 256, 0, st>>>(g, n, G, my_rank, my_flags_a, tag, gsum, f, flag_b_base, found_base, counter, status, mc_grads);
+    adamw_shard_push_kernel<__half><<<blocks, 256, 0, st>>>(p32, m, v, gsum, pp, rg, n_decay, G, my_rank, hp, beta1, beta2, eps, wd, grad_mult, f, flag_c_base, tag, counter, mc_p16);
   else
     return -1;
   RB_LAUNCH_CHECK();
@@ -391,18 +438,13 @@ RB_API int rb_adamw_shard_push(int dtype, float* p32, float* m, float* v, const 
                                long long n, long long n_decay, int G, int my_rank, const float* hp, float beta1,
                                float beta2, float eps, float wd, float grad_mult, void* const* flags, int flag_c_base,
                                const unsigned* step_ptr, unsigned* counter, int blocks, void* mc_p16, cudaStream_t st) {
-  if (G > kMaxPeers || n % 8 || n_decay % 8) return -3;
-  if (blocks < 1) blocks = 1;
-  PeerPtrs pp = make_ptrs(p16, G), f = make_ptrs(flags, G);
-  const StepTag tag{step_ptr, 1u, 0u};
-  if (dtype == RB_BF16)
-    adamw_shard_push_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(p32, m, v, gsum, pp, n, n_decay, G, my_rank, hp, beta1, beta2, eps, wd, grad_mult, f, flag_c_base, tag, counter, mc_p16);
-  else if (dtype == RB_F16)
-    adamw_shard_push_kernel<__half><<<blocks, 256, 0, st>>>(p32, m, v, gsum, pp, n, n_decay, G, my_rank, hp, beta1, beta2, eps, wd, grad_mult, f, flag_c_base, tag, counter, mc_p16);
-  else
-    return -1;
-  RB_LAUNCH_CHECK();
-  return 0;
+  if (n % 8) return -3;
+  const long long n_vec = n / 8, per = (n_vec + G - 1) / G;
+  const long long v0 = per * my_rank < n_vec ? per * my_rank : n_vec;
+  const long long v1 = per * (my_rank + 1) < n_vec ? per * (my_rank + 1) : n_vec;
+  const long long g0 = 0;
+  return rb_adamw_ranges_push(dtype, p32, m, v, gsum, p16, 1, &v0, &v1, &g0, n_decay, G, my_rank, hp, beta1, beta2, eps, wd,
+                              grad_mult, flags, flag_c_base, step_ptr, counter, blocks, mc_p16, st);
 }
 
 // ------------------------------------------------------------------------------------ peer-mapped allocations

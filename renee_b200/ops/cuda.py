@@ -667,6 +667,28 @@ def grad_reduce_scatter(g_dtype, grad_ptrs, n, G, my_rank, my_flags_a, step, gsu
           _stream())
 
 
+def grad_reduce_scatter_range(g_dtype, grad_ptrs, v0, v1, G, my_rank, my_flags_a, step, mul_a, add_a, gsum, flag_ptrs,
+                              flag_b_base, found_base, counter, blocks, mc_grads: int = 0):
+    """Sums vectors ``[v0, v1)`` (8 elements each) of the flat gradient over all ranks into ``gsum``; waits until
+    every rank's progress flag has reached ``step * mul_a + add_a``; ``flag_b_base < 0``: no completion signal."""
+    ws = workspace(my_flags_a.device)
+    _call("rb_grad_reduce_scatter_range", _I(DT[g_dtype]), grad_ptrs, _LL(v0), _LL(v1), _I(G), _I(my_rank), _p(my_flags_a),
+          _p(step), _U(mul_a), _U(add_a), _p(gsum), flag_ptrs, _I(flag_b_base), _I(found_base), _p(counter), _I(blocks),
+          _p(ws.status), _VP(mc_grads), _stream())
+
+
+def adamw_ranges_push(p_dtype, p32, m, v, gsum, p16_ptrs, ranges, n_decay, G, my_rank, hp_buf, beta1, beta2, eps, wd,
+                      grad_mult, flag_ptrs, flag_c_base, step, counter, blocks, mc_p16: int = 0):
+    """AdamW on ``ranges = [(v0, v1, g0), ...]`` (vector ranges of the flat buffer, start of their sums in ``gsum``)
+    and the push of the updated 16-bit values into every rank's compute copy."""
+    n = len(ranges)
+    arr = _LL * max(n, 1)
+    v0, v1, g0 = arr(*[r[0] for r in ranges]), arr(*[r[1] for r in ranges]), arr(*[r[2] for r in ranges])
+    _call("rb_adamw_ranges_push", _I(DT[p_dtype]), _p(p32), _p(m), _p(v), _p(gsum), p16_ptrs, _I(n), v0, v1, g0,
+          _LL(n_decay), _I(G), _I(my_rank), _p(hp_buf), _F(beta1), _F(beta2), _F(eps), _F(wd), _F(grad_mult), flag_ptrs,
+          _I(flag_c_base), _p(step), _p(counter), _I(blocks), _VP(mc_p16), _stream())
+
+
 def adamw_shard_push(p_dtype, p32, m, v, gsum, p16_ptrs, n, n_decay, G, my_rank, hp_buf, beta1, beta2, eps, wd, grad_mult,
                      flag_ptrs, flag_c_base, step, counter, blocks, mc_p16: int = 0):
     _call("rb_adamw_shard_push", _I(DT[p_dtype]), _p(p32), _p(m), _p(v), _p(gsum), p16_ptrs, _LL(n), _LL(n_decay), _I(G),

@@ -75,6 +75,7 @@ class PeerCollectives(TorchCollectives):
         self._ready = False
         self.grad = None
         self.host_step = 0
+        self._comm_stream = None
 
     # ------------------------------------------------------------------ allocation
     def _symm(self, numel: int, dtype, name: str = "symmetric"):
@@ -177,21 +178,118 @@ class PeerCollectives(TorchCollectives):
         return (self.shard_optimizer and self.p16 is not None and self.grad is not None
                 and enc.g.data_ptr() == self.grad.data_ptr() and enc.p16.data_ptr() == self.p16.data_ptr())
 
+    # ------------------------------------------------------------------ sharded optimizer, overlapped with backward
+    def _buckets(self, enc):
+        """Splits the flat gradient buffer into buckets that become final at successive points of the backward pass
+        and gives every rank 1/G of EACH bucket (so every rank has work for every bucket, also for the last and
+        largest one, the embeddings).  Stage ``s`` = 1 .. n_layers is reached when layer ``n_layers - s`` is done,
+        stage ``n_layers + 1`` at the end of the pass (embeddings, bottleneck, and the no-decay tail of the buffer:
+        biases and LayerNorm parameters of all layers).  Returns ``[(stage, v0, v1, g0)]`` for this rank: vector
+        (8-element) ranges of the flat buffer and the offset of their sums in ``gsum``."""
+        key = (id(enc), enc.numel)
+        if getattr(self, "_bucket_key", None) == key:
+            return self._bucket_plan
+        L = enc.cfg.n_layers
+        start = [enc.slots[f"transformer.layer.{l}.attention.q_lin.weight"].offset for l in range(L)]
+        last = enc.slots[f"transformer.layer.{L - 1}.ffn.lin2.weight"]
+        end = start[1:] + [(last.offset + last.numel + 127) // 128 * 128]   # a layer's matrices are contiguous
+        ranges = [(L - l, start[l], end[l]) for l in reversed(range(L))]            # (stage, lo, hi) in elements
+        ranges += [(L + 1, 0, start[0]), (L + 1, end[-1], enc.numel // 8 * 8)]
+        plan, g0 = [], 0
+        for stage, lo, hi in ranges:
+            n_vec = (hi - lo) // 8
+            per = (n_vec + self.G - 1) // self.G
+            a = lo // 8 + min(n_vec, per * self.rank)
+            b = lo // 8 + min(n_vec, per * (self.rank + 1))
+            if b > a:
+                plan.append((stage, a, b, g0))
+                g0 += b - a
+        need = g0 * 8
+        if self.gsum is None or self.gsum.numel() < need:
+            self.gsum = guard.zeros(need + 8, dtype=torch.float32, device=self.ctx.device, name="optimizer.gsum")
+        self._bucket_plan, self._bucket_key = plan, key
+        self._bucket_ranges = ranges
+        self._n_stages = L + 1
+        return plan
+
+    def owned_ranges(self, enc, rank: int):
+        """Element ranges of the flat buffer whose master weights rank ``rank`` keeps up to date."""
+        self._buckets(enc)
+        out = []
+        for _, lo, hi in self._bucket_ranges:
+            n_vec = (hi - lo) // 8
+            per = (n_vec + self.G - 1) // self.G
+            a, b = lo + min(n_vec, per * rank) * 8, lo + min(n_vec, per * (rank + 1)) * 8
+            if b > a:
+                out.append((a, b))
+        return out
+
+    def backward_begin(self, enc) -> None:
+        """Called before the encoder backward: the reduction of finished buckets runs on a second stream."""
+        if not self._sharded(enc):
+            return
+        self._buckets(enc)
+        if self._comm_stream is None:
+            self._comm_stream = torch.cuda.Stream(device=self.ctx.device)
+        self._stage = 0
+
+    def on_layer_done(self, enc, layer: int) -> None:
+        """Gradient of ``layer`` (``-1``: the embeddings, i.e. the end of the pass) is final on this rank: tell the
+        peers, and reduce this rank's part of the bucket as soon as every peer has told the same."""
+        from ..ops import cuda as cu
+        if not self._sharded(enc) or self._comm_stream is None:
+            return
+        L = enc.cfg.n_layers
+        stage = L - layer if layer >= 0 else L + 1
+        self._stage = stage
+        last = stage == L + 1
+        main = torch.cuda.current_stream()
+        # progress flag: step * 32 + stage (monotone within a step and from step to step)
+        cu.signal(self._flag_ptrs, self.G, F_ARA, self.rank, self.step, 32, stage)
+        side = self._comm_stream
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            mine = [b for b in self._bucket_plan if b[0] == stage]
+            blocks = cu.sm_count(self.ctx.device) * 2 if last else 32      # few CTAs while the backward GEMMs run
+            for i, (_, a, b, g0) in enumerate(mine):
+                final = last and i == len(mine) - 1
+                cu.grad_reduce_scatter_range(enc.g.dtype, self._grad_ptrs, a, b, self.G, self.rank, self.flags[F_ARA:],
+                                             self.step, 32, stage, self.gsum[g0 * 8:], self._flag_ptrs,
+                                             F_ARB if final else -1, F_FOUND, self.counters[48:], blocks,
+                                             mc_grads=self._mc_grad)
+            if last and not mine:
+                # nothing of the last bucket is this rank's: still tell the peers that its reductions are done
+                cu.signal(self._flag_ptrs, self.G, F_ARB, self.rank, self.step)
+        if last:
+            main.wait_stream(side)
+
     def optimizer_step(self, enc, hp, beta1, beta2, eps, wd) -> None:
-        """Sharded AdamW: reduce-scatter of the gradients, AdamW on this rank's slice of the masters, push of
-        the updated 16-bit slice into every rank's compute copy.  The found-inf decision is global because
-        the slice update only starts after every rank's reduction (and its non-finite report) has landed."""
+        """Sharded AdamW: reduce-scatter of the gradients, AdamW on this rank's part of the masters, push of
+        the updated 16-bit values into every rank's compute copy.  The found-inf decision is global because
+        the update only starts after every rank's reductions (and their non-finite reports) have landed.  When
+        the trainer drove ``backward_begin`` / ``on_layer_done`` the reductions already ran, bucket by bucket, under
+        the backward pass; otherwise they run here in one piece."""
         from ..ops import cuda as cu
         if not self._sharded(enc):
             return super().optimizer_step(enc, hp, beta1, beta2, eps, wd)
-        n = enc.numel
-        cu.signal(self._flag_ptrs, self.G, F_ARA, self.rank, self.step)
-        cu.grad_reduce_scatter(enc.g.dtype, self._grad_ptrs, n, self.G, self.rank, self.flags[F_ARA:], self.step, self.gsum,
-                               self._flag_ptrs, F_ARB, F_FOUND, self.counters[48:], cu.sm_count(self.ctx.device) * 2, mc_grads=self._mc_grad)
+        plan = self._buckets(enc)
+        sms = cu.sm_count(self.ctx.device)
+        if getattr(self, "_stage", 0) != self._n_stages:
+            # not overlapped (eager callers, tests): every bucket now, all flags at their final value
+            cu.signal(self._flag_ptrs, self.G, F_ARA, self.rank, self.step, 32, self._n_stages)
+            for i, (_, a, b, g0) in enumerate(plan):
+                cu.grad_reduce_scatter_range(enc.g.dtype, self._grad_ptrs, a, b, self.G, self.rank, self.flags[F_ARA:],
+                                             self.step, 32, self._n_stages, self.gsum[g0 * 8:], self._flag_ptrs,
+                                             F_ARB if i == len(plan) - 1 else -1, F_FOUND, self.counters[48:], sms * 2,
+                                             mc_grads=self._mc_grad)
+            if not plan:
+                cu.signal(self._flag_ptrs, self.G, F_ARB, self.rank, self.step)
+        self._stage = 0
         cu.wait_flags(self.flags[F_ARB:], self.G, self.step, 1, 0, self.flags[F_FOUND:], hp.buf)
-        cu.adamw_shard_push(enc.p16.dtype, enc.p32, enc.m, enc.v, self.gsum, self._p16_ptrs, n, enc.n_decay, self.G,
-                            self.rank, hp.buf, beta1, beta2, eps, wd, 1.0 / self.G, self._flag_ptrs, F_ARC, self.step,
-                            self.counters[52:], cu.sm_count(self.ctx.device) * 2, mc_p16=self._mc_p16)
+        cu.adamw_ranges_push(enc.p16.dtype, enc.p32, enc.m, enc.v, self.gsum, self._p16_ptrs,
+                             [(a, b, g0) for _, a, b, g0 in plan], enc.n_decay, self.G, self.rank, hp.buf, beta1, beta2,
+                             eps, wd, 1.0 / self.G, self._flag_ptrs, F_ARC, self.step, self.counters[52:], sms * 2,
+                             mc_p16=self._mc_p16)
         cu.wait_flags(self.flags[F_ARC:], self.G, self.step, 1, 0, None, None)
 
     def sync_master(self, enc) -> None:
@@ -200,8 +298,7 @@ class PeerCollectives(TorchCollectives):
         if not self._sharded(enc):
             return
         for r in range(self.G):
-            lo, hi = self.slice_range(enc.numel, r)
-            if hi > lo:
+            for lo, hi in self.owned_ranges(enc, r):
                 dist.broadcast(enc.p32[lo:hi], src=r, group=self.group)
 
     # ------------------------------------------------------------------ per-step protocol

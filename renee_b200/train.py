@@ -335,7 +335,11 @@ class XCTrainer:
         with nvtx_range("reduce_scatter"):
             de = comm.dx_to_local(dX, B, cfg.dropout, self.step_rng, _S_CLS_DROPOUT, bf)
         with nvtx_range("encoder_backward"):
-            enc.backward(de)
+            # with the peer-memory backend the gradient reduce-scatter runs bucket by bucket under the backward pass
+            hook = getattr(comm, "on_layer_done", None)
+            if hook is not None:
+                comm.backward_begin(enc)
+            enc.backward(de, on_layer_done=(lambda l: hook(enc, l)) if hook is not None else None)
         with nvtx_range("optimizer"):
             comm.optimizer_step(enc, self.hp, 0.9, 0.999, cfg.adam_eps, cfg.wd2)
             self.hp.update_scale()

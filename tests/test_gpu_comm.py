@@ -183,3 +183,70 @@ def test_sharded_adamw_emulated_matches_full_adamw():
         assert torch.equal(s["p32"][:lo], p0[:lo]) and torch.equal(s["p32"][hi:], p0[hi:])   # other slices untouched
         torch.testing.assert_close(s["p16"].float(), rp, rtol=1e-2, atol=1e-2)                  # every slice arrived
         assert k.flags[F_ARC:F_ARC + G].tolist() == [1] * G
+
+
+def test_bucketed_reduce_scatter_emulated_three_buckets():
+    """The overlapped form of the sharded optimizer: the flat gradient is reduced bucket by bucket, every rank
+    owning 1/G of EACH bucket, each bucket as soon as all ranks have reported the stage that completes it; then
+    one AdamW launch over all of a rank's ranges.  Equals all-reduce + full AdamW."""
+    from renee_b200.parallel.fused import F_ARC
+    G, n, n_decay = 4, 8 * 1200, 8 * 700
+    torch.manual_seed(3)
+    ranks = [Rank(r, G, 8, 8, n) for r in range(G)]
+    buckets = [(1, 8 * 700, 8 * 1100), (2, 8 * 300, 8 * 700), (3, 0, 8 * 300), (3, 8 * 1100, n)]   # (stage, lo, hi)
+    p0 = torch.randn(n, device=dev())
+    m0, v0 = torch.rand(n, device=dev()) * 0.1, torch.rand(n, device=dev()) * 0.01
+    st = []
+    for k in ranks:
+        k.grad.copy_((torch.randn(n, device=dev()) * 64).bfloat16())
+        hp = HyperParams(dev(), init_scale=64.0)
+        hp.buf[HP.LR_ENC] = 1e-2
+        hp.buf[HP.ADAM_STEP] = 2
+        st.append(dict(p32=p0.clone(), m=m0.clone(), v=v0.clone(), p16=p0.bfloat16(), hp=hp,
+                       gsum=torch.zeros(n // G + 256, device=dev())))
+    gsum_all = sum(k.grad.float() for k in ranks)
+    rp, rm, rv = p0.clone(), m0.clone(), v0.clone()
+    ref.adamw_step(rp, rm, rv, gsum_all, None, 1e-2, 0.9, 0.999, 1e-6, 0.01, n_decay, 3.0, (1 / 64.0) / G, 0.0)
+
+    def plan(r):
+        out, g0 = [], 0
+        for stage, lo, hi in buckets:
+            n_vec = (hi - lo) // 8
+            per = (n_vec + G - 1) // G
+            a, b = lo // 8 + min(n_vec, per * r), lo // 8 + min(n_vec, per * (r + 1))
+            if b > a:
+                out.append((stage, a, b, g0))
+                g0 += b - a
+        return out
+
+    g_ptrs = cu().ptr_array([k.grad.data_ptr() for k in ranks])
+    f_ptrs = cu().ptr_array([k.flags.data_ptr() for k in ranks])
+    p_ptrs = cu().ptr_array([s["p16"].data_ptr() for s in st])
+    for stage in (1, 2, 3):
+        for k in ranks:                                   # every emulated rank reports the stage ...
+            cu().signal(f_ptrs, G, F_ARA, k.r, k.step, 32, stage)
+        for k, s in zip(ranks, st):                       # ... then every rank reduces its part of the stage's buckets
+            mine = [b for b in plan(k.r) if b[0] == stage]
+            for i, (_, a, b, g0) in enumerate(mine):
+                final = stage == 3 and i == len(mine) - 1
+                cu().grad_reduce_scatter_range(torch.bfloat16, g_ptrs, a, b, G, k.r, k.flags[F_ARA:], k.step, 32, stage,
+                                               s["gsum"][g0 * 8:], f_ptrs, F_ARB if final else -1, F_FOUND,
+                                               k.counters[48:], 3)
+    for k, s in zip(ranks, st):
+        cu().wait_flags(k.flags[F_ARB:], G, k.step, 1, 0, k.flags[F_FOUND:], s["hp"].buf)
+    for k, s in zip(ranks, st):
+        cu().adamw_ranges_push(torch.bfloat16, s["p32"], s["m"], s["v"], s["gsum"], p_ptrs,
+                               [(a, b, g0) for _, a, b, g0 in plan(k.r)], n_decay, G, k.r, s["hp"].buf, 0.9, 0.999, 1e-6,
+                               0.01, 1.0 / G, f_ptrs, F_ARC, k.step, k.counters[52:], 3)
+    for k in ranks:
+        cu().wait_flags(k.flags[F_ARC:], G, k.step, 1, 0, None, None)
+    cu().check_status()
+    for k, s in zip(ranks, st):
+        own = torch.zeros(n, dtype=torch.bool, device=dev())
+        for _, a, b, _ in plan(k.r):
+            own[a * 8: b * 8] = True
+        torch.testing.assert_close(s["p32"][own], rp[own], rtol=1e-5, atol=1e-6)
+        torch.testing.assert_close(s["m"][own], rm[own], rtol=1e-5, atol=1e-7)
+        assert torch.equal(s["p32"][~own], p0[~own])                                      # other ranks' parts untouched
+        torch.testing.assert_close(s["p16"].float(), rp, rtol=1e-2, atol=1e-2)           # every part arrived
+        assert float(s["hp"].buf[HP.FOUND_INF]) == 0.0
