@@ -3,8 +3,9 @@
 Parity: ``FullPredictor`` (reference dl_base.py:700-799) and ``PrecEvaluator`` (dl_base.py:801-861).
 
 Prediction: every rank encodes its rows, embeddings are all-gathered, each rank takes the top-K of
-its own label shard (on a GPU: per label chunk the tcgen05 logits GEMM followed by a row-wise selection
-kernel, see ``ops/cuda.py::xfc_topk``), local label ids are offset to global ids and padded labels are
+its own label shard (on a GPU, K <= 8: a tcgen05 GEMM whose epilogue keeps a running top-8 per row, so the
+``[B, Ls]`` logits are never written; larger K: per label chunk the logits GEMM followed by a row-wise selection
+kernel; see ``ops/cuda.py::xfc_topk``), local label ids are offset to global ids and padded labels are
 clipped to ``L-1``, candidates are merged across ranks, and rank 0 assembles a CSR score matrix
 ``[N_tst, L]`` with exactly K entries per row.
 

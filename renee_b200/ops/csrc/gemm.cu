@@ -13,6 +13,9 @@
 //              ADD                  C = acc + R                                      (dgrad joined with the residual gradient)
 //              GELU_BWD             C = acc * gelu'(R) ;  column sums of C -> bias gradient accumulators
 //              SPLITK               fp32 partials reduced in L2, the last CTA of a tile converts and stores
+//              TOPK                 nothing is stored: every epilogue thread keeps the 8 largest entries of its row
+//                                   over all the tiles its CTA visits and writes them as candidates at the end
+//                                   (prediction: X W^T is never materialised; parity: dl_base.py:745-756)
 //
 // Structure.  Persistent CTAs walk the work items (tile x K-split).  320 threads: warp 0 TMA producer, warp 1
 // TMEM owner + MMA issuer, warps 2..9 epilogue (two groups of four warps, one TMEM lane quarter per warp, half
@@ -58,7 +61,7 @@ template <bool STAGED> struct Cfg {
 };
 
 enum Layout : int { L_NT = 0, L_NN = 1, L_TN = 2 };
-enum Epi : int { E_STORE = 0, E_BIAS_GELU = 1, E_BIAS_DROPOUT_RESID = 2, E_ADD = 3, E_GELU_BWD = 4, E_SPLITK = 5 };
+enum Epi : int { E_STORE = 0, E_BIAS_GELU = 1, E_BIAS_DROPOUT_RESID = 2, E_ADD = 3, E_GELU_BWD = 4, E_SPLITK = 5, E_TOPK = 6 };
 
 struct Params {
   int M, N;                      // output rows / columns
@@ -70,6 +73,7 @@ struct Params {
   float p; const int* seed; uint32_t stream;        // dropout      BIAS_DROPOUT_RESID
   float* colacc; int col_tot; int col_off;          // GELU_BWD: replicas of [col_tot] floats, this vector at col_off
   float* sk_scratch; unsigned* sk_counters;         // SPLITK: [tiles][128 NCTA x BN] fp32 (zero between launches), [tiles]
+  float* cand_val; int* cand_idx; int cand_ld;      // TOPK: [M, cand_ld] candidates, 8 per (CTA, epilogue group)
   int* status;
 };
 
@@ -111,12 +115,12 @@ __global__ void __launch_bounds__(THREADS, 1)
 enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
                 const __grid_constant__ CUtensorMap tmF, const Params p) {
-  using C_ = Cfg<EPI != E_SPLITK>;
+  using C_ = Cfg<EPI != E_SPLITK && EPI != E_TOPK>;
   constexpr bool A_MN = (LAYOUT == L_TN);
   constexpr bool B_MN = (LAYOUT != L_NT);
   constexpr int FMT = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
   constexpr bool HAS_IN = (EPI == E_BIAS_DROPOUT_RESID || EPI == E_ADD || EPI == E_GELU_BWD);   // tile-shaped input R
-  constexpr bool STAGED = (EPI != E_SPLITK);                                                     // outputs through panels
+  constexpr bool STAGED = (EPI != E_SPLITK && EPI != E_TOPK);                                   // outputs through panels
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* panels = smem + RING_BYTES;                           // [N_PANELS][PANEL_BYTES], 1024-byte aligned
@@ -257,8 +261,31 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     if (EPI == E_BIAS_DROPOUT_RESID && p.p > 0.f) { seed = (uint32_t)(*p.seed); inv_keep = 1.f / (1.f - p.p); }
     int t_local = 0;
     uint32_t in_count = 0;                                // R panels fetched so far (parity of my_in_bar)
+    // TOPK: this thread's 8 best (value, column) of its row so far, sorted descending; cur_m = row block they belong to
+    float tv[8];
+    int ti[8];
+    int cur_m = -1;
+    const int slot = ((int)blockIdx.x * 2 + g) * 8;
     for (int item = unit; item < n_items; item += n_units, ++t_local) {
       const int tile = item / p.splits;
+      if (EPI == E_TOPK) {
+        const int mt = tile / p.n_n_tiles;
+        if (mt != cur_m) {
+          if (cur_m >= 0) {
+            const int frow = cur_m * (BM * NCTA) + (int)rank * BM + r;
+            if (frow < p.M && n_pan > 0) {
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                p.cand_val[(size_t)frow * p.cand_ld + slot + k] = tv[k];
+                p.cand_idx[(size_t)frow * p.cand_ld + slot + k] = ti[k];
+              }
+            }
+          }
+#pragma unroll
+          for (int k = 0; k < 8; ++k) { tv[k] = -3.0e38f; ti[k] = 0; }
+          cur_m = mt;
+        }
+      }
       const int m0 = (tile / p.n_n_tiles) * (BM * NCTA) + (int)rank * BM;
       const int n0 = (tile % p.n_n_tiles) * p.BN;
       const int row = m0 + r;
@@ -383,6 +410,30 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           }
         }
       }
+      if (EPI == E_TOPK) {
+        for (int pi = 0; pi < n_pan; ++pi) {
+#pragma unroll
+          for (int hc = 0; hc < 2; ++hc) {
+            float v[32];
+            tc::tmem_ld32(tbase + 64 * pi + 32 * hc, v);
+            const int c0 = n0 + g_col + 64 * pi + 32 * hc;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float x = v[j];
+              if (x > tv[7] && c0 + j < p.N) {           // strict: of equal values the lower column stays
+                tv[7] = x; ti[7] = c0 + j;
+#pragma unroll
+                for (int k = 7; k > 0; --k) {
+                  if (tv[k] > tv[k - 1]) {
+                    const float a = tv[k]; tv[k] = tv[k - 1]; tv[k - 1] = a;
+                    const int b = ti[k]; ti[k] = ti[k - 1]; ti[k - 1] = b;
+                  }
+                }
+              }
+            }
+          }
+        }
+      }
       if (EPI == E_SPLITK) {
         const uint32_t tsk = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * ACC_STRIDE + (uint32_t)(g * half_cols);
         for (int c0 = 0; c0 < half_cols; c0 += 32) {
@@ -456,6 +507,16 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
     }
     if (STAGED && elected) tc::tma_store_wait_read<0>();   // the stores have read shared memory; they complete before the grid does
+    if (EPI == E_TOPK && cur_m >= 0 && n_pan > 0) {
+      const int frow = cur_m * (BM * NCTA) + (int)rank * BM + r;
+      if (frow < p.M) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          p.cand_val[(size_t)frow * p.cand_ld + slot + k] = tv[k];
+          p.cand_idx[(size_t)frow * p.cand_ld + slot + k] = ti[k];
+        }
+      }
+    }
   }
   tc::tc_fence_before();
   __syncthreads();
@@ -538,7 +599,7 @@ template <typename T, int LAYOUT, int EPI, int NCTA>
 static int launch_enc_gemm(const Maps& m, const Params& p, int units, cudaStream_t st) {
   static bool attr_set = false;
   auto k = enc_gemm_kernel<T, LAYOUT, EPI, NCTA>;
-  constexpr int smem = Cfg<EPI != E_SPLITK>::kSmem;
+  constexpr int smem = Cfg<EPI != E_SPLITK && EPI != E_TOPK>::kSmem;
   if (!attr_set) {
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -5;
     attr_set = true;
@@ -574,6 +635,7 @@ static int dispatch_enc_gemm(int layout, int epi, const Maps& m, const Params& p
     if (epi == E_STORE) return launch_enc_gemm<T, L_NT, E_STORE, NCTA>(m, p, units, st);
     if (epi == E_BIAS_GELU) return launch_enc_gemm<T, L_NT, E_BIAS_GELU, NCTA>(m, p, units, st);
     if (epi == E_BIAS_DROPOUT_RESID) return launch_enc_gemm<T, L_NT, E_BIAS_DROPOUT_RESID, NCTA>(m, p, units, st);
+    if (epi == E_TOPK) return launch_enc_gemm<T, L_NT, E_TOPK, NCTA>(m, p, units, st);
   } else if (layout == L_NN) {
     if (epi == E_STORE) return launch_enc_gemm<T, L_NN, E_STORE, NCTA>(m, p, units, st);
     if (epi == E_ADD) return launch_enc_gemm<T, L_NN, E_ADD, NCTA>(m, p, units, st);
@@ -629,7 +691,7 @@ static Plan make_plan(int layout, int epi, int M, int N, int K, int bn_forced, i
         if (t_kb < 2.0 * bn) t_kb = 2.0 * bn;
         const int n_pan = bn >= 128 ? bn / 128 : 1;
         double tail;
-        if (epi == E_SPLITK) tail = 800.0 * n_pan;
+        if (epi == E_SPLITK || epi == E_TOPK) tail = 800.0 * n_pan;
         else if (epi == E_STORE) tail = 1200.0 * n_pan;
         else if (epi == E_BIAS_GELU) tail = 2400.0 * n_pan;
         else tail = 1200.0 + 2800.0 * (n_pan - 1);
@@ -707,6 +769,42 @@ RB_API int rb_enc_gemm(int dtype, int layout, int epi, const void* A, const void
     rc = bf16 ? dispatch_enc_gemm<__nv_bfloat16, 2>(layout, epi, m, p, units, st) : dispatch_enc_gemm<__half, 2>(layout, epi, m, p, units, st);
   else
     rc = bf16 ? dispatch_enc_gemm<__nv_bfloat16, 1>(layout, epi, m, p, units, st) : dispatch_enc_gemm<__half, 1>(layout, epi, m, p, units, st);
+  if (rc) return rc;
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+// Prediction: candidates for the top-k (k <= 8) of every row of X W^T without materialising the product.
+//   X [B, ldx >= D], W [Ls, ldw >= D] (16-bit, same dtype); cand_val / cand_idx [B, cand_ld] with
+//   cand_ld >= rb_xfc_topk8_width(): every (CTA, epilogue group) writes the 8 best (value, column of W) it met in
+//   the row into its own 8 entries; entries nobody writes must have been pre-filled with -inf by the caller.
+// The k best of a row's candidates are the k best of the row (k <= 8).
+RB_API int rb_xfc_topk8_width(void) { return sm_count() * 2 * 8; }
+
+RB_API int rb_xfc_topk8(int dtype, const void* X, const void* W, int B, int Ls, int D, int ldx, int ldw, float* cand_val,
+                        int* cand_idx, int cand_ld, int* status, cudaStream_t st) {
+  if (dtype != RB_BF16 && dtype != RB_F16) return -1;
+  if (B < 1 || Ls < 1 || D < 1 || ldx % 8 || ldw % 8 || cand_ld < rb_xfc_topk8_width()) return -3;
+  const bool bf16 = dtype == RB_BF16;
+  const Plan pl = make_plan(L_NT, E_TOPK, B, Ls, D, 0, 0);
+  const int BN = pl.bn, b_rows = BN / pl.ncta;
+  Maps m;
+  int rc = tc::make_tmap_2d(&m.a, X, B, D, ldx, 64, BM, bf16);
+  if (rc) return rc;
+  rc = tc::make_tmap_2d(&m.b, W, Ls, D, ldw, 64, b_rows, bf16);
+  if (rc) return rc;
+  m.c = m.a; m.r = m.a; m.f = m.a;
+  Params p{};
+  p.M = B; p.N = Ls; p.BN = BN;
+  p.n_m_tiles = (B + BM * pl.ncta - 1) / (BM * pl.ncta); p.n_n_tiles = (Ls + BN - 1) / BN;
+  p.kb_total = (D + BK - 1) / BK; p.splits = 1; p.kb_per_split = p.kb_total;
+  p.cand_val = cand_val; p.cand_idx = cand_idx; p.cand_ld = cand_ld; p.status = status;
+  const long n_items = (long)p.n_m_tiles * p.n_n_tiles;
+  const int max_units = sm_count() / pl.ncta;
+  const int units = n_items < max_units ? (int)n_items : max_units;
+  rc = pl.ncta == 2
+           ? (bf16 ? dispatch_enc_gemm<__nv_bfloat16, 2>(L_NT, E_TOPK, m, p, units, st) : dispatch_enc_gemm<__half, 2>(L_NT, E_TOPK, m, p, units, st))
+           : (bf16 ? dispatch_enc_gemm<__nv_bfloat16, 1>(L_NT, E_TOPK, m, p, units, st) : dispatch_enc_gemm<__half, 1>(L_NT, E_TOPK, m, p, units, st));
   if (rc) return rc;
   RB_LAUNCH_CHECK();
   return 0;

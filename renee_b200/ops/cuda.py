@@ -553,12 +553,36 @@ def topk_rows(Z, n, k, label0, out_val, out_idx):
     _call("rb_topk_rows", _p(Z), _I(ldZ), _I(B), _I(n), _I(k), _I(label0), _p(out_val), _p(out_idx), _stream())
 
 
+def xfc_topk8(W, X, k):
+    """Top-k (k <= 8) of every row of ``X Wᵀ`` with the selection fused into the GEMM epilogue: each epilogue
+    thread of the persistent tcgen05 GEMM keeps the 8 best entries of its row over all label tiles its CTA
+    visits, so the ``[B, Ls]`` logits are never written; the few thousand candidates per row are then reduced by
+    the row-selection kernel.  Returns ``(values [B, k] fp32 descending, label ids [B, k] int64)``."""
+    B, D = X.shape
+    Ls = W.shape[0]
+    width = int(lib().rb_xfc_topk8_width())
+    cv = torch.full((B, width), -3.0e38, dtype=torch.float32, device=X.device)
+    ci = torch.zeros(B, width, dtype=torch.int32, device=X.device)
+    ws = workspace(X.device)
+    _call("rb_xfc_topk8", _I(DT[X.dtype]), _p(X), _p(W), _I(B), _I(Ls), _I(D), _I(X.stride(0)), _I(W.stride(0)), _p(cv),
+          _p(ci), _I(width), _p(ws.status), _stream())
+    vals = torch.empty(B, k, dtype=torch.float32, device=X.device)
+    pos = torch.empty(B, k, dtype=torch.int32, device=X.device)
+    topk_rows(cv, width, k, 0, vals, pos)
+    idx = torch.gather(ci, 1, pos.long())
+    v, order = torch.sort(vals, dim=1, descending=True)
+    return v, torch.gather(idx, 1, order).long()
+
+
 def xfc_topk(xfc, X, k):
-    """Local top-k of ``X Wᵀ`` over this rank's shard: per label chunk, the tcgen05 logits GEMM writes fp32
-    logits batch-major into an L2-sized buffer and a radix-select kernel extracts each row's k best; the
-    per-chunk candidates (k each) are merged at the end."""
+    """Local top-k of ``X Wᵀ`` over this rank's shard.  ``k <= 8`` (evaluation during training uses 5): fused into
+    the GEMM epilogue (:func:`xfc_topk8`).  Larger ``k`` (100 for the final evaluation): per label chunk, the tcgen05
+    logits GEMM writes fp32 logits batch-major into an L2-sized buffer and a radix-select kernel extracts each
+    row's k best; the per-chunk candidates (k each) are merged at the end."""
     B, D = X.shape
     k_eff = min(k, xfc.Ls)
+    if k_eff <= 8 and D % 64 == 0 and os.environ.get("RENEE_B200_FUSED_TOPK", "1") != "0":
+        return xfc_topk8(xfc.W, X, k_eff)
     chunk = min(xfc.chunk, max(128, (32 << 20) // (4 * B) // 128 * 128))
     ldZ = (min(chunk, xfc.Ls) + 7) // 8 * 8
     Z = torch.empty(B, ldZ, dtype=torch.float32, device=X.device)

@@ -203,3 +203,21 @@ def test_flat_encoder_on_own_gemms_matches_library_gemms(S, b):
         scale = float(y.abs().max().clamp_min(1e-4))
         err = float((x - y).abs().max())
         assert err <= 6e-2 * scale + 1e-3, f"{name}: max err {err} at scale {scale}"
+
+
+@pytest.mark.parametrize("B,D,Ls,k", [(256, 768, 16384, 5), (100, 128, 40000, 8), (512, 768, 5003 * 8, 3), (33, 64, 1000, 5)])
+def test_fused_topk8_equals_torch_topk(B, D, Ls, k):
+    """The running top-8 in the GEMM epilogue (logits never written) against ``torch.topk`` of the fp32 product of
+    the same fp16 operands: same values; same labels wherever the k-th value is not tied."""
+    torch.manual_seed(B + Ls)
+    X = (torch.randn(B, D, device=dev()) * 0.5).half()
+    W = (torch.randn(Ls, D, device=dev()) * 0.05).half()
+    v, i = cu().xfc_topk8(W, X, k)
+    Z = X.float() @ W.float().t()
+    vr, ir = torch.topk(Z, k, dim=1)
+    torch.testing.assert_close(v, vr, rtol=2e-3, atol=2e-3)           # fp32 accumulation order differs
+    assert int(i.max()) < Ls and int(i.min()) >= 0
+    # the labels are the right ones: their exact logits equal the reference top-k values
+    torch.testing.assert_close(torch.gather(Z, 1, i), vr, rtol=2e-3, atol=2e-3)
+    assert (i == ir).float().mean() > 0.98
+    cu().check_status()
