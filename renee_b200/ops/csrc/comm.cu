@@ -73,6 +73,29 @@ __global__ void __launch_bounds__(256) ag_push_kernel(const float* __restrict__ 
   }
 }
 
+// ------------------------------------------------------------------------------------ generic all-gather push
+// grid = (G, nblk).  Block (peer, j) copies its share of this rank's n16 16-byte words into `peer`'s buffer at word
+// offset slot16, then the last block per peer raises flag [flag_base + my_rank] there.  Used for the cross-rank merge
+// of top-k candidates at prediction time (the reference: two NCCL all-gathers per batch, dl_base.py:774-775).
+__global__ void __launch_bounds__(256) peer_gather_kernel(const uint4* __restrict__ src, long long n16, PeerPtrs dst,
+                                                          long long slot16, PeerPtrs flags, int flag_base, int my_rank,
+                                                          StepTag tag, unsigned* __restrict__ counters) {
+  const int peer = blockIdx.x;
+  uint4* out = reinterpret_cast<uint4*>(dst.p[peer]) + slot16;
+  for (long long i = (long long)blockIdx.y * blockDim.x + threadIdx.x; i < n16; i += (long long)gridDim.y * blockDim.x)
+    out[i] = src[i];
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned done = atomicAdd(counters + peer, 1u);
+    if (done == gridDim.y - 1) {
+      counters[peer] = 0u;
+      __threadfence_system();
+      st_release_sys(reinterpret_cast<uint32_t*>(flags.p[peer]) + flag_base + my_rank, tag.value());
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------ reduce-scatter pull
 // grid = rows of this rank; de[r, :] = dropout_bwd( sum_q partial_q[row0 + r, :] )
 __global__ void __launch_bounds__(128) rs_pull_kernel(PeerPtrs partials, int G, int row0, int b, int D,
@@ -322,6 +345,19 @@ RB_API int rb_ag_push(const float* e, int b, int D, float p, const int* seed, un
   dim3 grid(G, nblk);
   ag_push_kernel<<<grid, 256, 0, st>>>(e, b, D, p, seed, stream_id, make_ptrs(xbufs, G), row0, make_ptrs(flags, G),
                                        flag_base, my_rank, StepTag{step_ptr, 1u, 0u}, counters);
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+RB_API int rb_peer_gather(const void* src, long long bytes, void* const* dst, long long slot_bytes, void* const* flags,
+                          int flag_base, int my_rank, int G, const unsigned* step_ptr, unsigned* counters, cudaStream_t st) {
+  if (G > kMaxPeers || bytes % 16 || slot_bytes % 16 || bytes < 16) return -3;
+  const long long n16 = bytes / 16;
+  int nblk = (int)((n16 + 255) / 256);
+  if (nblk > 16) nblk = 16;
+  dim3 grid(G, nblk);
+  peer_gather_kernel<<<grid, 256, 0, st>>>((const uint4*)src, n16, make_ptrs(dst, G), slot_bytes / 16, make_ptrs(flags, G),
+                                           flag_base, my_rank, StepTag{step_ptr, 1u, 0u}, counters);
   RB_LAUNCH_CHECK();
   return 0;
 }

@@ -13,6 +13,10 @@
 //              ADD                  C = acc + R                                      (dgrad joined with the residual gradient)
 //              GELU_BWD             C = acc * gelu'(R) ;  column sums of C -> bias gradient accumulators
 //              SPLITK               fp32 partials reduced in L2, the last CTA of a tile converts and stores
+//              SIGMOID_POS          C = sigmoid(acc) - Y: the classifier's logit gradient; Y from a label-sorted list of
+//                                   positives applied to the staged tile in shared memory before it is stored
+//              DX                   dX += scale * acc by vector reductions into an fp32 matrix (contraction over the
+//                                   labels of a chunk, split over the CTAs); the last CTA raises the peers' flags
 //              TOPK                 nothing is stored: every epilogue thread keeps the 8 largest entries of its row
 //                                   over all the tiles its CTA visits and writes them as candidates at the end
 //                                   (prediction: X W^T is never materialised; parity: dl_base.py:745-756)
@@ -36,7 +40,7 @@
 //
 // Every wait is bounded (tc.cuh): a protocol error ends with a status word, never with a hang.
 #include <type_traits>
-#include "tc.cuh"
+#include "peer.cuh"
 
 namespace rb {
 namespace eg {
@@ -61,7 +65,7 @@ template <bool STAGED> struct Cfg {
 };
 
 enum Layout : int { L_NT = 0, L_NN = 1, L_TN = 2 };
-enum Epi : int { E_STORE = 0, E_BIAS_GELU = 1, E_BIAS_DROPOUT_RESID = 2, E_ADD = 3, E_GELU_BWD = 4, E_SPLITK = 5, E_TOPK = 6 };
+enum Epi : int { E_STORE = 0, E_BIAS_GELU = 1, E_BIAS_DROPOUT_RESID = 2, E_ADD = 3, E_GELU_BWD = 4, E_SPLITK = 5, E_TOPK = 6, E_SIGMOID_POS = 7, E_DX = 8 };
 
 struct Params {
   int M, N;                      // output rows / columns
@@ -74,6 +78,12 @@ struct Params {
   float* colacc; int col_tot; int col_off;          // GELU_BWD: replicas of [col_tot] floats, this vector at col_off
   float* sk_scratch; unsigned* sk_counters;         // SPLITK: [tiles][128 NCTA x BN] fp32 (zero between launches), [tiles]
   float* cand_val; int* cand_idx; int cand_ld;      // TOPK: [M, cand_ld] candidates, 8 per (CTA, epilogue group)
+  // SIGMOID_POS (classifier logits + gradient): label-sorted positives, label id of row 0, all-gather flags to wait for
+  const int* pos_rows; const int* pos_labels; const int* nnz_ptr; int label0;
+  const uint32_t* wait_flags; int wait_n; const uint32_t* step_ptr;
+  // DX (classifier input gradient): fp32 accumulation target, loss scale, completion signal to the peers
+  float* dX; int ldX; const float* hp;
+  unsigned* done_counter; void* peer_flags[16]; int n_peers; int flag_index;
   int* status;
 };
 
@@ -115,12 +125,12 @@ __global__ void __launch_bounds__(THREADS, 1)
 enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
                 const __grid_constant__ CUtensorMap tmF, const Params p) {
-  using C_ = Cfg<EPI != E_SPLITK && EPI != E_TOPK>;
+  using C_ = Cfg<EPI != E_SPLITK && EPI != E_TOPK && EPI != E_DX>;
   constexpr bool A_MN = (LAYOUT == L_TN);
   constexpr bool B_MN = (LAYOUT != L_NT);
   constexpr int FMT = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
   constexpr bool HAS_IN = (EPI == E_BIAS_DROPOUT_RESID || EPI == E_ADD || EPI == E_GELU_BWD);   // tile-shaped input R
-  constexpr bool STAGED = (EPI != E_SPLITK && EPI != E_TOPK);                                   // outputs through panels
+  constexpr bool STAGED = (EPI != E_SPLITK && EPI != E_TOPK && EPI != E_DX);                    // outputs through panels
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* panels = smem + RING_BYTES;                           // [N_PANELS][PANEL_BYTES], 1024-byte aligned
@@ -174,6 +184,14 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     // ---------------- TMA producer: one continuous stream of (item, k block) stages
     int s = 0;
     uint32_t ph = 0;
+    if (EPI == E_SIGMOID_POS && p.wait_flags != nullptr) {
+      // all-gather prologue: every rank has pushed its rows of X into this GPU's buffer and raised its flag; the
+      // loads below go through the async proxy, hence the proxy fence after the acquire
+      const uint32_t want = *p.step_ptr;
+      for (int q = 0; q < p.wait_n; ++q)
+        if (!wait_flag(p.wait_flags + q, want, p.status, 100 + q)) aborted = true;
+      asm volatile("fence.proxy.async;" ::: "memory");
+    }
     for (int item = unit; item < n_items && !aborted; item += n_units) {
       const int tile = item / p.splits, split = item - tile * p.splits;
       const int m0 = (tile / p.n_n_tiles) * (BM * NCTA) + (int)rank * BM;
@@ -335,6 +353,9 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               if (EPI == E_STORE) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) o[j] = a[j];
+              } else if (EPI == E_SIGMOID_POS) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = (c + j < p.N) ? 1.f / (1.f + __expf(-a[j])) : 0.f;
               } else if (EPI == E_BIAS_GELU) {
                 float b[8];
                 if (c < p.N) unpack8<T>(__ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.bias) + c)), b);
@@ -386,6 +407,28 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               if (c < p.N) atomicAdd(p.colacc + (size_t)(blockIdx.x % kColReplicas) * p.col_tot + p.col_off + c, colsum[hc]);
             }
           }
+          if (EPI == E_SIGMOID_POS && p.pos_labels != nullptr) {
+            // subtract 1 at the tile's positives while the tile is still in shared memory: entries of the label-sorted
+            // list whose label is one of this CTA's 128 rows and whose batch row is one of the panel's 64 columns
+            asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");      // every row of the panel is written
+            const int nnz = *p.nnz_ptr;
+            const int lab_lo = p.label0 + m0;
+            const int lab_hi = p.label0 + min(m0 + BM, p.M);
+            int lo = 0, hi = nnz;
+            while (lo < hi) { const int mid = (lo + hi) >> 1; if (p.pos_labels[mid] < lab_lo) lo = mid + 1; else hi = mid; }
+            const int e0 = lo;
+            hi = nnz;
+            while (lo < hi) { const int mid = (lo + hi) >> 1; if (p.pos_labels[mid] < lab_hi) lo = mid + 1; else hi = mid; }
+            const int e1 = lo;
+            for (int e = e0 + (int)(threadIdx.x - 64 - 128 * g); e < e1; e += 128) {
+              const int bcol = p.pos_rows[e] - pcol;
+              if (bcol >= 0 && bcol < 64 && pcol + bcol < p.N) {
+                const int prow = p.pos_labels[e] - lab_lo;
+                T* cell = reinterpret_cast<T*>(pan + panel_off(prow, bcol >> 3)) + (bcol & 7);
+                *cell = from_f<T>(to_f(*cell) - 1.f);      // duplicates are removed by the collator: one writer per cell
+              }
+            }
+          }
           tc::fence_proxy_async();                 // generic-proxy writes of the panel before the async-proxy store
           asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
           if (elected) {
@@ -431,6 +474,22 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
               }
             }
+          }
+        }
+      }
+      if (EPI == E_DX) {
+        const float scale = p.hp[HP_SCALE];
+        const uint32_t tdx = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * ACC_STRIDE + (uint32_t)(g * half_cols);
+        for (int c0 = 0; c0 < half_cols; c0 += 32) {
+          float v[32];
+          tc::tmem_ld32(tdx + c0, v);
+          const int col0 = n0 + g * half_cols + c0;
+          if (row < p.M) {
+            float* d = p.dX + (size_t)row * p.ldX + col0;
+#pragma unroll
+            for (int j4 = 0; j4 < 8; ++j4)
+              if (col0 + 4 * j4 < p.N)
+                red_add_f32x4(d + 4 * j4, v[4 * j4] * scale, v[4 * j4 + 1] * scale, v[4 * j4 + 2] * scale, v[4 * j4 + 3] * scale);
           }
         }
       }
@@ -507,6 +566,20 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
     }
     if (STAGED && elected) tc::tma_store_wait_read<0>();   // the stores have read shared memory; they complete before the grid does
+    if (EPI == E_DX && p.done_counter != nullptr) {
+      // reduce-scatter epilogue: the last CTA of this rank's dX GEMM tells every rank that the partial sums in this
+      // rank's buffer are complete
+      __threadfence_system();
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (threadIdx.x == 64) {
+        if (atomicAdd(p.done_counter, 1u) == gridDim.x - 1) {
+          *p.done_counter = 0u;
+          __threadfence_system();
+          const uint32_t tagv = *p.step_ptr;
+          for (int q = 0; q < p.n_peers; ++q) st_release_sys(reinterpret_cast<uint32_t*>(p.peer_flags[q]) + p.flag_index, tagv);
+        }
+      }
+    }
     if (EPI == E_TOPK && cur_m >= 0 && n_pan > 0) {
       const int frow = cur_m * (BM * NCTA) + (int)rank * BM + r;
       if (frow < p.M) {
@@ -599,7 +672,7 @@ template <typename T, int LAYOUT, int EPI, int NCTA>
 static int launch_enc_gemm(const Maps& m, const Params& p, int units, cudaStream_t st) {
   static bool attr_set = false;
   auto k = enc_gemm_kernel<T, LAYOUT, EPI, NCTA>;
-  constexpr int smem = Cfg<EPI != E_SPLITK && EPI != E_TOPK>::kSmem;
+  constexpr int smem = Cfg<EPI != E_SPLITK && EPI != E_TOPK && EPI != E_DX>::kSmem;
   if (!attr_set) {
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -5;
     attr_set = true;
@@ -636,12 +709,14 @@ static int dispatch_enc_gemm(int layout, int epi, const Maps& m, const Params& p
     if (epi == E_BIAS_GELU) return launch_enc_gemm<T, L_NT, E_BIAS_GELU, NCTA>(m, p, units, st);
     if (epi == E_BIAS_DROPOUT_RESID) return launch_enc_gemm<T, L_NT, E_BIAS_DROPOUT_RESID, NCTA>(m, p, units, st);
     if (epi == E_TOPK) return launch_enc_gemm<T, L_NT, E_TOPK, NCTA>(m, p, units, st);
+    if (epi == E_SIGMOID_POS) return launch_enc_gemm<T, L_NT, E_SIGMOID_POS, NCTA>(m, p, units, st);
   } else if (layout == L_NN) {
     if (epi == E_STORE) return launch_enc_gemm<T, L_NN, E_STORE, NCTA>(m, p, units, st);
     if (epi == E_ADD) return launch_enc_gemm<T, L_NN, E_ADD, NCTA>(m, p, units, st);
     if (epi == E_GELU_BWD) return launch_enc_gemm<T, L_NN, E_GELU_BWD, NCTA>(m, p, units, st);
   } else if (layout == L_TN) {
     if (epi == E_SPLITK) return launch_enc_gemm<T, L_TN, E_SPLITK, NCTA>(m, p, units, st);
+    if (epi == E_DX) return launch_enc_gemm<T, L_TN, E_DX, NCTA>(m, p, units, st);
   }
   return -4;
 }
@@ -676,11 +751,16 @@ static Plan make_plan(int layout, int epi, int M, int N, int K, int bn_forced, i
       if (!bn_forced && bn > 64 && bn / 2 >= N) continue;            // a narrower tile already covers every column
       const int tiles = ((M + BM * ncta - 1) / (BM * ncta)) * ((N + bn - 1) / bn);
       const int units = sms / ncta;
-      const int max_splits = layout == L_TN ? (kb < 16 ? kb : 16) : 1;
-      for (int splits = 1; splits <= max_splits; splits *= 2) {
+      int max_splits = layout == L_TN ? (kb < 16 ? kb : 16) : 1;
+      int first_split = 1;
+      if (epi == E_DX) {                      // partial sums are reduced into the output directly: split as far as the units go
+        first_split = units / tiles < 1 ? 1 : (units / tiles > kb ? kb : units / tiles);
+        max_splits = first_split;
+      }
+      for (int splits = first_split; splits <= max_splits; splits = (splits == max_splits ? max_splits + 1 : splits * 2)) {
         const int kb_per = (kb + splits - 1) / splits;
         const int eff_splits = (kb + kb_per - 1) / kb_per;
-        if (eff_splits != splits && splits > 1) continue;
+        if (eff_splits != splits && splits > 1 && epi != E_DX) continue;
         const long items = (long)tiles * eff_splits;
         const long rounds = (items + units - 1) / units;
         const double busy = (double)(items < units ? items : units) * ncta / sms;      // fraction of the SMs at work
@@ -691,11 +771,11 @@ static Plan make_plan(int layout, int epi, int M, int N, int K, int bn_forced, i
         if (t_kb < 2.0 * bn) t_kb = 2.0 * bn;
         const int n_pan = bn >= 128 ? bn / 128 : 1;
         double tail;
-        if (epi == E_SPLITK || epi == E_TOPK) tail = 800.0 * n_pan;
+        if (epi == E_SPLITK || epi == E_TOPK || epi == E_DX) tail = 800.0 * n_pan;
         else if (epi == E_STORE) tail = 1200.0 * n_pan;
         else if (epi == E_BIAS_GELU) tail = 2400.0 * n_pan;
         else tail = 1200.0 + 2800.0 * (n_pan - 1);
-        const double cost = 3000.0 + rounds * (kb_per * t_kb) + tail + (eff_splits > 1 ? 10000.0 : 0.0);
+        const double cost = 3000.0 + rounds * (kb_per * t_kb) + tail + (eff_splits > 1 && epi != E_DX ? 10000.0 : 0.0);
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = Plan{ncta, bn, eff_splits, tiles}; }
       }
     }
@@ -805,6 +885,77 @@ RB_API int rb_xfc_topk8(int dtype, const void* X, const void* W, int B, int Ls, 
   rc = pl.ncta == 2
            ? (bf16 ? dispatch_enc_gemm<__nv_bfloat16, 2>(L_NT, E_TOPK, m, p, units, st) : dispatch_enc_gemm<__half, 2>(L_NT, E_TOPK, m, p, units, st))
            : (bf16 ? dispatch_enc_gemm<__nv_bfloat16, 1>(L_NT, E_TOPK, m, p, units, st) : dispatch_enc_gemm<__half, 1>(L_NT, E_TOPK, m, p, units, st));
+  if (rc) return rc;
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+template <int DUMMY = 0>
+static int launch_planned(const Plan& pl, bool bf16, int layout, int epi, const Maps& m, Params& p, int K, cudaStream_t st) {
+  p.BN = pl.bn;
+  p.n_m_tiles = (p.M + BM * pl.ncta - 1) / (BM * pl.ncta); p.n_n_tiles = (p.N + pl.bn - 1) / pl.bn;
+  p.kb_total = (K + BK - 1) / BK;
+  p.splits = pl.splits;
+  p.kb_per_split = (p.kb_total + p.splits - 1) / p.splits;
+  const long n_items = (long)p.n_m_tiles * p.n_n_tiles * p.splits;
+  int max_units = sm_count() / pl.ncta;
+  if (g_max_units > 0 && g_max_units < max_units) max_units = g_max_units;
+  const int units = n_items < max_units ? (int)n_items : max_units;
+  return pl.ncta == 2
+             ? (bf16 ? dispatch_enc_gemm<__nv_bfloat16, 2>(layout, epi, m, p, units, st) : dispatch_enc_gemm<__half, 2>(layout, epi, m, p, units, st))
+             : (bf16 ? dispatch_enc_gemm<__nv_bfloat16, 1>(layout, epi, m, p, units, st) : dispatch_enc_gemm<__half, 1>(layout, epi, m, p, units, st));
+}
+
+// Classifier logits + gradient on the persistent GEMM: Gt[Lc, ldG] = sigmoid(W X^T) - Y for the fp16 label chunk
+// W[Lc, D] and the gathered embeddings X[B, D]; columns B .. ldG of Gt are written as zeros.  Positives: label-sorted
+// (row, label) pairs, labels numbered from label0 at row 0 of W; they are subtracted in shared memory before the tile
+// is stored.  wait_flags != null: the loads wait until flags[0 .. wait_n) have reached *step_ptr (all-gather landed).
+// Replaces, in the reference, torch.matmul + sigmoid_ + index_put_ (dl_base.py:572, 593-594) / the CUTLASS
+// sigmoid-GEMM (xfc_gemm_kernel.cu:59-100).
+RB_API int rb_xfc_logits_grad_v2(const void* W, int Lc, int D, const void* X, int B, void* Gt, int ldG, const int* pos_rows,
+                                 const int* pos_labels, const int* nnz_ptr, int label0, const unsigned* wait_flags,
+                                 int wait_n, const unsigned* step_ptr, int* status, cudaStream_t st) {
+  if (D % 8 || ldG % 8 || Lc < 1 || B < 1 || ldG < B) return -3;
+  const Plan pl = make_plan(L_NT, E_SIGMOID_POS, Lc, B, D, 0, 0);
+  Maps m;
+  int rc = tc::make_tmap_2d(&m.a, W, Lc, D, D, 64, BM, false);
+  if (rc) return rc;
+  rc = tc::make_tmap_2d(&m.b, X, B, D, D, 64, pl.bn / pl.ncta, false);
+  if (rc) return rc;
+  rc = tc::make_tmap_2d(&m.c, Gt, Lc, ldG, ldG, 64, BM, false);
+  if (rc) return rc;
+  m.r = m.c; m.f = m.c;
+  Params p{};
+  p.M = Lc; p.N = B; p.status = status;
+  p.pos_rows = pos_rows; p.pos_labels = pos_labels; p.nnz_ptr = nnz_ptr; p.label0 = label0;
+  p.wait_flags = wait_flags; p.wait_n = wait_n; p.step_ptr = step_ptr;
+  rc = launch_planned(pl, false, L_NT, E_SIGMOID_POS, m, p, D, st);
+  if (rc) return rc;
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+// dX[B, D] += hp[SCALE] * Gt^T W over the label chunk (fp32, vector reductions; dX zeroed before the first chunk).
+// done_counter != null: the last CTA stores *step_ptr into word flag_index of every peer's flag array.
+RB_API int rb_xfc_dx_v2(const void* Gt, int ldG, const void* W, int Lc, int D, int B, float* dX, const float* hp,
+                        unsigned* done_counter, void* const* peer_flags, int n_peers, int flag_index,
+                        const unsigned* step_ptr, int* status, cudaStream_t st) {
+  if (D % 8 || ldG % 8 || Lc < 1 || B < 1 || n_peers > 16) return -3;
+  const Plan pl = make_plan(L_TN, E_DX, B, D, Lc, 0, 0);
+  Maps m;
+  int rc = tc::make_tmap_2d(&m.a, Gt, Lc, B, ldG, 64, 64, false);
+  if (rc) return rc;
+  rc = tc::make_tmap_2d(&m.b, W, Lc, D, D, 64, 64, false);
+  if (rc) return rc;
+  m.c = m.a; m.r = m.a; m.f = m.a;
+  Params p{};
+  p.M = B; p.N = D; p.status = status;
+  p.dX = dX; p.ldX = D; p.hp = hp;
+  if (done_counter != nullptr) {
+    p.done_counter = done_counter; p.n_peers = n_peers; p.flag_index = flag_index; p.step_ptr = step_ptr;
+    for (int q = 0; q < n_peers; ++q) p.peer_flags[q] = peer_flags[q];
+  }
+  rc = launch_planned(pl, false, L_TN, E_DX, m, p, Lc, st);
   if (rc) return rc;
   RB_LAUNCH_CHECK();
   return 0;

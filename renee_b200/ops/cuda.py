@@ -463,6 +463,34 @@ def xfc_logits_grad(W, X, Gt, ldG, pos_rows, pos_labels, nnz, label0, loss_acc=N
           _p(nnz), _I(label0), _p(loss_acc), _p(raw_out), _p(wf), _I(wn), _p(wstep), _p(ws.status), _stream())
 
 
+def xfc_v2() -> bool:
+    """The classifier's logits+gradient and dX GEMMs run on the persistent CTA-pair GEMM of ``gemm.cu`` (positives
+    applied to the staged tile in shared memory, dX by scaled vector reductions); ``RENEE_B200_XFC_V2=0`` selects the
+    one-tile-per-CTA kernels of ``xfc.cu`` instead.  Steps that sample the loss always use the latter (its epilogue
+    carries the loss partial sums)."""
+    return os.environ.get("RENEE_B200_XFC_V2", "1") != "0"
+
+
+def xfc_logits_grad_v2(W, X, Gt, ldG, pos_rows, pos_labels, nnz, label0, wait=None):
+    Lc, D = W.shape
+    B = X.shape[0]
+    ws = workspace(W.device)
+    wf, wn, wstep = (wait if wait is not None else (None, 0, None))
+    _call("rb_xfc_logits_grad_v2", _p(W), _I(Lc), _I(D), _p(X), _I(B), _p(Gt), _I(ldG), _p(pos_rows), _p(pos_labels), _p(nnz),
+          _I(label0), _p(wf), _I(wn), _p(wstep), _p(ws.status), _stream())
+
+
+def xfc_dx_v2(Gt, ldG, W, B, dX, hp_buf, signal=None):
+    Lc, D = W.shape
+    ws = workspace(W.device)
+    if signal is None:
+        cnt, ptrs, n, idx, step = None, None, 0, 0, None
+    else:
+        cnt, ptrs, n, idx, step = signal
+    _call("rb_xfc_dx_v2", _p(Gt), _I(ldG), _p(W), _I(Lc), _I(D), _I(B), _p(dX), _p(hp_buf), _p(cnt),
+          ptrs if ptrs is not None else _VP(0), _I(n), _I(idx), _p(step), _p(ws.status), _stream())
+
+
 def set_xfc_persistent(on: bool) -> None:
     """Chooses the persistent logits kernel (one CTA per SM walking the tiles, epilogue of tile i under the main
     loop of tile i + 1) for label chunks with more 128-label tiles than SMs.  Off by default."""
@@ -530,13 +558,20 @@ def xfc_step(xfc, X, pos_rows, pos_labels, nnz, dX_out, hp, mo, wd, want_loss, w
     for ci, l0 in enumerate(chunks):
         l1 = min(xfc.Ls, l0 + xfc.chunk)
         Wc, Mc = xfc.W[l0:l1], xfc.M[l0:l1]
-        xfc_logits_grad(Wc, X, Gt, ldG, pos_rows, pos_labels, nnz, l0, loss_acc=loss, wait=wait if ci == 0 else None)
+        v2 = xfc_v2() and not want_loss and D % 64 == 0
+        if v2:
+            xfc_logits_grad_v2(Wc, X, Gt, ldG, pos_rows, pos_labels, nnz, l0, wait=wait if ci == 0 else None)
+        else:
+            xfc_logits_grad(Wc, X, Gt, ldG, pos_rows, pos_labels, nnz, l0, loss_acc=loss, wait=wait if ci == 0 else None)
         if want_loss and ci == 0:
             # minus the logits at the positives, taken before any chunk's weights are updated (and after
             # the first GEMM's wait, so X is complete)
             _call("rb_xfc_pos_logit_sum", _p(xfc.W), _p(X), _I(D), _p(pos_rows), _p(pos_labels), _p(nnz), _p(loss),
                   _stream())
-        xfc_dx(Gt, ldG, Wc, B, dX_out, hp.buf, dx_splits(B, D, l1 - l0), signal=signal if ci == len(chunks) - 1 else None)
+        if v2:
+            xfc_dx_v2(Gt, ldG, Wc, B, dX_out, hp.buf, signal=signal if ci == len(chunks) - 1 else None)
+        else:
+            xfc_dx(Gt, ldG, Wc, B, dX_out, hp.buf, dx_splits(B, D, l1 - l0), signal=signal if ci == len(chunks) - 1 else None)
         if side_stream is not None and ci == len(chunks) - 1:
             main = torch.cuda.current_stream()
             side_stream.wait_stream(main)
@@ -658,6 +693,14 @@ def ag_push(e, p, rng, stream_id, xbuf_ptrs, row0, flag_ptrs, flag_base, my_rank
     b, D = e.shape
     _call("rb_ag_push", _p(e), _I(b), _I(D), _F(p), _p(rng.dev), _U(stream_id), xbuf_ptrs, _I(row0), flag_ptrs,
           _I(flag_base), _I(my_rank), _I(G), _p(step), _p(counters), _stream())
+
+
+def peer_gather(src, dst_ptrs, slot_bytes, flag_ptrs, flag_base, my_rank, G, step, counters):
+    """Copies ``src`` (contiguous, a multiple of 16 bytes) into every rank's buffer at byte offset ``slot_bytes`` and
+    raises this rank's flag of class ``flag_base`` there."""
+    nbytes = src.numel() * src.element_size()
+    _call("rb_peer_gather", _p(src), _LL(nbytes), dst_ptrs, _LL(slot_bytes), flag_ptrs, _I(flag_base), _I(my_rank), _I(G),
+          _p(step), _p(counters), _stream())
 
 
 def rs_pull(partial_ptrs, G, row0, b, D, de, my_flags, step, p, rng, stream_id):

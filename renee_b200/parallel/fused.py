@@ -45,7 +45,7 @@ from .collectives import TorchCollectives
 from .dist import DistContext
 
 # word offsets of the flag classes inside the symmetric flag array (16 words each)
-F_AG, F_RS, F_ARA, F_ARB, F_FOUND, F_ARC = 0, 16, 32, 48, 64, 80
+F_AG, F_RS, F_ARA, F_ARB, F_FOUND, F_ARC, F_EV = 0, 16, 32, 48, 64, 80, 96
 FLAG_WORDS = 128
 
 
@@ -333,6 +333,49 @@ class PeerCollectives(TorchCollectives):
         de = bufs["de"][: e - s]
         cu.rs_pull(self._dx_ptrs[self.parity], self.G, s, e - s, self.D, de, self.flags[F_RS:], self.step, p, rng, stream_id)
         return de
+
+    # ------------------------------------------------------------------ prediction: cross-rank top-k merge
+    def merge_topk(self, vals: torch.Tensor, idxs: torch.Tensor, k: int):
+        """``vals/idxs [n, k]`` per rank (global label ids) → global top-k on every rank, over peer memory: every rank
+        stores its candidates (values and ids packed in one ``[n, 2k]`` block) into slot ``rank`` of every rank's
+        buffer and raises a flag; after all flags one selection kernel picks the k best of the ``G k`` candidates
+        of a row.  Buffers alternate by call parity (a rank can be at most one call ahead of a peer)."""
+        from ..ops import cuda as cu
+        if self.G == 1 or not vals.is_cuda:
+            return super().merge_topk(vals, idxs, k)
+        n, kk = vals.shape
+        width = (2 * kk + 3) // 4 * 4                                   # floats per row, a multiple of 16 bytes
+        need = n * width
+        if getattr(self, "_ev_cap", 0) < need:
+            cap = max(need, 256 * 256)
+            self._ev_buf, self._ev_ptrs = [], []
+            for _ in range(2):
+                t, ptrs = self._symm(self.G * cap, torch.float32, name="eval.topk")
+                self._ev_buf.append(t)
+                self._ev_ptrs.append(cu.ptr_array(ptrs))
+            self._ev_cap = cap
+            self._ev_step = torch.zeros(1, dtype=torch.int32, device=self.ctx.device)
+            self._ev_calls = 0
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)
+        self._ev_calls += 1
+        par = self._ev_calls & 1
+        pack = torch.zeros(n, width, dtype=torch.float32, device=vals.device)
+        pack[:, :kk] = vals.float()
+        pack[:, kk:2 * kk] = idxs.to(torch.int32).view(torch.float32)
+        cu.step_inc(self._ev_step)
+        cu.peer_gather(pack, self._ev_ptrs[par], self.rank * self._ev_cap * 4, self._flag_ptrs, F_EV, self.rank, self.G,
+                       self._ev_step, self.counters[16:])
+        cu.wait_flags(self.flags[F_EV:], self.G, self._ev_step, 1, 0, None, None)
+        got = self._ev_buf[par].view(self.G, self._ev_cap)[:, :need].view(self.G, n, width)
+        cv = got[:, :, :kk].permute(1, 0, 2).reshape(n, self.G * kk).contiguous()
+        ci = got[:, :, kk:2 * kk].permute(1, 0, 2).reshape(n, self.G * kk).contiguous().view(torch.int32)
+        k_eff = min(k, self.G * kk)
+        ov = torch.empty(n, k_eff, dtype=torch.float32, device=vals.device)
+        op = torch.empty(n, k_eff, dtype=torch.int32, device=vals.device)
+        cu.topk_rows(cv, self.G * kk, k_eff, 0, ov, op)
+        v, order = torch.sort(ov, dim=1, descending=True)
+        return v, torch.gather(torch.gather(ci, 1, op.long()), 1, order).long()
 
     def allreduce_grads(self, g: torch.Tensor, hp) -> float:
         from ..ops import cuda as cu

@@ -189,6 +189,13 @@ def _cases(dev, dt, NS):
                 if kind == "logits":
                     return (lambda i: cu.xfc_logits_grad(W[i], X, Gt[i], B, zero, zero, zero, 0)), ns, \
                         L * D * 2 + L * B * 2 + B * D * 2, gemm
+                if kind == "logits2":
+                    return (lambda i: cu.xfc_logits_grad_v2(W[i], X, Gt[i], B, zero, zero, zero, 0)), ns, \
+                        L * D * 2 + L * B * 2 + B * D * 2, gemm
+                if kind == "dx2":
+                    dX = torch.zeros(B, D, device=dev)
+                    return (lambda i: cu.xfc_dx_v2(Gt[i], B, W[i], B, dX, hp.buf)), ns, \
+                        L * D * 2 + L * B * 2 + B * D * 4, gemm
                 if kind == "dx":
                     dX = torch.zeros(B, D, device=dev)
                     splits = cu.dx_splits(B, D, L)
@@ -200,8 +207,10 @@ def _cases(dev, dt, NS):
                         4 * L * D * 2 + L * B * 2 + B * D * 2, gemm
                 raise KeyError(kind)
             return make
-        yield f"xfc_logits_grad B={B} L={L}", xfc("logits")
-        yield f"xfc_dx B={B} L={L}", xfc("dx")
+        yield f"xfc_logits_grad (one tile per CTA) B={B} L={L}", xfc("logits")
+        yield f"xfc_logits_grad (persistent CTA pairs) B={B} L={L}", xfc("logits2")
+        yield f"xfc_dx (one tile per CTA) B={B} L={L}", xfc("dx")
+        yield f"xfc_dx (persistent CTA pairs) B={B} L={L}", xfc("dx2")
         yield f"xfc_dw_sgd B={B} L={L}", xfc("dw")
 
     def topk():

@@ -278,6 +278,31 @@ def test_xfc_dx(B, D, Lc, nnz):
         torch.testing.assert_close(dX, ref.xfc_dx(Gr, W, 4096.0), rtol=2e-3, atol=4096.0 * 2e-3)
 
 
+@pytest.mark.parametrize("B,D,Lc,nnz", XFC_SHAPES + [(256, 768, 24676, 3000), (1024, 768, 12345, 9000), (100, 128, 40000, 500)])
+def test_xfc_logits_grad_and_dx_on_the_persistent_gemm(B, D, Lc, nnz):
+    """The classifier's first two GEMMs on the persistent CTA-pair kernel: sigmoid(W X^T) - Y with the positives
+    applied in shared memory (pad columns zero), and dX = scale * Gt^T W by vector reductions, against the oracle."""
+    X, W, rows, labels = _xfc_problem(B, D, Lc, nnz)
+    ldG = (B + 7) // 8 * 8
+    Gt = torch.full((Lc, ldG), 7.0, dtype=torch.float16, device=dev())
+    n = torch.tensor([rows.numel()], dtype=torch.int32, device=dev())
+    cu().xfc_logits_grad_v2(W, X, Gt, ldG, rows, labels, n, 0)
+    cu().check_status()
+    Gr, _ = ref.xfc_logit_grad(X, W, rows, labels)
+    torch.testing.assert_close(Gt[:, :B].float(), Gr.float(), rtol=2e-3, atol=2e-3)
+    if ldG > B:
+        assert float(Gt[:, B:].abs().max()) == 0.0
+    # a label offset: the same positives numbered from 1000
+    Gt2 = torch.empty_like(Gt)
+    cu().xfc_logits_grad_v2(W, X, Gt2, ldG, rows, labels + 1000, n, 1000)
+    assert torch.equal(Gt2, Gt)
+    hp = HyperParams(dev(), init_scale=4096.0)
+    dX = torch.zeros(B, D, device=dev())
+    cu().xfc_dx_v2(Gt, ldG, W, B, dX, hp.buf)
+    cu().check_status()
+    torch.testing.assert_close(dX, ref.xfc_dx(Gt[:, :B], W, 4096.0), rtol=2e-3, atol=4096.0 * 2e-3)
+
+
 @pytest.mark.parametrize("B,D,Lc,nnz", XFC_SHAPES)
 def test_xfc_dw_sgd(B, D, Lc, nnz):
     X, W, rows, labels = _xfc_problem(B, D, Lc, nnz)

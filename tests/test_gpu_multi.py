@@ -57,6 +57,21 @@ def _worker(rank, world, port, out_dir):
             assert tr.graph_active()
             print(f"rank {rank}: multicast grad={comm._mc_grad != 0} p16={comm._mc_p16 != 0}", flush=True)
         results[name] = {k: v.cpu() for k, v in tr.state_dict().items()}
+        if name == "peer":
+            # cross-rank top-k merge over peer memory equals the NCCL all-gather + topk merge (several calls:
+            # the buffers alternate by call parity; two sizes: the buffers grow on demand)
+            from renee_b200.parallel.collectives import TorchCollectives
+            lib_comm = TorchCollectives(ctx)
+            g = torch.Generator(device=ctx.device).manual_seed(100 + rank)
+            for n_rows, kk in ((37, 5), (64, 5), (64, 100), (37, 5)):
+                vals = torch.randn(n_rows, kk, generator=g, device=ctx.device)
+                idxs = torch.randint(0, 1 << 20, (n_rows, kk), generator=g, device=ctx.device) + rank * (1 << 20)
+                v1, i1 = comm.merge_topk(vals, idxs, kk)
+                v2, i2 = lib_comm.merge_topk(vals, idxs, kk)
+                torch.testing.assert_close(v1, v2, rtol=0, atol=0)
+                assert torch.equal(i1, i2)
+            torch.cuda.synchronize()
+            cu.check_status()
         torch.distributed.barrier()
     torch.save(results, os.path.join(out_dir, f"r{rank}.pt"))
     shutdown()
