@@ -1,5 +1,6 @@
 // Shared device helpers for the sm_100a kernels of renee_b200.
 #pragma once
+#include <type_traits>
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -91,6 +92,21 @@ template <> __device__ __forceinline__ void unpack8<float>(const Raw8<float>& r,
 
 // Rounds through T (what a store followed by a load would give)
 template <typename T> __device__ __forceinline__ float round_through(float x) { return to_f(from_f<T>(x)); }
+
+// fp32 -> fp16 with stochastic rounding: add uniform noise below the 13 mantissa bits fp16 drops, then
+// truncate.  Unbiased for values in fp16's normal range, which keeps updates smaller than half an ulp
+// of W from being lost systematically late in the learning-rate schedule.
+__device__ __forceinline__ __half sr_half(float x, uint32_t rnd) {
+  uint32_t b = __float_as_uint(x);
+  b = (b + (rnd & 0x1FFFu)) & ~0x1FFFu;
+  return __float2half_rz(__uint_as_float(b));
+}
+// The same for either 16-bit type, returned as the fp32 value of the rounded number (bf16 drops 16 bits).
+template <typename T> __device__ __forceinline__ float sr_round(float x, uint32_t rnd) {
+  if (std::is_same<T, __half>::value) return __half2float(sr_half(x, rnd));
+  const uint32_t b = (__float_as_uint(x) + (rnd & 0xFFFFu)) & ~0xFFFFu;
+  return __uint_as_float(b);
+}
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -59,13 +59,18 @@ constexpr int TMEM_COLS = ACC_BUFS * ACC_STRIDE;
 // loop is bound by load latency over the bytes in flight, so the ring takes everything else (192 KB).
 constexpr int RING_BYTES = 192 * 1024;          // operand bytes in flight per CTA
 constexpr int MAX_STAGES = 8;                   // a stage is 16 KB of A + BN / NCTA rows of B: 24 KB (8 stages) .. 48 KB (4)
-template <bool STAGED> struct Cfg {
-  static constexpr int kPanels = STAGED ? N_PANELS : 0;
-  static constexpr int kSmem = RING_BYTES + kPanels * PANEL_BYTES + 1024 + 512;
-};
 
 enum Layout : int { L_NT = 0, L_NN = 1, L_TN = 2 };
-enum Epi : int { E_STORE = 0, E_BIAS_GELU = 1, E_BIAS_DROPOUT_RESID = 2, E_ADD = 3, E_GELU_BWD = 4, E_SPLITK = 5, E_TOPK = 6, E_SIGMOID_POS = 7, E_DX = 8 };
+enum Epi : int { E_STORE = 0, E_BIAS_GELU = 1, E_BIAS_DROPOUT_RESID = 2, E_ADD = 3, E_GELU_BWD = 4, E_SPLITK = 5, E_TOPK = 6, E_SIGMOID_POS = 7, E_DX = 8, E_DW_SGD = 9 };
+
+// DW_SGD updates two tile-shaped tensors in place (weights and momentum): two panels per group, a 160 KB ring.
+constexpr int ring_bytes(int epi) { return epi == E_DW_SGD ? RING_BYTES - N_PANELS * PANEL_BYTES : RING_BYTES; }
+template <int EPI> struct Cfg {
+  static constexpr bool kStaged = (EPI != E_SPLITK && EPI != E_TOPK && EPI != E_DX);
+  static constexpr int kPanels = !kStaged ? 0 : (EPI == E_DW_SGD ? 2 * N_PANELS : N_PANELS);
+  static constexpr int kRing = ring_bytes(EPI);
+  static constexpr int kSmem = kRing + kPanels * PANEL_BYTES + 1024 + 512;
+};
 
 struct Params {
   int M, N;                      // output rows / columns
@@ -84,6 +89,9 @@ struct Params {
   // DX (classifier input gradient): fp32 accumulation target, loss scale, completion signal to the peers
   float* dX; int ldX; const float* hp;
   unsigned* done_counter; void* peer_flags[16]; int n_peers; int flag_index;
+  // DW_SGD (classifier weights): momentum, weight decay, rounding mode; the row stride numbers the elements for the
+  // rounding hash; the learning rate and the seed come from hp
+  float mo, wd; int stochastic_round; int ldW;
   int* status;
 };
 
@@ -125,15 +133,17 @@ __global__ void __launch_bounds__(THREADS, 1)
 enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
                 const __grid_constant__ CUtensorMap tmF, const Params p) {
-  using C_ = Cfg<EPI != E_SPLITK && EPI != E_TOPK && EPI != E_DX>;
+  using C_ = Cfg<EPI>;
+  constexpr int RING = C_::kRing;
   constexpr bool A_MN = (LAYOUT == L_TN);
   constexpr bool B_MN = (LAYOUT != L_NT);
   constexpr int FMT = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
-  constexpr bool HAS_IN = (EPI == E_BIAS_DROPOUT_RESID || EPI == E_ADD || EPI == E_GELU_BWD);   // tile-shaped input R
-  constexpr bool STAGED = (EPI != E_SPLITK && EPI != E_TOPK && EPI != E_DX);                    // outputs through panels
+  constexpr bool HAS_IN = (EPI == E_BIAS_DROPOUT_RESID || EPI == E_ADD || EPI == E_GELU_BWD || EPI == E_DW_SGD);   // tile-shaped input R
+  constexpr bool STAGED = C_::kStaged;                                                           // outputs through panels
+  constexpr uint32_t IN_BYTES = EPI == E_DW_SGD ? 2 * PANEL_BYTES : PANEL_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* panels = smem + RING_BYTES;                           // [N_PANELS][PANEL_BYTES], 1024-byte aligned
+  uint8_t* panels = smem + RING;                           // [N_PANELS][PANEL_BYTES], 1024-byte aligned
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(panels + C_::kPanels * PANEL_BYTES);
   uint64_t* empty_bar = full_bar + MAX_STAGES;
   uint64_t* tmem_full_bar = empty_bar + MAX_STAGES;      // [ACC_BUFS]
@@ -151,7 +161,7 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   const int n_items = p.n_m_tiles * p.n_n_tiles * p.splits;
   const int b_rows = p.BN / NCTA;                                                 // B rows (N index) this CTA loads
   const int STAGE = A_BYTES + b_rows * BK * 2;                                    // 24, 32 or 48 KB
-  const int STAGES = min(MAX_STAGES, RING_BYTES / STAGE);
+  const int STAGES = min(MAX_STAGES, RING / STAGE);
   const uint32_t stage_tx = (uint32_t)NCTA * (uint32_t)STAGE;
 
   if (threadIdx.x == 0) {
@@ -159,7 +169,7 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     tc::prefetch_tmap(&tmB);
     if (STAGED) tc::prefetch_tmap(&tmC);
     if (HAS_IN) tc::prefetch_tmap(&tmR);
-    if (EPI == E_BIAS_GELU) tc::prefetch_tmap(&tmF);
+    if (EPI == E_BIAS_GELU || EPI == E_DW_SGD) tc::prefetch_tmap(&tmF);
     for (int s = 0; s < MAX_STAGES; ++s) { tc::mbar_init(full_bar + s, 1); tc::mbar_init(empty_bar + s, 1); }
     for (int a = 0; a < ACC_BUFS; ++a) { tc::mbar_init(tmem_full_bar + a, 1); tc::mbar_init(tmem_empty_bar + a, 8 * NCTA); }
     for (int a = 0; a < N_PANELS; ++a) tc::mbar_init(in_bar + a, 1);
@@ -273,6 +283,7 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int bar_id = 2 + g;                             // named barrier of this group (128 threads)
     const bool elected = (warp == 2 + 4 * g) && lane == 0;                   // first warp of the group, lane 0
     uint8_t* pan = panels + g * PANEL_BYTES;              // this group's staging panel
+    uint8_t* pan2 = panels + (N_PANELS + g) * PANEL_BYTES;   // DW_SGD: the momentum panel beside the weight panel
     uint64_t* my_in_bar = in_bar + g;
     uint32_t seed = 0u;
     float inv_keep = 1.f;
@@ -313,8 +324,9 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         // fetch the tile's first R panel while its main loop still runs; the panel is free once the stores
         // issued from it have read it
         tc::tma_store_wait_read<0>();
-        tc::mbar_expect_tx(my_in_bar, PANEL_BYTES);
+        tc::mbar_expect_tx(my_in_bar, IN_BYTES);
         tc::tma_load_2d(pan, &tmR, my_in_bar, n0 + g_col, m0);
+        if (EPI == E_DW_SGD) tc::tma_load_2d(pan2, &tmF, my_in_bar, n0 + g_col, m0);
       }
       if (!tc::mbar_wait(tmem_full_bar + buf, use & 1, aborted, p.status, tc::SITE_TMEM_FULL, item)) *s_abort = 1;
       asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -331,8 +343,9 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           if (HAS_IN) {
             if (pi > 0 && elected) {                         // later panels: fetched once the previous store has read the buffer
               tc::tma_store_wait_read<0>();
-              tc::mbar_expect_tx(my_in_bar, PANEL_BYTES);
+              tc::mbar_expect_tx(my_in_bar, IN_BYTES);
               tc::tma_load_2d(pan, &tmR, my_in_bar, pcol, m0);
+              if (EPI == E_DW_SGD) tc::tma_load_2d(pan2, &tmF, my_in_bar, pcol, m0);
             }
             if (!tc::mbar_wait(my_in_bar, in_count & 1, aborted, p.status, tc::SITE_FULL, 2000 + pi)) *s_abort = 1;
             ++in_count;
@@ -387,6 +400,22 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 unpack8<T>(*slot, res);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) o[j] = a[j] + res[j];
+              } else if (EPI == E_DW_SGD) {
+                // momentum SGD on the tile: m = mo m + (dW + wd w), w -= lr m, with m rounded to 16 bit first
+                uint4* slot2 = reinterpret_cast<uint4*>(pan2 + panel_off(r, chunk));
+                float w[8], mm[8];
+                unpack8<T>(*slot, w);
+                unpack8<T>(*slot2, mm);
+                const float lr = p.hp[HP_LR_XFC];
+                const uint32_t sr_seed = reinterpret_cast<const uint32_t*>(p.hp)[HP_SEED];
+                const uint32_t e = (uint32_t)row * (uint32_t)p.ldW + (uint32_t)c;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  mm[j] = round_through<T>(p.mo * mm[j] + (a[j] + p.wd * w[j]));
+                  const float nw = w[j] - lr * mm[j];
+                  o[j] = p.stochastic_round ? sr_round<T>(nw, mix32(sr_seed, 0x5152u, e + j)) : nw;
+                }
+                *slot2 = pack8<T>(mm);
               } else {   // E_GELU_BWD: rows past M read F = 0 and a zero accumulator, so they add nothing to the sums
                 float f[8];
                 unpack8<T>(*slot, f);
@@ -433,6 +462,7 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
           if (elected) {
             tc::tma_store_2d(EPI == E_BIAS_GELU ? &tmF : &tmC, pan, pcol, m0);
+            if (EPI == E_DW_SGD) tc::tma_store_2d(&tmF, pan2, pcol, m0);
             tc::tma_store_commit();
           }
           if (EPI == E_BIAS_GELU) {
@@ -672,7 +702,7 @@ template <typename T, int LAYOUT, int EPI, int NCTA>
 static int launch_enc_gemm(const Maps& m, const Params& p, int units, cudaStream_t st) {
   static bool attr_set = false;
   auto k = enc_gemm_kernel<T, LAYOUT, EPI, NCTA>;
-  constexpr int smem = Cfg<EPI != E_SPLITK && EPI != E_TOPK && EPI != E_DX>::kSmem;
+  constexpr int smem = Cfg<EPI>::kSmem;
   if (!attr_set) {
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -5;
     attr_set = true;
@@ -714,6 +744,7 @@ static int dispatch_enc_gemm(int layout, int epi, const Maps& m, const Params& p
     if (epi == E_STORE) return launch_enc_gemm<T, L_NN, E_STORE, NCTA>(m, p, units, st);
     if (epi == E_ADD) return launch_enc_gemm<T, L_NN, E_ADD, NCTA>(m, p, units, st);
     if (epi == E_GELU_BWD) return launch_enc_gemm<T, L_NN, E_GELU_BWD, NCTA>(m, p, units, st);
+    if (epi == E_DW_SGD) return launch_enc_gemm<T, L_NN, E_DW_SGD, NCTA>(m, p, units, st);
   } else if (layout == L_TN) {
     if (epi == E_SPLITK) return launch_enc_gemm<T, L_TN, E_SPLITK, NCTA>(m, p, units, st);
     if (epi == E_DX) return launch_enc_gemm<T, L_TN, E_DX, NCTA>(m, p, units, st);
@@ -766,7 +797,7 @@ static Plan make_plan(int layout, int epi, int M, int N, int K, int bn_forced, i
         const double busy = (double)(items < units ? items : units) * ncta / sms;      // fraction of the SMs at work
         const double bytes = A_BYTES + (double)(bn / ncta) * BK * 2;
         double t_kb = bytes / (29.0 / (busy > 0.25 ? busy : 0.25));
-        const int stages = (int)(RING_BYTES / bytes) < MAX_STAGES ? (int)(RING_BYTES / bytes) : MAX_STAGES;
+        const int stages = (int)(ring_bytes(epi) / bytes) < MAX_STAGES ? (int)(ring_bytes(epi) / bytes) : MAX_STAGES;
         if (t_kb < 3900.0 / stages) t_kb = 3900.0 / stages;          // load latency over the ring depth
         if (t_kb < 2.0 * bn) t_kb = 2.0 * bn;
         const int n_pan = bn >= 128 ? bn / 128 : 1;
@@ -956,6 +987,34 @@ RB_API int rb_xfc_dx_v2(const void* Gt, int ldG, const void* W, int Lc, int D, i
     for (int q = 0; q < n_peers; ++q) p.peer_flags[q] = peer_flags[q];
   }
   rc = launch_planned(pl, false, L_TN, E_DX, m, p, Lc, st);
+  if (rc) return rc;
+  RB_LAUNCH_CHECK();
+  return 0;
+}
+
+// Classifier weight update on the persistent GEMM: dW = Gt X over the batch (never stored), then momentum SGD on the
+// [128 x 64] tiles of W and Mom [Lc, D] (fp16) in shared memory: both tiles come in by TMA under the main loop and
+// leave by TMA; lr and the rounding seed are read from hp on the device.
+// Replaces, in the reference, the fused dW GEMM + SGD epilogue (xfc_gemm_kernel.cu:102-151).
+RB_API int rb_xfc_dw_sgd_v2(const void* Gt, int ldG, const void* X, int B, void* W, void* Mom, int Lc, int D,
+                            const float* hp, float mo, float wd, int stochastic_round, int bn_forced, int ncta_forced,
+                            int* status, cudaStream_t st) {
+  if (D % 8 || ldG % 8 || Lc < 1 || B < 1) return -3;
+  const Plan pl = make_plan(L_NN, E_DW_SGD, Lc, D, B, bn_forced, ncta_forced);
+  Maps m;
+  int rc = tc::make_tmap_2d(&m.a, Gt, Lc, B, ldG, 64, BM, false);
+  if (rc) return rc;
+  rc = tc::make_tmap_2d(&m.b, X, B, D, D, 64, 64, false);
+  if (rc) return rc;
+  rc = tc::make_tmap_2d(&m.c, W, Lc, D, D, 64, BM, false);
+  if (rc) return rc;
+  m.r = m.c;
+  rc = tc::make_tmap_2d(&m.f, Mom, Lc, D, D, 64, BM, false);
+  if (rc) return rc;
+  Params p{};
+  p.M = Lc; p.N = D; p.status = status;
+  p.hp = hp; p.mo = mo; p.wd = wd; p.stochastic_round = stochastic_round; p.ldW = D;
+  rc = launch_planned(pl, false, L_NN, E_DW_SGD, m, p, B, st);
   if (rc) return rc;
   RB_LAUNCH_CHECK();
   return 0;

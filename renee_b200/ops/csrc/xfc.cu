@@ -55,15 +55,6 @@ struct GemmParams {
   int stochastic_round;   // DW (TMA kernel): round the updated weights to fp16 stochastically
 };
 
-// fp32 -> fp16 with stochastic rounding: add uniform noise below the 13 mantissa bits fp16 drops, then
-// truncate.  Unbiased for values in fp16's normal range, which keeps updates smaller than half an ulp
-// of W from being lost systematically late in the learning-rate schedule.
-__device__ __forceinline__ __half sr_half(float x, uint32_t rnd) {
-  uint32_t b = __float_as_uint(x);
-  b = (b + (rnd & 0x1FFFu)) & ~0x1FFFu;
-  return __float2half_rz(__uint_as_float(b));
-}
-
 __device__ __forceinline__ int lower_bound_i32(const int* a, int n, int key) {
   int lo = 0, hi = n;
   while (lo < hi) {

@@ -510,10 +510,16 @@ def xfc_dx(Gt, ldG, W, B, dX, hp_buf, splits, signal=None):
           ptrs if ptrs is not None else _VP(0), _I(n), _I(idx), _p(step), _p(ws.status), _stream())
 
 
-def xfc_dw_sgd(Gt, ldG, X, W, M, hp_buf, mo, wd, tma_tiles=True, stochastic_round=False):
+def xfc_dw_sgd(Gt, ldG, X, W, M, hp_buf, mo, wd, tma_tiles=True, stochastic_round=False, v2=False, bn=0, ncta=0):
+    """W, M updated in place from dW = Gt X (never stored).  ``v2``: the persistent CTA-pair GEMM with the W / M tiles
+    staged through shared memory by TMA; otherwise the one-tile-per-CTA kernel."""
     Lc, D = W.shape
     B = X.shape[0]
     ws = workspace(W.device)
+    if v2:
+        _call("rb_xfc_dw_sgd_v2", _p(Gt), _I(ldG), _p(X), _I(B), _p(W), _p(M), _I(Lc), _I(D), _p(hp_buf), _F(mo), _F(wd),
+              _I(1 if stochastic_round else 0), _I(bn), _I(ncta), _p(ws.status), _stream())
+        return
     _call("rb_xfc_dw_sgd", _p(Gt), _I(ldG), _p(X), _I(B), _p(W), _p(M), _I(Lc), _I(D), _p(hp_buf), _F(mo), _F(wd),
           _I(int(tma_tiles)), _I(1 if stochastic_round else 0), _p(ws.status), _stream())
 
@@ -555,6 +561,7 @@ def xfc_step(xfc, X, pos_rows, pos_labels, nnz, dX_out, hp, mo, wd, want_loss, w
         loss.zero_()
     dX_out.zero_()
     chunks = list(range(0, xfc.Ls, xfc.chunk))
+    dw_v2 = xfc_v2() and os.environ.get("RENEE_B200_XFC_DW_V2", "1") != "0"
     for ci, l0 in enumerate(chunks):
         l1 = min(xfc.Ls, l0 + xfc.chunk)
         Wc, Mc = xfc.W[l0:l1], xfc.M[l0:l1]
@@ -576,9 +583,9 @@ def xfc_step(xfc, X, pos_rows, pos_labels, nnz, dX_out, hp, mo, wd, want_loss, w
             main = torch.cuda.current_stream()
             side_stream.wait_stream(main)
             with torch.cuda.stream(side_stream):
-                xfc_dw_sgd(Gt, ldG, X, Wc, Mc, hp.buf, mo, wd, stochastic_round=xfc.stochastic_round)
+                xfc_dw_sgd(Gt, ldG, X, Wc, Mc, hp.buf, mo, wd, stochastic_round=xfc.stochastic_round, v2=dw_v2)
         else:
-            xfc_dw_sgd(Gt, ldG, X, Wc, Mc, hp.buf, mo, wd, stochastic_round=xfc.stochastic_round)
+            xfc_dw_sgd(Gt, ldG, X, Wc, Mc, hp.buf, mo, wd, stochastic_round=xfc.stochastic_round, v2=dw_v2)
     return loss[0] if want_loss else None
 
 

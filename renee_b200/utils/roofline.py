@@ -201,9 +201,10 @@ def _cases(dev, dt, NS):
                     splits = cu.dx_splits(B, D, L)
                     return (lambda i: cu.xfc_dx(Gt[i], B, W[i], B, dX, hp.buf, splits)), ns, \
                         L * D * 2 + L * B * 2 + B * D * 4, gemm
-                if kind == "dw":
+                if kind in ("dw", "dw2"):
                     M = [torch.zeros(L, D, device=dev, dtype=torch.float16) for _ in range(ns)]
-                    return (lambda i: cu.xfc_dw_sgd(Gt[i], B, X, W[i], M[i], hp.buf, 0.9, 1e-4)), ns, \
+                    v2 = kind == "dw2"
+                    return (lambda i: cu.xfc_dw_sgd(Gt[i], B, X, W[i], M[i], hp.buf, 0.9, 1e-4, v2=v2)), ns, \
                         4 * L * D * 2 + L * B * 2 + B * D * 2, gemm
                 raise KeyError(kind)
             return make
@@ -211,7 +212,8 @@ def _cases(dev, dt, NS):
         yield f"xfc_logits_grad (persistent CTA pairs) B={B} L={L}", xfc("logits2")
         yield f"xfc_dx (one tile per CTA) B={B} L={L}", xfc("dx")
         yield f"xfc_dx (persistent CTA pairs) B={B} L={L}", xfc("dx2")
-        yield f"xfc_dw_sgd B={B} L={L}", xfc("dw")
+        yield f"xfc_dw_sgd (one tile per CTA) B={B} L={L}", xfc("dw")
+        yield f"xfc_dw_sgd (persistent CTA pairs) B={B} L={L}", xfc("dw2")
 
     def topk():
         B, L = 256, 16384

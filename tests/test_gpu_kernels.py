@@ -303,8 +303,9 @@ def test_xfc_logits_grad_and_dx_on_the_persistent_gemm(B, D, Lc, nnz):
     torch.testing.assert_close(dX, ref.xfc_dx(Gt[:, :B], W, 4096.0), rtol=2e-3, atol=4096.0 * 2e-3)
 
 
+@pytest.mark.parametrize("v2", [False, True], ids=["tile-per-cta", "persistent-pairs"])
 @pytest.mark.parametrize("B,D,Lc,nnz", XFC_SHAPES)
-def test_xfc_dw_sgd(B, D, Lc, nnz):
+def test_xfc_dw_sgd(B, D, Lc, nnz, v2):
     X, W, rows, labels = _xfc_problem(B, D, Lc, nnz)
     Gr, _ = ref.xfc_logit_grad(X, W, rows, labels)
     ldG = (B + 7) // 8 * 8
@@ -315,7 +316,7 @@ def test_xfc_dw_sgd(B, D, Lc, nnz):
     hp.buf[HP.LR_XFC] = 0.05
     Wr, Mr = W.float().clone(), M.float().clone()
     ref.sgd_update(Wr, Mr, Gr.float() @ X.float(), 0.05, 0.9, 1e-3)
-    cu().xfc_dw_sgd(Gt, ldG, X, W, M, hp.buf, 0.9, 1e-3)
+    cu().xfc_dw_sgd(Gt, ldG, X, W, M, hp.buf, 0.9, 1e-3, v2=v2)
     cu().check_status()
     torch.testing.assert_close(M.float(), Mr, rtol=2e-3, atol=2e-3)
     torch.testing.assert_close(W.float(), Wr, rtol=2e-3, atol=2e-3)
@@ -447,6 +448,14 @@ def test_xfc_dw_sgd_both_kernels_agree_and_stochastic_rounding_is_unbiased():
     cu().xfc_dw_sgd(Gt, B, X, W3, M3, hp.buf, 0.9, 1e-3, tma_tiles=2)      # 256-column tiles, one CTA per SM
     cu().check_status()
     assert torch.equal(W1, W3) and torch.equal(M1, M3)
+    # the persistent CTA-pair kernel, every tile shape: the same sums in the same order per element up to the last bit
+    for bn, ncta in ((0, 0), (256, 2), (128, 2), (256, 1), (128, 1), (64, 1)):
+        W4, M4 = W.clone(), M.clone()
+        cu().xfc_dw_sgd(Gt, B, X, W4, M4, hp.buf, 0.9, 1e-3, v2=True, bn=bn, ncta=ncta)
+        cu().check_status()
+        assert (M4.float() - M1.float()).abs().max().item() <= 2e-5, (bn, ncta)
+        assert (W4.float() - W1.float()).abs().max().item() <= 2e-4, (bn, ncta)
+        assert (W4 != W1).float().mean().item() < 0.01, (bn, ncta)
     # updates of a tenth of an ulp: round-to-nearest loses them all, stochastic rounding keeps their mean
     Wc = torch.ones(Lc, D, dtype=torch.float16, device=dev())
     Mc = torch.full((Lc, D), 1.0, dtype=torch.float16, device=dev())
@@ -462,3 +471,7 @@ def test_xfc_dw_sgd_both_kernels_agree_and_stochastic_rounding_is_unbiased():
     delta = (Ws.float() - 1.0).mean().item()
     assert abs(delta + 1e-4) < 2e-5, delta
     assert set(torch.unique(Ws).tolist()) <= {1.0, 1.0 - 2.0 ** -11}
+    Wp, Mp = Wc.clone(), Mc.clone()
+    cu().xfc_dw_sgd(Z, B, X, Wp, Mp, hp.buf, 1.0, 0.0, stochastic_round=True, v2=True)
+    cu().check_status()
+    assert torch.equal(Wp, Ws) and torch.equal(Mp, Ms)       # the same hash of (seed, element) in both kernels
