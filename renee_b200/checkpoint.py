@@ -33,7 +33,33 @@ def _optimizer_states(tr) -> tuple[dict, dict]:
     if tr.cfg.default_impl:
         return tr.xfc_optimizer.state_dict(), tr.tf_optimizer.state_dict()
     enc = tr.encoder
-    return tr.xfc.optimizer_state_dict(), {"exp_avg": enc.m.detach().clone(), "exp_avg_sq": enc.v.detach().clone()}
+    return tr.xfc.optimizer_state_dict(), {"exp_avg": enc.m.detach().clone(), "exp_avg_sq": enc.v.detach().clone(),
+                                           "layout": _flat_layout(enc)}
+
+
+def _flat_layout(enc) -> list:
+    """(name, offset, numel) of every parameter in the flat buffers: the moments are stored flat, so a checkpoint
+    carries the layout it was written with."""
+    return [(n, int(s.offset), int(s.numel)) for n, s in enc.slots.items()]
+
+
+def _load_flat_moments(enc, tf_opt: dict, device) -> None:
+    """Copy the flat moments back; a checkpoint written under another ordering of the flat buffer is re-mapped by
+    parameter name (one without a recorded layout is taken to have this build's ordering only if the sizes agree)."""
+    here = _flat_layout(enc)
+    there = tf_opt.get("layout")
+    for key, dst in (("exp_avg", enc.m), ("exp_avg_sq", enc.v)):
+        src = tf_opt[key]
+        if there is None or [tuple(x) for x in there] == here:
+            if src.numel() != dst.numel():
+                raise RuntimeError(f"optimizer state {key}: {src.numel()} elements in the checkpoint, {dst.numel()} here")
+            dst.copy_(src.to(device))
+            continue
+        old = {n: (o, k) for n, o, k in there}
+        for n, o, k in here:
+            if n not in old or old[n][1] != k:
+                raise RuntimeError(f"optimizer state {key}: parameter {n!r} missing or of another size in the checkpoint")
+            dst[o:o + k].copy_(src[old[n][0]:old[n][0] + k].to(device))
 
 
 def save_checkpoint(tr, out_dir: str, loss: float) -> str:
@@ -80,8 +106,7 @@ def load_checkpoint(tr, out_dir: str) -> float:
         tr.tf_optimizer.load_state_dict(sd["tf_optimizer_state_dict"])
     else:
         tr.xfc.load_optimizer_state_dict(sd["xfc_optimizer_state_dict"])
-        tr.encoder.m.copy_(sd["tf_optimizer_state_dict"]["exp_avg"].to(tr.device))
-        tr.encoder.v.copy_(sd["tf_optimizer_state_dict"]["exp_avg_sq"].to(tr.device))
+        _load_flat_moments(tr.encoder, sd["tf_optimizer_state_dict"], tr.device)
     tr.xfc_sched.load_state_dict(sd["xfc_scheduler_state_dict"])
     tr.tf_sched.load_state_dict(sd["tf_scheduler_state_dict"])
     tr.rng.load_state_dict(sd.get("dropout_rng", tr.rng.state_dict()))

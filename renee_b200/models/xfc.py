@@ -29,13 +29,16 @@ Differences from the reference, made for B200:
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..ops import reference as ref
 from ..utils import guard
 
 INIT_CHUNK = 1 << 16
-GT_L2_BUDGET_BYTES = 48 << 20   # keep the Gt chunk well inside the 126 MB L2
+GT_L2_BUDGET_BYTES = 128 << 20  # bound of the Gt scratch; measured: larger chunks amortise the kernels' fill and drain
+                                # better than an L2-resident Gt pays (3.98 -> 3.92 ms at 131 K labels, 48 -> 96 MB)
 
 
 class XFCClassifier:
@@ -77,7 +80,8 @@ class XFCClassifier:
 
     def _pick_chunk(self) -> int:
         per_accum = (self.Ls + self.accum - 1) // self.accum
-        cap = max(128, GT_L2_BUDGET_BYTES // (2 * max(self.max_batch, 1)))
+        budget = int(float(os.environ.get("RENEE_B200_XFC_GT_MB", GT_L2_BUDGET_BYTES / (1 << 20))) * (1 << 20))
+        cap = max(128, budget // (2 * max(self.max_batch, 1)))
         chunk = min(per_accum, cap)
         return max(128, (chunk + 127) // 128 * 128)
 

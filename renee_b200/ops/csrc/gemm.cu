@@ -21,9 +21,10 @@
 //                                   over all the tiles its CTA visits and writes them as candidates at the end
 //                                   (prediction: X W^T is never materialised; parity: dl_base.py:745-756)
 //
-// Structure.  Persistent CTAs walk the work items (tile x K-split).  320 threads: warp 0 TMA producer, warp 1
-// TMEM owner + MMA issuer, warps 2..9 epilogue (two groups of four warps, one TMEM lane quarter per warp, half
-// of the tile's columns per group).  The shared-memory ring keeps streaming across item boundaries and TMEM
+// Structure.  Persistent CTAs walk the work items (tile x K-split).  576 threads: warp 0 TMA producer, warp 1
+// TMEM owner + MMA issuer, warps 2..17 epilogue (four groups of four warps, one TMEM lane quarter per warp, one
+// 64-column panel of the tile per group: the epilogue is bound by instruction latency, not by issue slots, and
+// sixteen warps hide what eight could not).  The shared-memory ring keeps streaming across item boundaries and TMEM
 // holds two accumulators, so the epilogue of item i runs under the main loop of item i + 1.
 //
 // Two tile shapes.  NCTA = 1: a CTA owns a 128 x BN tile.  NCTA = 2 (`cta_group::2`): the two CTAs of a cluster
@@ -49,8 +50,10 @@ constexpr int BM = 128;                         // accumulator rows per CTA
 constexpr int BK = 64;
 constexpr int A_BYTES = BM * BK * 2;            // 16 KB
 constexpr int PANEL_BYTES = BM * 64 * 2;        // one staging panel: 128 rows x 64 x 16 bit
-constexpr int N_PANELS = 2;                     // one per epilogue group
-constexpr int THREADS = 320;
+constexpr int EGROUPS = 4;                      // epilogue groups of four warps (one per TMEM lane quarter)
+constexpr int N_PANELS = EGROUPS;               // one staging panel per epilogue group
+constexpr int EPI_THREADS = 128 * EGROUPS;
+constexpr int THREADS = 64 + EPI_THREADS;       // producer warp, MMA warp, sixteen epilogue warps
 constexpr int ACC_BUFS = 2;
 constexpr int ACC_STRIDE = 256;                 // TMEM columns between the two accumulators
 constexpr int TMEM_COLS = ACC_BUFS * ACC_STRIDE;
@@ -64,10 +67,15 @@ enum Layout : int { L_NT = 0, L_NN = 1, L_TN = 2 };
 enum Epi : int { E_STORE = 0, E_BIAS_GELU = 1, E_BIAS_DROPOUT_RESID = 2, E_ADD = 3, E_GELU_BWD = 4, E_SPLITK = 5, E_TOPK = 6, E_SIGMOID_POS = 7, E_DX = 8, E_DW_SGD = 9 };
 
 // DW_SGD updates two tile-shaped tensors in place (weights and momentum): two panels per group, a 160 KB ring.
-constexpr int ring_bytes(int epi) { return epi == E_DW_SGD ? RING_BYTES - N_PANELS * PANEL_BYTES : RING_BYTES; }
+constexpr int SMEM_BUDGET = 224 * 1024;         // ring + panels
+constexpr bool staged_epi(int epi) { return epi != E_SPLITK && epi != E_TOPK && epi != E_DX; }
+constexpr int panel_count(int epi) { return !staged_epi(epi) ? 0 : (epi == E_DW_SGD ? 2 * N_PANELS : N_PANELS); }
+constexpr int ring_bytes(int epi) {
+  return SMEM_BUDGET - panel_count(epi) * PANEL_BYTES < RING_BYTES ? SMEM_BUDGET - panel_count(epi) * PANEL_BYTES : RING_BYTES;
+}
 template <int EPI> struct Cfg {
-  static constexpr bool kStaged = (EPI != E_SPLITK && EPI != E_TOPK && EPI != E_DX);
-  static constexpr int kPanels = !kStaged ? 0 : (EPI == E_DW_SGD ? 2 * N_PANELS : N_PANELS);
+  static constexpr bool kStaged = staged_epi(EPI);
+  static constexpr int kPanels = panel_count(EPI);
   static constexpr int kRing = ring_bytes(EPI);
   static constexpr int kSmem = kRing + kPanels * PANEL_BYTES + 1024 + 512;
 };
@@ -171,7 +179,7 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     if (HAS_IN) tc::prefetch_tmap(&tmR);
     if (EPI == E_BIAS_GELU || EPI == E_DW_SGD) tc::prefetch_tmap(&tmF);
     for (int s = 0; s < MAX_STAGES; ++s) { tc::mbar_init(full_bar + s, 1); tc::mbar_init(empty_bar + s, 1); }
-    for (int a = 0; a < ACC_BUFS; ++a) { tc::mbar_init(tmem_full_bar + a, 1); tc::mbar_init(tmem_empty_bar + a, 8 * NCTA); }
+    for (int a = 0; a < ACC_BUFS; ++a) { tc::mbar_init(tmem_full_bar + a, 1); tc::mbar_init(tmem_empty_bar + a, 4 * EGROUPS * NCTA); }
     for (int a = 0; a < N_PANELS; ++a) tc::mbar_init(in_bar + a, 1);
     *s_abort = 0;
     *s_last = 0;
@@ -277,9 +285,12 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int quarter = warp & 3;
     const int g = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;                    // row of the CTA's accumulator = TMEM lane
-    const int half_cols = p.BN >> 1;                      // 32, 64 or 128
-    const int n_pan = half_cols >= 64 ? half_cols / 64 : (g == 0 ? 1 : 0);   // BN = 64: group 0 takes the one panel
-    const int g_col = half_cols >= 64 ? g * half_cols : 0;
+    // staged epilogues: group g takes the 64-column panel g of the tile (BN / 64 groups have one, the others idle);
+    // the others split the tile's columns into BN / EGROUPS (at least 32) per group
+    const int n_pan = g < (p.BN >> 6) ? 1 : 0;
+    const int g_col = g * 64;
+    const int ucols = p.BN / EGROUPS < 32 ? 32 : p.BN / EGROUPS;
+    const bool u_active = g * ucols < p.BN;
     const int bar_id = 2 + g;                             // named barrier of this group (128 threads)
     const bool elected = (warp == 2 + 4 * g) && lane == 0;                   // first warp of the group, lane 0
     uint8_t* pan = panels + g * PANEL_BYTES;              // this group's staging panel
@@ -294,7 +305,7 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     float tv[8];
     int ti[8];
     int cur_m = -1;
-    const int slot = ((int)blockIdx.x * 2 + g) * 8;
+    const int slot = ((int)blockIdx.x * EGROUPS + g) * 8;
     for (int item = unit; item < n_items; item += n_units, ++t_local) {
       const int tile = item / p.splits;
       if (EPI == E_TOPK) {
@@ -302,7 +313,7 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         if (mt != cur_m) {
           if (cur_m >= 0) {
             const int frow = cur_m * (BM * NCTA) + (int)rank * BM + r;
-            if (frow < p.M && n_pan > 0) {
+            if (frow < p.M && u_active) {
 #pragma unroll
               for (int k = 0; k < 8; ++k) {
                 p.cand_val[(size_t)frow * p.cand_ld + slot + k] = tv[k];
@@ -329,39 +340,31 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         if (EPI == E_DW_SGD) tc::tma_load_2d(pan2, &tmF, my_in_bar, n0 + g_col, m0);
       }
       if (!tc::mbar_wait(tmem_full_bar + buf, use & 1, aborted, p.status, tc::SITE_TMEM_FULL, item)) *s_abort = 1;
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      if (*s_abort) break;                                   // the same answer in all eight warps
+      asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+      if (*s_abort) break;                                   // the same answer in every epilogue warp
       tc::tc_fence_after();
       const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * ACC_STRIDE + (uint32_t)g_col;
-      if (STAGED) {
-        for (int pi = 0; pi < n_pan; ++pi) {
-          const int pcol = n0 + g_col + 64 * pi;             // first column of the panel
-          // the accumulator fragments of the panel: 64 columns of this thread's row
-          float v[2][32];
-          tc::tmem_ld32(tbase + 64 * pi, v[0]);
-          tc::tmem_ld32(tbase + 64 * pi + 32, v[1]);
+      if (STAGED && n_pan > 0) {
+        {
+          const int pcol = n0 + g_col;                       // first column of this group's panel
           if (HAS_IN) {
-            if (pi > 0 && elected) {                         // later panels: fetched once the previous store has read the buffer
-              tc::tma_store_wait_read<0>();
-              tc::mbar_expect_tx(my_in_bar, IN_BYTES);
-              tc::tma_load_2d(pan, &tmR, my_in_bar, pcol, m0);
-              if (EPI == E_DW_SGD) tc::tma_load_2d(pan2, &tmF, my_in_bar, pcol, m0);
-            }
-            if (!tc::mbar_wait(my_in_bar, in_count & 1, aborted, p.status, tc::SITE_FULL, 2000 + pi)) *s_abort = 1;
+            if (!tc::mbar_wait(my_in_bar, in_count & 1, aborted, p.status, tc::SITE_FULL, 2000 + g)) *s_abort = 1;
             ++in_count;
           } else {
             if (elected) tc::tma_store_wait_read<0>();       // the buffer is free once the previous store has read it
             asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
           }
-          float colsum[2] = {0.f, 0.f};
+          uint4 keep2[EPI == E_BIAS_GELU ? 8 : 1];           // BIAS_GELU: the second output, packed, until the first has left
 #pragma unroll
-          for (int hc = 0; hc < 2; ++hc) {                   // two 32-column fragments per panel
+          for (int hc = 0; hc < 2; ++hc) {                   // two 32-column accumulator fragments per panel
+            float v[32];
+            tc::tmem_ld32(tbase + 32 * hc, v);
 #pragma unroll
             for (int j8 = 0; j8 < 4; ++j8) {
               const int chunk = 4 * hc + j8;
               const int c = pcol + 8 * chunk;
               uint4* slot = reinterpret_cast<uint4*>(pan + panel_off(r, chunk));
-              float* a = &v[hc][8 * j8];
+              float* a = &v[8 * j8];
               float o[8];
               if (EPI == E_STORE) {
 #pragma unroll
@@ -426,14 +429,12 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
               }
               *slot = pack8<T>(o);
+              if (EPI == E_BIAS_GELU) keep2[EPI == E_BIAS_GELU ? chunk : 0] = pack8<T>(a);
             }
-            if (EPI == E_GELU_BWD && p.colacc != nullptr) colsum[hc] = warp_colsum32(v[hc], lane);
-          }
-          if (EPI == E_GELU_BWD && p.colacc != nullptr) {
-#pragma unroll
-            for (int hc = 0; hc < 2; ++hc) {
-              const int c = pcol + 32 * hc + lane;           // lane L holds the sum of column L of the fragment
-              if (c < p.N) atomicAdd(p.colacc + (size_t)(blockIdx.x % kColReplicas) * p.col_tot + p.col_off + c, colsum[hc]);
+            if (EPI == E_GELU_BWD && p.colacc != nullptr) {
+              const float cs = warp_colsum32(v, lane);       // lane L holds the sum of column L of the fragment
+              const int c = pcol + 32 * hc + lane;
+              if (c < p.N) atomicAdd(p.colacc + (size_t)(blockIdx.x % kColReplicas) * p.col_tot + p.col_off + c, cs);
             }
           }
           if (EPI == E_SIGMOID_POS && p.pos_labels != nullptr) {
@@ -470,10 +471,8 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             if (elected) tc::tma_store_wait_read<0>();
             asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
 #pragma unroll
-            for (int hc = 0; hc < 2; ++hc)
-#pragma unroll
-              for (int j8 = 0; j8 < 4; ++j8)
-                *reinterpret_cast<uint4*>(pan + panel_off(r, 4 * hc + j8)) = pack8<T>(&v[hc][8 * j8]);
+            for (int chunk = 0; chunk < 8; ++chunk)
+              *reinterpret_cast<uint4*>(pan + panel_off(r, chunk)) = keep2[EPI == E_BIAS_GELU ? chunk : 0];
             tc::fence_proxy_async();
             asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
             if (elected) {
@@ -484,12 +483,12 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
       }
       if (EPI == E_TOPK) {
-        for (int pi = 0; pi < n_pan; ++pi) {
-#pragma unroll
-          for (int hc = 0; hc < 2; ++hc) {
+        const uint32_t ttk = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * ACC_STRIDE + (uint32_t)(g * ucols);
+        {
+          for (int cc = 0; u_active && cc < ucols; cc += 32) {
             float v[32];
-            tc::tmem_ld32(tbase + 64 * pi + 32 * hc, v);
-            const int c0 = n0 + g_col + 64 * pi + 32 * hc;
+            tc::tmem_ld32(ttk + cc, v);
+            const int c0 = n0 + g * ucols + cc;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const float x = v[j];
@@ -509,11 +508,11 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
       if (EPI == E_DX) {
         const float scale = p.hp[HP_SCALE];
-        const uint32_t tdx = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * ACC_STRIDE + (uint32_t)(g * half_cols);
-        for (int c0 = 0; c0 < half_cols; c0 += 32) {
+        const uint32_t tdx = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * ACC_STRIDE + (uint32_t)(g * ucols);
+        for (int c0 = 0; u_active && c0 < ucols; c0 += 32) {
           float v[32];
           tc::tmem_ld32(tdx + c0, v);
-          const int col0 = n0 + g * half_cols + c0;
+          const int col0 = n0 + g * ucols + c0;
           if (row < p.M) {
             float* d = p.dX + (size_t)row * p.ldX + col0;
 #pragma unroll
@@ -524,11 +523,11 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
       }
       if (EPI == E_SPLITK) {
-        const uint32_t tsk = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * ACC_STRIDE + (uint32_t)(g * half_cols);
-        for (int c0 = 0; c0 < half_cols; c0 += 32) {
+        const uint32_t tsk = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * ACC_STRIDE + (uint32_t)(g * ucols);
+        for (int c0 = 0; u_active && c0 < ucols; c0 += 32) {
           float v[32];
           tc::tmem_ld32(tsk + c0, v);
-          const int c_in_tile = g * half_cols + c0;
+          const int c_in_tile = g * ucols + c0;
           const int col0 = n0 + c_in_tile;
           if (row < p.M) {
             if (p.splits == 1) {
@@ -556,9 +555,9 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         // the scratch (each CTA of a pair counts its own half)
         unsigned* cnt = p.sk_counters + (size_t)tile * NCTA + rank;
         __threadfence();
-        asm volatile("bar.sync 1, 256;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
         if (threadIdx.x == 64) *s_last = (atomicAdd(cnt, 1u) == (unsigned)(p.splits - 1)) ? 1 : 0;
-        asm volatile("bar.sync 1, 256;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
         if (*s_last) {
           // this CTA's 128 x BN block of the tile's scratch is contiguous: walk it with coalesced 16-byte accesses,
           // several loads in flight per thread
@@ -568,16 +567,16 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           const int n4 = BM * p.BN / 4;
           const int bn4 = p.BN / 4;
           const int et = (int)threadIdx.x - 64;
-          for (int base = et; base < n4; base += 256 * 4) {
+          for (int base = et; base < n4; base += EPI_THREADS * 4) {
             float4 x[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-              const int i4 = base + 256 * u;
+              const int i4 = base + EPI_THREADS * u;
               x[u] = i4 < n4 ? __ldcg(blk + i4) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-              const int i4 = base + 256 * u;
+              const int i4 = base + EPI_THREADS * u;
               if (i4 < n4) {
                 __stcg(blk + i4, make_float4(0.f, 0.f, 0.f, 0.f));
                 const int rr = i4 / bn4, cc = (i4 - rr * bn4) * 4;
@@ -600,7 +599,7 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       // reduce-scatter epilogue: the last CTA of this rank's dX GEMM tells every rank that the partial sums in this
       // rank's buffer are complete
       __threadfence_system();
-      asm volatile("bar.sync 1, 256;" ::: "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
       if (threadIdx.x == 64) {
         if (atomicAdd(p.done_counter, 1u) == gridDim.x - 1) {
           *p.done_counter = 0u;
@@ -610,7 +609,7 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
       }
     }
-    if (EPI == E_TOPK && cur_m >= 0 && n_pan > 0) {
+    if (EPI == E_TOPK && cur_m >= 0 && u_active) {
       const int frow = cur_m * (BM * NCTA) + (int)rank * BM + r;
       if (frow < p.M) {
 #pragma unroll
@@ -800,7 +799,7 @@ static Plan make_plan(int layout, int epi, int M, int N, int K, int bn_forced, i
         const int stages = (int)(ring_bytes(epi) / bytes) < MAX_STAGES ? (int)(ring_bytes(epi) / bytes) : MAX_STAGES;
         if (t_kb < 3900.0 / stages) t_kb = 3900.0 / stages;          // load latency over the ring depth
         if (t_kb < 2.0 * bn) t_kb = 2.0 * bn;
-        const int n_pan = bn >= 128 ? bn / 128 : 1;
+        const int n_pan = 1;                                         // one staging panel per group and tile
         double tail;
         if (epi == E_SPLITK || epi == E_TOPK || epi == E_DX) tail = 800.0 * n_pan;
         else if (epi == E_STORE) tail = 1200.0 * n_pan;
@@ -890,7 +889,7 @@ RB_API int rb_enc_gemm(int dtype, int layout, int epi, const void* A, const void
 //   cand_ld >= rb_xfc_topk8_width(): every (CTA, epilogue group) writes the 8 best (value, column of W) it met in
 //   the row into its own 8 entries; entries nobody writes must have been pre-filled with -inf by the caller.
 // The k best of a row's candidates are the k best of the row (k <= 8).
-RB_API int rb_xfc_topk8_width(void) { return sm_count() * 2 * 8; }
+RB_API int rb_xfc_topk8_width(void) { return sm_count() * EGROUPS * 8; }
 
 RB_API int rb_xfc_topk8(int dtype, const void* X, const void* W, int B, int Ls, int D, int ldx, int ldw, float* cand_val,
                         int* cand_idx, int cand_ld, int* status, cudaStream_t st) {

@@ -1,5 +1,6 @@
 """Optimized (manual, loss-skipping) training equals the autograd default path step for step."""
 import numpy as np
+import pytest
 import torch
 
 from renee_b200.data import xcrepo
@@ -126,3 +127,24 @@ def test_accum_through_the_loader_equals_accum_one(tmp_path):
             if "k_lin.bias" in k:
                 continue        # its true gradient is zero (softmax is shift-invariant): Adam amplifies rounding noise
             torch.testing.assert_close(v, sd[k], rtol=1e-3, atol=1e-5, msg=lambda m: f"accum={accum} {k}: {m}")
+
+
+def test_flat_moments_are_remapped_by_name_when_the_layout_differs():
+    """The flat AdamW moments of a checkpoint written under another ordering of the flat buffer land at the right
+    parameters (and a parameter of another size is refused)."""
+    from types import SimpleNamespace
+    from renee_b200 import checkpoint as ck
+
+    def slot(o, k):
+        return SimpleNamespace(offset=o, numel=k)
+    enc = SimpleNamespace(slots={"b": slot(0, 4), "a": slot(4, 2)}, m=torch.zeros(6), v=torch.zeros(6))
+    old = {"layout": [("a", 0, 2), ("b", 2, 4)], "exp_avg": torch.arange(6.), "exp_avg_sq": torch.arange(6.) * 10}
+    ck._load_flat_moments(enc, old, "cpu")
+    assert enc.m.tolist() == [2., 3., 4., 5., 0., 1.]
+    assert enc.v.tolist() == [20., 30., 40., 50., 0., 10.]
+    same = {"layout": ck._flat_layout(enc), "exp_avg": torch.ones(6), "exp_avg_sq": torch.ones(6)}
+    ck._load_flat_moments(enc, same, "cpu")
+    assert enc.m.tolist() == [1.] * 6
+    bad = {"layout": [("a", 0, 3), ("b", 3, 3)], "exp_avg": torch.ones(6), "exp_avg_sq": torch.ones(6)}
+    with pytest.raises(RuntimeError):
+        ck._load_flat_moments(enc, bad, "cpu")
