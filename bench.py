@@ -38,6 +38,8 @@ CONFIGS = {
     "100m": dict(labels=100_000_000, seq=32, len_lo=6, batch=1024, lam=3.0, zipf=1.1, dropout=0.85),
     # the per-GPU share of 131k-s32 at 8 GPUs, runnable on one GPU (profiling of the small-shape regime)
     "131k-s32-shard8": dict(labels=16384, seq=32, len_lo=6, batch=32, lam=1.3, zipf=1.1, dropout=0.85),
+    "131k-s32-shard4": dict(labels=32768, seq=32, len_lo=6, batch=64, lam=1.3, zipf=1.1, dropout=0.85),
+    "131k-s32-shard2": dict(labels=65536, seq=32, len_lo=6, batch=128, lam=1.3, zipf=1.1, dropout=0.85),
     "tiny": dict(labels=8192, seq=32, len_lo=6, batch=64, lam=1.3, zipf=1.1, dropout=0.85),
 }
 

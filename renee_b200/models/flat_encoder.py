@@ -45,6 +45,13 @@ def _no_decay(name: str) -> bool:
     return any(nd in name for nd in ("bias", "LayerNorm.bias", "LayerNorm.weight"))
 
 
+# Tokens per step and GPU from which the own GEMMs are used in "auto" mode.  Measured step times on one B200, own /
+# library GEMMs: 16384 tokens 7.14 / 7.12 ms, 8192: 3.76 / 3.61, 4096: 2.41 / 2.23, 2048: 1.82 / 1.53, 1024: 1.48 /
+# 1.22 -- below 8192 tokens the fixed cost per launch of a persistent kernel (TMEM allocation, cluster start-up, a
+# serial K loop on the few SMs the tiles cover) outweighs the fused epilogues.
+OWN_GEMM_MIN_TOKENS = 8192
+
+
 @dataclass
 class _Slot:
     offset: int
@@ -123,13 +130,19 @@ class FlatEncoder:
         self._acts_key = None
         self._plan = None
         self.generation = 0
-        self.own_gemm = False
+        self.own_gemm = False          # whether the current step's linears run on the own GEMM kernels
+        self._own_mode = "0"
+        self._own_supported = False
         self._wgrad_stream = None
         if self.device.type == "cuda" and act_dtype != torch.float32:
             import os
             from ..ops import cuda as cu
-            self.own_gemm = cu.enc_gemm_supported(self.p16, H, Fd)
-            if self.own_gemm and os.environ.get("RENEE_B200_WGRAD_STREAM", "1") != "0":
+            # RENEE_B200_OWN_GEMM: 1 = the own tcgen05 GEMMs with fused epilogues always, 0 = library GEMMs + separate
+            # element-wise kernels, auto (default) = own from OWN_GEMM_MIN_TOKENS tokens per step and GPU upwards
+            self._own_mode = os.environ.get("RENEE_B200_OWN_GEMM", "auto")
+            self._own_supported = cu.enc_gemm_supported(self.p16, H, Fd)
+            self.own_gemm = self._own_supported and self._own_mode != "auto"
+            if self._own_supported and os.environ.get("RENEE_B200_WGRAD_STREAM", "1") != "0":
                 # weight-gradient GEMMs are off the critical path of the backward pass (nothing reads them before
                 # the optimizer): they run on a second stream, where they fill the SMs that the data-gradient
                 # GEMMs' last partial wave of tiles leaves idle (and, at small token counts, the SMs those GEMMs
@@ -218,6 +231,8 @@ class FlatEncoder:
         self._alloc(b, S)
         A = self._acts
         T, H = b * S, cfg.dim
+        if self._own_mode == "auto":
+            self.own_gemm = self._own_supported and T >= OWN_GEMM_MIN_TOKENS
         P = self.p16
         pd = cfg.dropout if train else 0.0
         pa = cfg.attention_dropout if train else 0.0

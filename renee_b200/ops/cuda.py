@@ -329,7 +329,7 @@ _SK: dict = {}
 def enc_gemm_supported(t: torch.Tensor, *dims: int) -> bool:
     """The own GEMMs serve 16-bit CUDA tensors whose feature dimensions are multiples of 64."""
     return bool(t.is_cuda and t.dtype in (torch.bfloat16, torch.float16) and all(d % 64 == 0 for d in dims)
-                and os.environ.get("RENEE_B200_OWN_GEMM", "1") != "0")
+                and os.environ.get("RENEE_B200_OWN_GEMM", "auto") != "0")
 
 
 def _enc_gemm(layout, epi, A, B, C, M, N, K, bias=None, R=None, F=None, p=0.0, rng=None, stream=0, colacc=None,

@@ -175,6 +175,23 @@ def _engine(own: bool, S=32, b=24):
     return enc
 
 
+def test_flat_encoder_picks_the_gemm_path_by_token_count():
+    """Default mode: library GEMMs below OWN_GEMM_MIN_TOKENS tokens per step, the own kernels from there on."""
+    from renee_b200.models.encoder import EncoderConfig
+    from renee_b200.models import flat_encoder as fe
+    from renee_b200.ops import StepRNG
+    os.environ.pop("RENEE_B200_OWN_GEMM", None)
+    enc = fe.FlatEncoder(EncoderConfig(n_layers=1), dev(), torch.bfloat16, "cls", 0, seed=3)
+    rng = StepRNG(1, torch.tensor([1], dtype=torch.int32, device=dev()))
+    for b, S in ((8, 32), (fe.OWN_GEMM_MIN_TOKENS // 32, 32)):
+        ids = torch.randint(1000, 30000, (b, S), device=dev(), dtype=torch.int32)
+        mask = torch.ones(b, S, device=dev(), dtype=torch.int32)
+        out = enc.forward(ids, mask, rng, train=False)
+        assert enc.own_gemm == (b * S >= fe.OWN_GEMM_MIN_TOKENS)
+        assert torch.isfinite(out).all()
+    cu().check_status()
+
+
 @pytest.mark.parametrize("S,b", [(32, 24), (20, 7)])
 def test_flat_encoder_on_own_gemms_matches_library_gemms(S, b):
     """Same weights, same dropout seeds: forward output and every parameter gradient agree to 16-bit tolerance."""

@@ -383,8 +383,8 @@ def test_trainer_step_on_gpu_tracks_cpu_reference():
 
 
 @pytest.mark.parametrize("accum", [1, 2, 4])
-def test_trainer_on_tensor_core_path_tracks_cpu_fp32_trainer(accum):
-    """bf16 encoder on the own tcgen05 GEMMs + fp16 classifier on the tcgen05 classifier kernels (the benchmark's
+def test_trainer_on_tensor_core_path_tracks_cpu_fp32_trainer(accum, monkeypatch):
+    """bf16 encoder on the own tcgen05 GEMMs (forced: by default they take over from 8192 tokens per step) + fp16 classifier on the tcgen05 classifier kernels (the benchmark's
     path), three steps at dropout 0 with a partial final batch, against the CPU fp32 trainer; also with split
     accumulation (label chunks), whose result must not depend on ``accum``."""
     import numpy as np
@@ -411,6 +411,7 @@ def test_trainer_on_tensor_core_path_tracks_cpu_fp32_trainer(accum):
                                 XCCollator(sh, ds, 0, accum, max(1, 32 // accum), True))
         return XCTrainer(cfg, enc, sh, DistContext(device=torch.device(device)), steps_per_epoch=3), loader
 
+    monkeypatch.setenv("RENEE_B200_OWN_GEMM", "1")
     a, la = make("cuda:0", fp16xfc=True)                       # bf16 encoder, fp16 W + momentum
     b, lb = make("cpu", fp32encoder=True, fp16xfc=False)
     assert a.encoder.own_gemm and a.xfc.dtype == torch.float16
