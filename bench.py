@@ -31,7 +31,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 CONFIGS = {
-    # BASELINE configs 2-5 (config 1 is the CPU plumbing run: tests/test_cpu_plumbing.py)
+    # the benchmark workloads: 131 K labels at sequence lengths 32 and 128, 1.3 M and 100 M labels (the small CPU
+    # plumbing workload is tests/test_cpu_plumbing.py)
     "131k-s32": dict(labels=131072, seq=32, len_lo=6, batch=256, lam=1.3, zipf=1.1, dropout=0.85),
     "131k-s128": dict(labels=131072, seq=128, len_lo=32, batch=128, lam=4.5, zipf=1.1, dropout=0.85),
     "1.3m": dict(labels=1310720, seq=32, len_lo=6, batch=512, lam=21.0, zipf=1.05, dropout=0.85),

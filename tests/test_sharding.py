@@ -1,4 +1,6 @@
 """Label padding/sharding rule (reference main.py:76-97) and batch row split (dl_base.py:348-358)."""
+import pytest
+
 from renee_b200.utils.sharding import batch_row_range, shard_labels
 
 
@@ -27,3 +29,39 @@ def test_batch_rows_cover_and_spread_remainder():
                 assert a[1] == b[0]
             sizes = [e - s for s, e in rows]
             assert max(sizes) - min(sizes) <= 1 and sizes == sorted(sizes, reverse=True)
+
+
+@pytest.mark.parametrize("G", [2, 3, 8])
+def test_gradient_buckets_partition_the_flat_buffer(G):
+    """Every rank owns 1/G of every bucket of the flat gradient buffer: over all ranks the owned ranges cover the
+    buffer exactly once, on 16-byte boundaries, and the reduce plan of a rank is its owned ranges in backward order
+    with consecutive offsets into its fp32 sum buffer."""
+    from types import SimpleNamespace
+
+    import torch
+
+    from renee_b200.models.encoder import EncoderConfig
+    from renee_b200.models.flat_encoder import FlatEncoder
+    from renee_b200.parallel.fused import PeerCollectives
+
+    enc = FlatEncoder(EncoderConfig(dim=128, n_layers=3, n_heads=2, hidden_dim=256, vocab_size=200, max_position_embeddings=16),
+                      "cpu", torch.float32, "cls", 0, seed=1)
+    covered = torch.zeros(enc.numel, dtype=torch.int32)
+    for rank in range(G):
+        pc = SimpleNamespace(G=G, rank=rank, gsum=None, ctx=SimpleNamespace(device=torch.device("cpu")))
+        plan = PeerCollectives._buckets(pc, enc)
+        pc._buckets = lambda e, _pc=pc: _pc._bucket_plan
+        owned = PeerCollectives.owned_ranges(pc, enc, rank)
+        assert sorted((a * 8, b * 8) for _, a, b, _ in plan) == sorted(owned)
+        stages = [s for s, _, _, _ in plan]
+        assert stages == sorted(stages) and stages[0] == 1 and stages[-1] == enc.cfg.n_layers + 1
+        g = 0
+        for _, a, b, g0 in plan:
+            assert g0 == g and b > a
+            g += b - a
+        assert pc.gsum.numel() >= g * 8
+        for a, b in owned:
+            assert a % 8 == 0 and b % 8 == 0
+            covered[a:b] += 1
+    n = enc.numel // 8 * 8
+    assert int(covered[:n].min()) == 1 and int(covered[:n].max()) == 1
