@@ -82,7 +82,13 @@ def _cases(dev, dt, NS):
             else:
                 f, db = rn(Tn, K), vec(K)
                 extra = Tn * K * 2
-                fn = lambda i: cu.linear_dgrad(dy[i], W, out[i], "gelu_bwd", pre=f[i], dbias=db)
+                # as in the engine's backward pass: the bias-gradient column sums only accumulate here, one launch
+                # at the end of the pass converts all of them
+                plan = cu.DeferredColumns(dev, dt)
+
+                def fn(i):
+                    with cu.deferred_columns(plan):
+                        cu.linear_dgrad(dy[i], W, out[i], "gelu_bwd", pre=f[i], dbias=db)
             return fn, NS, (Tn * N + N * K + Tn * K) * 2 + extra, 2.0 * Tn * K * N
         return make
 
