@@ -228,6 +228,14 @@ def _cases(dev, dt, NS):
         return (lambda i: cu.topk_rows(Zt[i], L, 100, 0, ov, oi)), NS, B * L * 4, 0.0
     yield "topk_rows k=100", topk
 
+    def topk_fused():
+        # prediction with k = 5 over a 131072-label shard: W is read once, no logits are written
+        B, L, D = 256, 131072, 768
+        X = torch.randn(B, D, device=dev).half()
+        W = [(torch.randn(L, D, device=dev) * 0.05).half() for _ in range(2)]
+        return (lambda i: cu.xfc_topk8(W[i % 2], X, 5)), 2, L * D * 2 + B * D * 2, 2.0 * B * L * D
+    yield "xfc_topk k=5 fused into the logits GEMM (B=256, L=131072; all its launches)", topk_fused
+
     def adamw():
         n = 66_400_000 // 1024 * 1024
         p32, am, av = torch.zeros(n, device=dev), torch.zeros(n, device=dev), torch.zeros(n, device=dev)
