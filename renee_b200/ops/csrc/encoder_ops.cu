@@ -239,8 +239,8 @@ __device__ __forceinline__ void smem_add8(float* p, const float (&v)[8]) {
   *reinterpret_cast<float4*>(p + 4) = b;
 }
 
-template <typename T, int NV, bool EMBED>
-__global__ void __launch_bounds__(128, 6) ln_bwd_kernel(
+template <typename T, int NV, bool EMBED, int WARPS = 4>
+__global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 6 : (WARPS == 8 ? 2 : 1)) ln_bwd_kernel(
     const T* __restrict__ dy, const T* __restrict__ pre, const int* __restrict__ ids,
     const T* __restrict__ word, const T* __restrict__ pos, const T* __restrict__ gamma,
     const float* __restrict__ mean, const float* __restrict__ rstd,
@@ -597,9 +597,10 @@ RB_API int rb_embed_ln_fwd(int dtype, const int* ids, const void* word, const vo
   return 0;
 }
 
-static int ln_bwd_blocks(int rows, int S, bool embed) {
-  int blocks = (rows + 3) / 4;
-  if (blocks > sm_count() * 5) blocks = sm_count() * 5;
+static int ln_bwd_blocks(int rows, int S, bool embed, int warps = 4) {
+  int blocks = (rows + warps - 1) / warps;
+  const int per_sm = warps == 4 ? 5 : (warps == 8 ? 2 : 1);
+  if (blocks > sm_count() * per_sm) blocks = sm_count() * per_sm;
   if (embed) {  // total warps (4 per block) must be a multiple of S: round blocks to a multiple of S
     blocks = (blocks / S) * S;
     if (blocks == 0) blocks = S;
@@ -607,20 +608,37 @@ static int ln_bwd_blocks(int rows, int S, bool embed) {
   return blocks;
 }
 
-RB_API int rb_bias_dropout_add_ln_bwd(int dtype, const void* dy, const void* pre, const void* gamma, const float* mean,
-                                      const float* rstd, void* d_pre, void* d_branch, float* acc, unsigned* counter,
-                                      void* dgamma, void* dbeta, void* dbias, int rows, int H, float p, const int* seed,
-                                      unsigned stream_id, cudaStream_t st) {
-  if (H % 8) return -3;
-  const int blocks = ln_bwd_blocks(rows, 1, false);
-  const size_t smem = 4 * 3 * (size_t)H * sizeof(float);
-  DISPATCH_T(dtype, DISPATCH_NV(H, (cudaFuncSetAttribute(ln_bwd_kernel<T, NV, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                                    launch_pdl(ln_bwd_kernel<T, NV, false>, dim3(blocks), dim3(128), smem, st,
+// Warps per CTA of the LayerNorm backward kernel.  Every CTA ends with a flush of its 3 H column sums into the fp32
+// replicas (L2 reductions); fewer, larger CTAs flush less often per row.
+static int g_ln_bwd_warps = 8;
+RB_API void rb_set_ln_bwd_warps(int w) { g_ln_bwd_warps = (w == 8 || w == 16) ? w : 4; }
+
+template <int WARPS>
+static int launch_ln_bwd(int dtype, const void* dy, const void* pre, const void* gamma, const float* mean,
+                         const float* rstd, void* d_pre, void* d_branch, float* acc, unsigned* counter, void* dgamma,
+                         void* dbeta, void* dbias, int rows, int H, float p, const int* seed, unsigned stream_id,
+                         cudaStream_t st) {
+  const int blocks = ln_bwd_blocks(rows, 1, false, WARPS);
+  const size_t smem = (size_t)WARPS * 3 * (size_t)H * sizeof(float);
+  DISPATCH_T(dtype, DISPATCH_NV(H, (cudaFuncSetAttribute(ln_bwd_kernel<T, NV, false, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                                    launch_pdl(ln_bwd_kernel<T, NV, false, WARPS>, dim3(blocks), dim3(WARPS * 32), smem, st,
       (const T*)dy, (const T*)pre, (const int*)nullptr, (const T*)nullptr, (const T*)nullptr, (const T*)gamma, mean, rstd,
       (T*)d_pre, (T*)d_branch, (T*)nullptr, (T*)nullptr, acc, counter, (T*)dgamma, (T*)dbeta, (T*)dbias, rows, H, 1, 0, p,
       seed, stream_id))));
   RB_LAUNCH_CHECK();
   return 0;
+}
+
+RB_API int rb_bias_dropout_add_ln_bwd(int dtype, const void* dy, const void* pre, const void* gamma, const float* mean,
+                                      const float* rstd, void* d_pre, void* d_branch, float* acc, unsigned* counter,
+                                      void* dgamma, void* dbeta, void* dbias, int rows, int H, float p, const int* seed,
+                                      unsigned stream_id, cudaStream_t st) {
+  if (H % 8) return -3;
+  int w = g_ln_bwd_warps;
+  while (w > 4 && (size_t)w * 3 * H * sizeof(float) > 200 * 1024) w >>= 1;     // the per-warp column sums must fit
+  if (w == 16) return launch_ln_bwd<16>(dtype, dy, pre, gamma, mean, rstd, d_pre, d_branch, acc, counter, dgamma, dbeta, dbias, rows, H, p, seed, stream_id, st);
+  if (w == 8) return launch_ln_bwd<8>(dtype, dy, pre, gamma, mean, rstd, d_pre, d_branch, acc, counter, dgamma, dbeta, dbias, rows, H, p, seed, stream_id, st);
+  return launch_ln_bwd<4>(dtype, dy, pre, gamma, mean, rstd, d_pre, d_branch, acc, counter, dgamma, dbeta, dbias, rows, H, p, seed, stream_id, st);
 }
 
 RB_API int rb_embed_ln_bwd(int dtype, const void* dy, const int* ids, const void* word, const void* pos,

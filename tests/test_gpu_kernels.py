@@ -27,11 +27,24 @@ def tol(dt):
     return dict(rtol=2e-2, atol=2e-2) if dt != torch.float32 else dict(rtol=2e-4, atol=2e-5)
 
 
+@pytest.fixture
+def ln_bwd_warps():
+    """Sets the number of warps per CTA of the LayerNorm backward kernel for one test."""
+    import ctypes
+
+    def set_(w):
+        cu().lib().rb_set_ln_bwd_warps(ctypes.c_int(w))
+    yield set_
+    set_(cu().LN_BWD_WARPS)
+
+
+@pytest.mark.parametrize("warps", [4, 8, 16])
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32, torch.float16])
 @pytest.mark.parametrize("H,p", [(768, 0.1), (128, 0.0), (384, 0.3)])
-def test_bias_dropout_add_ln(dt, H, p):
+def test_bias_dropout_add_ln(dt, H, p, warps, ln_bwd_warps):
     torch.manual_seed(0)
-    T = 77
+    T = 77 if warps == 4 else 1500            # the larger case gives every warp of the bigger CTAs several rows
+    ln_bwd_warps(warps)
     x, res = torch.randn(T, H, device=dev()).to(dt), torch.randn(T, H, device=dev()).to(dt)
     bias, gam, bet = [torch.randn(H, device=dev()).to(dt) for _ in range(3)]
     rng = _rng()
