@@ -39,6 +39,8 @@ class XCBatch:
     pos_labels: torch.Tensor | None = None    # [nnz] int32, label id inside this rank's shard (ascending)
     row_ids: np.ndarray | None = None   # global dataset rows (for evaluation bookkeeping)
     dense_targets: torch.Tensor | None = None  # [B, Ls] float (default/autograd path only)
+    uploaded: object = None             # callable or None: the consumer calls it once its host-to-device copies of
+                                        # this batch are issued (pinned staging slots of PrefetchLoader)
 
     @property
     def z(self) -> torch.Tensor:
@@ -130,16 +132,71 @@ class GlobalBatchSampler:
             yield perm[s: s + self.global_batch]
 
 
+class _StagingSlot:
+    """One set of page-locked host buffers that successive batches are copied into.  Allocating page-locked
+    memory per batch goes through the driver (and, once the consumer runs ahead of the device, cannot be served from
+    a cache, because the previous blocks are still being read by queued copies); a fixed ring is allocated once.
+    A slot is refilled only after the copies issued from its previous batch have completed: the consumer records
+    an event behind them (``XCBatch.uploaded``), the loader thread waits for it.  A consumer that never calls
+    ``uploaded`` costs a device synchronisation at reuse instead."""
+
+    NAMES = ("input_ids", "attention_mask", "pos_rows", "pos_labels")
+
+    def __init__(self):
+        self.bufs: dict = {}
+        self.event = None
+        self.handed_out = False
+
+    def _buffer(self, name: str, t: torch.Tensor) -> torch.Tensor:
+        buf = self.bufs.get(name)
+        n = t.numel()
+        if buf is None or buf.numel() < n or buf.dtype != t.dtype:
+            buf = torch.empty(max(n + n // 4, 64), dtype=t.dtype)
+            if torch.cuda.is_available():
+                buf = buf.pin_memory()
+            self.bufs[name] = buf
+        return buf[:n].view(t.shape)
+
+    def wait(self) -> None:
+        if not self.handed_out:
+            return
+        if self.event is not None:
+            self.event.synchronize()
+        elif torch.cuda.is_available():
+            torch.cuda.synchronize()
+        self.handed_out, self.event = False, None
+
+    def mark_uploaded(self) -> None:
+        if torch.cuda.is_available():
+            ev = torch.cuda.Event()
+            ev.record()
+            self.event = ev
+
+    def fill(self, b: XCBatch) -> XCBatch:
+        for name in self.NAMES:
+            t = getattr(b, name)
+            if isinstance(t, torch.Tensor):
+                v = self._buffer(name, t)
+                v.copy_(t)
+                setattr(b, name, v)
+        b.uploaded = self.mark_uploaded
+        self.handed_out = True
+        return b
+
+
 class PrefetchLoader:
     """Background-thread loader: collates the next batches while the device runs the current step.
     (The reference uses 4 DataLoader worker processes, main.py:102; collation here is a handful of
-    numpy gathers, so one thread and pinned staging buffers are enough.)"""
+    numpy gathers, so one thread and a ring of pinned staging buffers are enough.)"""
 
     def __init__(self, sampler: GlobalBatchSampler, collator: XCCollator, depth: int = 3, pin: bool = False):
         self.sampler = sampler
         self.collator = collator
         self.depth = depth
         self.pin = pin
+        # a batch can be in the queue (depth), in the consumer's hands (1) or being filled (1)
+        self._slots = [_StagingSlot() for _ in range(depth + 2)] if pin else []
+        self._next_slot = 0
 
     def __len__(self) -> int:
         return len(self.sampler)
@@ -161,7 +218,12 @@ class PrefetchLoader:
                     if stop.is_set():
                         return
                     b = self.collator(ids)
-                    q.put(b.pin() if self.pin else b)
+                    if self.pin:
+                        slot = self._slots[self._next_slot]
+                        self._next_slot = (self._next_slot + 1) % len(self._slots)
+                        slot.wait()
+                        b = slot.fill(b)
+                    q.put(b)
                 q.put(None)
             except BaseException as exc:  # surfaced to the consumer
                 q.put(exc)

@@ -228,6 +228,8 @@ class XCTrainer:
         bf["pos_rows"][:nnz].copy_(batch.pos_rows, non_blocking=True)
         bf["pos_labels"][:nnz].copy_(batch.pos_labels, non_blocking=True)
         bf["nnz"].fill_(nnz)
+        if batch.uploaded is not None:
+            batch.uploaded()            # the loader may refill the batch's staging buffers once these copies are done
         return b, nnz
 
     def h2d_bytes(self, batch: XCBatch) -> int:

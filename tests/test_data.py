@@ -101,3 +101,29 @@ def test_sampler_same_on_every_rank_and_keeps_partial_batch():
     assert a == b and len(a) == len(s) == 7 and len(a[-1]) == 7
     assert sorted(sum(a, [])) == list(range(103))
     assert a != [x.tolist() for x in s.epoch(4)]
+
+
+def test_prefetch_loader_staging_ring_delivers_the_collated_batches():
+    """``pin=True``: batches are copied into a fixed ring of staging buffers (page-locked on a GPU box).  Every batch
+    must arrive intact although the ring is shorter than the epoch, a slot is refilled only after its batch was
+    handed over and acknowledged, and the ring does not grow."""
+    from renee_b200.data.collate import PrefetchLoader
+    spec = SyntheticSpec(num_labels=512, seq_len=12, len_lo=3, len_hi=12, poisson_lam=2.0, seed=5)
+    ids, mask, lab = SyntheticXC(spec).rows(np.arange(90))
+    ds = xcrepo.InMemoryDataset(ids, mask, lab)
+    sh = shard_labels(512, 2)
+    coll = XCCollator(sh, ds, 1, 1, 8, True)
+    loader = PrefetchLoader(GlobalBatchSampler(90, 8, True, 3), coll, depth=2, pin=True)
+    assert len(loader._slots) == 4
+    for epoch in range(2):
+        want = [coll(rows) for rows in GlobalBatchSampler(90, 8, True, 3).epoch(epoch)]
+        n, acked = 0, []
+        for got, ref_b in zip(loader.epoch(epoch), want):
+            for name in ("input_ids", "attention_mask", "pos_rows", "pos_labels"):
+                assert torch.equal(getattr(got, name), getattr(ref_b, name)), (epoch, n, name)
+            assert got.batch_size == ref_b.batch_size and callable(got.uploaded)
+            acked.append(got.input_ids.data_ptr())
+            got.uploaded()
+            n += 1
+        assert n == len(want) == 12
+        assert len(set(acked)) <= 4                       # the same four slots, over and over
