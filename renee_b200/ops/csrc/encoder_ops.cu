@@ -610,7 +610,7 @@ static int ln_bwd_blocks(int rows, int S, bool embed, int warps = 4) {
 
 // Warps per CTA of the LayerNorm backward kernel.  Every CTA ends with a flush of its 3 H column sums into the fp32
 // replicas (L2 reductions); fewer, larger CTAs flush less often per row.
-static int g_ln_bwd_warps = 8;
+static int g_ln_bwd_warps = 4;
 RB_API void rb_set_ln_bwd_warps(int w) { g_ln_bwd_warps = (w == 8 || w == 16) ? w : 4; }
 
 template <int WARPS>

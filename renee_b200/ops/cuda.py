@@ -33,8 +33,9 @@ def lib():
     return _LIB
 
 
-LN_BWD_WARPS = 8     # warps per CTA of the LayerNorm backward kernel (4, 8 or 16; RENEE_B200_LN_BWD_WARPS overrides): measured
-                     # 34.9 / 29.2 / 30.6 us for 8192 x 768 with 4 / 8 / 16
+LN_BWD_WARPS = 4     # warps per CTA of the LayerNorm backward kernel (4, 8 or 16; RENEE_B200_LN_BWD_WARPS overrides).  Measured:
+                     # 8192 x 768 alone 34.9 / 29.2 / 30.6 us with 4 / 8 / 16, but the training step does not gain (3.75 /
+                     # 3.74 / 3.73 ms at 8192 tokens) and loses 5 % at 4096 tokens per GPU (2.43 / 2.56 / 2.57 ms)
 
 
 def _load():
