@@ -36,6 +36,8 @@ dX flag, which q raised after its step-n pull in stream order.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -60,7 +62,6 @@ class PeerCollectives(TorchCollectives):
         # PeerFailure exit of one rank while its memory is bound to a multicast object can raise NVLink
         # faults on the other ranks' GPUs, and the bounded flag waits do not cover a multimem access whose
         # member has gone.  The default stays on plain peer loads/stores over CUDA IPC mappings.
-        import os
         self.use_nvls = (os.environ.get("RENEE_B200_NVLS", "0") == "1") if use_nvls is None else bool(use_nvls)
         self._mc_grad = 0
         self._mc_p16 = 0
@@ -226,7 +227,11 @@ class PeerCollectives(TorchCollectives):
 
     def backward_begin(self, enc) -> None:
         """Called before the encoder backward: the reduction of finished buckets runs on a second stream."""
-        if not self._sharded(enc):
+        # Opt-in (RENEE_B200_RS_OVERLAP=1).  Measured on B200s at the 131 K-label config, overlapped / in one piece after
+        # the pass: 2.42 / 2.31 ms per step on 2 GPUs, 1.75 / 1.66 on 4 (and 5.53 / 5.49 at 1.3 M labels on 2): the
+        # per-layer signal kernels and the bucket kernels' share of the SMs cost the short backward pass of a rank
+        # more than the hidden transfer (at most 133 MB of 16-bit gradients over NVLink, about 0.15 ms) saves.
+        if not self._sharded(enc) or os.environ.get("RENEE_B200_RS_OVERLAP", "0") != "1":
             return
         self._buckets(enc)
         if self._comm_stream is None:

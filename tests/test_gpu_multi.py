@@ -134,12 +134,14 @@ def _shard_worker(rank, world, port, out_dir):
         shutdown()
 
 
-@pytest.mark.parametrize("world", [2, 4, 8])
-def test_sharding_invariance_against_one_gpu(tmp_path, world):
+@pytest.mark.parametrize("world,overlap", [(2, "0"), (2, "1"), (4, "0"), (8, "0")])
+def test_sharding_invariance_against_one_gpu(tmp_path, world, overlap, monkeypatch):
     """Label-sharded training on G GPUs gives the single-GPU weights: the classifier shards, concatenated, equal
-    the G = 1 matrix and every rank's encoder equals the G = 1 encoder (up to summation order in 16 bits)."""
+    the G = 1 matrix and every rank's encoder equals the G = 1 encoder (up to summation order in 16 bits).  With
+    two GPUs also with the gradient reduce-scatter issued bucket by bucket under the backward pass (opt-in)."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
+    monkeypatch.setenv("RENEE_B200_RS_OVERLAP", overlap)      # inherited by the spawned ranks
     out = str(tmp_path)
     mp.spawn(_shard_worker, args=(1, _free_port(), out), nprocs=1, join=True)
     mp.spawn(_shard_worker, args=(world, _free_port(), out), nprocs=world, join=True)
