@@ -316,6 +316,32 @@ def test_xfc_logits_grad_and_dx_on_the_persistent_gemm(B, D, Lc, nnz):
     torch.testing.assert_close(dX, ref.xfc_dx(Gt[:, :B], W, 4096.0), rtol=2e-3, atol=4096.0 * 2e-3)
 
 
+def test_xfc_kernels_at_the_benchmark_chunk_shape():
+    """The three classifier kernels at the shape the one-GPU benchmark runs them at (256 rows, 768 dims, the whole
+    131072-label shard as one chunk), against the PyTorch oracle."""
+    B, D, Lc, nnz = 256, 768, 131072, 400
+    X, W, rows, labels = _xfc_problem(B, D, Lc, nnz, seed=11)
+    Gt = torch.empty(Lc, B, dtype=torch.float16, device=dev())
+    n = torch.tensor([rows.numel()], dtype=torch.int32, device=dev())
+    cu().xfc_logits_grad_v2(W, X, Gt, B, rows, labels, n, 0)
+    cu().check_status()
+    Gr, _ = ref.xfc_logit_grad(X, W, rows, labels)
+    torch.testing.assert_close(Gt.float(), Gr.float(), rtol=2e-3, atol=2e-3)
+    hp = HyperParams(dev(), init_scale=64.0)
+    hp.buf[HP.LR_XFC] = 0.05
+    dX = torch.zeros(B, D, device=dev())
+    cu().xfc_dx_v2(Gt, B, W, B, dX, hp.buf)
+    cu().check_status()
+    torch.testing.assert_close(dX, ref.xfc_dx(Gt, W, 64.0), rtol=5e-3, atol=64.0 * 2e-2)
+    M = torch.zeros(Lc, D, dtype=torch.float16, device=dev())
+    Wr, Mr = W.float().clone(), M.float().clone()
+    ref.sgd_update(Wr, Mr, Gt.float() @ X.float(), 0.05, 0.9, 1e-3)
+    cu().xfc_dw_sgd(Gt, B, X, W, M, hp.buf, 0.9, 1e-3, v2=True)
+    cu().check_status()
+    torch.testing.assert_close(M.float(), Mr, rtol=2e-3, atol=2e-3)
+    torch.testing.assert_close(W.float(), Wr, rtol=2e-3, atol=2e-3)
+
+
 @pytest.mark.parametrize("v2", [False, True], ids=["tile-per-cta", "persistent-pairs"])
 @pytest.mark.parametrize("B,D,Lc,nnz", XFC_SHAPES)
 def test_xfc_dw_sgd(B, D, Lc, nnz, v2):
