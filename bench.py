@@ -209,6 +209,7 @@ def run_ours(args) -> dict:
     e2e_ms = f0.elapsed_time(f1)
     clocks = sampler.stop() if rank == 0 else None
     cu.check_status()
+    tr.check_device_status()          # bounded waits all met; with RENEE_B200_GUARD=1 also every guard band intact
     assert tr.n_captures == captures0, "a CUDA-graph capture landed inside a timed region"
     t = torch.tensor([ms, pre_ms, e2e_ms, per_step[0], per_step[K // 2], per_step[-1]], dtype=torch.float64,
                      device=ctx.device)
@@ -236,6 +237,7 @@ def run_ours(args) -> dict:
                       "cuda_graph": tr.graph_active(), "fused_comm": comm is not None,
                       "nvls": bool(comm is not None and comm.use_nvls), "watchdog": tr.watchdog is not None,
                       "own_gemm": bool(getattr(tr.encoder, "own_gemm", False)),
+                      "guard_bands": "intact" if os.environ.get("RENEE_B200_GUARD") == "1" else "off",
                       "persistent_logits": bool(args.persistent_logits)},
            "clocks": clocks,
            "e2e": {"value": round(B * K / (e2e_ms / 1e3), 2), "unit": "samples/s", "ms_per_step": round(e2e_ms / K, 4),
