@@ -94,6 +94,7 @@ struct Params {
   // SIGMOID_POS (classifier logits + gradient): label-sorted positives, label id of row 0, all-gather flags to wait for
   const int* pos_rows; const int* pos_labels; const int* nnz_ptr; int label0;
   const uint32_t* wait_flags; int wait_n; const uint32_t* step_ptr;
+  float* loss_acc;               // SIGMOID_POS, loss-sampling steps: += sum of softplus(z) over the valid logits
   // DX (classifier input gradient): fp32 accumulation target, loss scale, completion signal to the peers
   float* dX; int ldX; const float* hp;
   unsigned* done_counter; void* peer_flags[16]; int n_peers; int flag_index;
@@ -305,6 +306,7 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     float tv[8];
     int ti[8];
     int cur_m = -1;
+    float loss = 0.f;                                     // SIGMOID_POS: this thread's share of sum softplus(z)
     const int slot = ((int)blockIdx.x * EGROUPS + g) * 8;
     for (int item = unit; item < n_items; item += n_units, ++t_local) {
       const int tile = item / p.splits;
@@ -370,6 +372,13 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
                 for (int j = 0; j < 8; ++j) o[j] = a[j];
               } else if (EPI == E_SIGMOID_POS) {
+                if (p.loss_acc != nullptr && row < p.M) {
+                  // sampled loss (dl_base.py:579-583): softplus of every logit here; minus the logits at the positives
+                  // by a separate small kernel
+#pragma unroll
+                  for (int j = 0; j < 8; ++j)
+                    if (c + j < p.N) loss += fmaxf(a[j], 0.f) + log1pf(__expf(-fabsf(a[j])));
+                }
 #pragma unroll
                 for (int j = 0; j < 8; ++j) o[j] = (c + j < p.N) ? 1.f / (1.f + __expf(-a[j])) : 0.f;
               } else if (EPI == E_BIAS_GELU) {
@@ -595,6 +604,10 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
     }
     if (STAGED && elected) tc::tma_store_wait_read<0>();   // the stores have read shared memory; they complete before the grid does
+    if (EPI == E_SIGMOID_POS && p.loss_acc != nullptr) {
+      loss = warp_sum(loss);
+      if (lane == 0 && loss != 0.f) atomicAdd(p.loss_acc, loss);
+    }
     if (EPI == E_DX && p.done_counter != nullptr) {
       // reduce-scatter epilogue: the last CTA of this rank's dX GEMM tells every rank that the partial sums in this
       // rank's buffer are complete
@@ -944,7 +957,7 @@ static int launch_planned(const Plan& pl, bool bf16, int layout, int epi, const 
 // sigmoid-GEMM (xfc_gemm_kernel.cu:59-100).
 RB_API int rb_xfc_logits_grad_v2(const void* W, int Lc, int D, const void* X, int B, void* Gt, int ldG, const int* pos_rows,
                                  const int* pos_labels, const int* nnz_ptr, int label0, const unsigned* wait_flags,
-                                 int wait_n, const unsigned* step_ptr, int* status, cudaStream_t st) {
+                                 int wait_n, const unsigned* step_ptr, float* loss_acc, int* status, cudaStream_t st) {
   if (D % 8 || ldG % 8 || Lc < 1 || B < 1 || ldG < B) return -3;
   const Plan pl = make_plan(L_NT, E_SIGMOID_POS, Lc, B, D, 0, 0);
   Maps m;
@@ -958,7 +971,7 @@ RB_API int rb_xfc_logits_grad_v2(const void* W, int Lc, int D, const void* X, in
   Params p{};
   p.M = Lc; p.N = B; p.status = status;
   p.pos_rows = pos_rows; p.pos_labels = pos_labels; p.nnz_ptr = nnz_ptr; p.label0 = label0;
-  p.wait_flags = wait_flags; p.wait_n = wait_n; p.step_ptr = step_ptr;
+  p.wait_flags = wait_flags; p.wait_n = wait_n; p.step_ptr = step_ptr; p.loss_acc = loss_acc;
   rc = launch_planned(pl, false, L_NT, E_SIGMOID_POS, m, p, D, st);
   if (rc) return rc;
   RB_LAUNCH_CHECK();

@@ -477,13 +477,14 @@ def xfc_v2() -> bool:
     return os.environ.get("RENEE_B200_XFC_V2", "1") != "0"
 
 
-def xfc_logits_grad_v2(W, X, Gt, ldG, pos_rows, pos_labels, nnz, label0, wait=None):
+def xfc_logits_grad_v2(W, X, Gt, ldG, pos_rows, pos_labels, nnz, label0, wait=None, loss_acc=None):
+    """``Gt = sigmoid(W Xᵀ) - Y`` on the persistent CTA-pair GEMM; with ``loss_acc`` also ``+= Σ softplus(z)``."""
     Lc, D = W.shape
     B = X.shape[0]
     ws = workspace(W.device)
     wf, wn, wstep = (wait if wait is not None else (None, 0, None))
     _call("rb_xfc_logits_grad_v2", _p(W), _I(Lc), _I(D), _p(X), _I(B), _p(Gt), _I(ldG), _p(pos_rows), _p(pos_labels), _p(nnz),
-          _I(label0), _p(wf), _I(wn), _p(wstep), _p(ws.status), _stream())
+          _I(label0), _p(wf), _I(wn), _p(wstep), _p(loss_acc), _p(ws.status), _stream())
 
 
 def xfc_dx_v2(Gt, ldG, W, B, dX, hp_buf, signal=None):
@@ -571,9 +572,10 @@ def xfc_step(xfc, X, pos_rows, pos_labels, nnz, dX_out, hp, mo, wd, want_loss, w
     for ci, l0 in enumerate(chunks):
         l1 = min(xfc.Ls, l0 + xfc.chunk)
         Wc, Mc = xfc.W[l0:l1], xfc.M[l0:l1]
-        v2 = xfc_v2() and not want_loss and D % 64 == 0
+        v2 = xfc_v2() and D % 64 == 0
         if v2:
-            xfc_logits_grad_v2(Wc, X, Gt, ldG, pos_rows, pos_labels, nnz, l0, wait=wait if ci == 0 else None)
+            xfc_logits_grad_v2(Wc, X, Gt, ldG, pos_rows, pos_labels, nnz, l0, wait=wait if ci == 0 else None,
+                               loss_acc=loss)
         else:
             xfc_logits_grad(Wc, X, Gt, ldG, pos_rows, pos_labels, nnz, l0, loss_acc=loss, wait=wait if ci == 0 else None)
         if want_loss and ci == 0:
