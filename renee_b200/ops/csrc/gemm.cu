@@ -1,5 +1,5 @@
-// Encoder GEMMs for sm_100a: one persistent tcgen05 / TMEM kernel family with the element-wise neighbours of
-// every linear layer fused into the epilogue.  They stand in for the cuBLAS calls behind the reference's HF
+// GEMMs for sm_100a: one persistent tcgen05 / TMEM kernel family with the element-wise neighbours of every linear
+// layer of the encoder, and the three products of the classifier step, fused into the epilogue.  They stand in for the cuBLAS calls behind the reference's HF
 // nn.Linear layers and its FP32Linear (main.py:126-129, dl_base.py:104-111) and for the ATen kernels around
 // them (bias add, GELU, dropout, residual add, GELU backward, bias-gradient column sums).
 //
@@ -14,9 +14,13 @@
 //              GELU_BWD             C = acc * gelu'(R) ;  column sums of C -> bias gradient accumulators
 //              SPLITK               fp32 partials reduced in L2, the last CTA of a tile converts and stores
 //              SIGMOID_POS          C = sigmoid(acc) - Y: the classifier's logit gradient; Y from a label-sorted list of
-//                                   positives applied to the staged tile in shared memory before it is stored
+//                                   positives applied to the staged tile in shared memory before it is stored; on
+//                                   loss-sampling steps also the sum of softplus(acc) (parity: dl_base.py:572-594)
 //              DX                   dX += scale * acc by vector reductions into an fp32 matrix (contraction over the
 //                                   labels of a chunk, split over the CTAs); the last CTA raises the peers' flags
+//              DW_SGD               classifier weights: W and momentum tiles [128 x 64] come in by TMA under the main loop,
+//                                   m = mo m + (acc + wd w), w -= lr m (stochastic rounding optional) in shared memory,
+//                                   both tiles leave by TMA; dW = Gt X is never stored (parity: dl_base.py:623-633, 343-344)
 //              TOPK                 nothing is stored: every epilogue thread keeps the 8 largest entries of its row
 //                                   over all the tiles its CTA visits and writes them as candidates at the end
 //                                   (prediction: X W^T is never materialised; parity: dl_base.py:745-756)
