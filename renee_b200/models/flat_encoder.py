@@ -23,6 +23,7 @@ State-dict keys are those of HF DistilBERT (see :mod:`renee_b200.models.encoder`
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 
 import torch
@@ -49,7 +50,7 @@ def _no_decay(name: str) -> bool:
 # library GEMMs: 16384 tokens 7.14 / 7.12 ms, 8192: 3.76 / 3.61, 4096: 2.41 / 2.23, 2048: 1.82 / 1.53, 1024: 1.48 /
 # 1.22 -- below 8192 tokens the fixed cost per launch of a persistent kernel (TMEM allocation, cluster start-up, a
 # serial K loop on the few SMs the tiles cover) outweighs the fused epilogues.
-OWN_GEMM_MIN_TOKENS = 8192
+OWN_GEMM_MIN_TOKENS = int(os.environ.get("RENEE_B200_OWN_GEMM_MIN_TOKENS", "8192"))
 
 
 @dataclass
@@ -135,7 +136,6 @@ class FlatEncoder:
         self._own_supported = False
         self._wgrad_stream = None
         if self.device.type == "cuda" and act_dtype != torch.float32:
-            import os
             from ..ops import cuda as cu
             # RENEE_B200_OWN_GEMM: 1 = the own tcgen05 GEMMs with fused epilogues always, 0 = library GEMMs + separate
             # element-wise kernels, auto (default) = own from OWN_GEMM_MIN_TOKENS tokens per step and GPU upwards
